@@ -1,0 +1,161 @@
+/*
+ * mlb.h - C ABI of the B200 decode path (libmini_llm_b200.so).
+ *
+ * The reference (mini-llm-cuda) has no FFI: its decode path is a set of C++ free functions
+ * over global pointers. Each entry point below names the reference interface it stands in
+ * for. All functions return 0 (MLB_OK) on success and a negative mlb_status otherwise;
+ * mlb_last_error() gives the thread-local message. The library never exits, aborts or
+ * traps; every device-side wait is bounded. Buffers passed in are caller-owned HOST memory
+ * unless a parameter says otherwise; objects returned are library-owned until *_free.
+ * One mlb_session is driven by one host thread at a time; sessions on different GPUs may
+ * be driven concurrently from different threads. There is no CPU fallback: without a CUDA
+ * device every compute entry point fails with MLB_E_CUDA.
+ */
+#ifndef MLB_H_
+#define MLB_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MLB_MAX_LAYERS 128
+
+typedef enum mlb_status {
+    MLB_OK = 0,
+    MLB_E_INVALID = -1,      /* bad argument or inconsistent configuration            */
+    MLB_E_IO = -2,           /* file missing / unreadable                             */
+    MLB_E_FORMAT = -3,       /* malformed or truncated model.bin / JSON               */
+    MLB_E_CUDA = -4,         /* CUDA runtime error (message holds the CUDA string)    */
+    MLB_E_NOMEM = -5,        /* host or device allocation failed                      */
+    MLB_E_KV_FULL = -6,      /* the paged KV pool has no free page                    */
+    MLB_E_CONTEXT_FULL = -7, /* a sequence reached max_context                        */
+    MLB_E_TIMEOUT = -8,      /* a bounded device-side wait ran out                    */
+    MLB_E_UNSUPPORTED = -9   /* shape outside what the kernels are built for          */
+} mlb_status;
+
+typedef enum mlb_dtype {
+    MLB_DT_DEFAULT = 0,      /* as the file's config says (float32 when it says nothing) */
+    MLB_DT_F32 = 1,
+    MLB_DT_BF16 = 2,
+    MLB_DT_FP8_E4M3 = 3      /* weights only: per-output-row fp32 scale = max|row|/448 */
+} mlb_dtype;
+
+typedef enum mlb_layer_type { MLB_LAYER_ATTENTION = 0, MLB_LAYER_DELTA_NET = 1 } mlb_layer_type;
+
+/* Runtime form of the reference's compile-time dims (network_meta.h:3-20). As an override
+ * for mlb_model_load, a field < 0 (NaN for the floats) means "take it from the file". */
+typedef struct mlb_config {
+    int32_t dim, layers, heads, kv_heads, head_dim, ffn_dim, vocab, max_context;
+    int32_t ple_dim;                 /* per-layer-embedding width, 0 = off                 */
+    int32_t qk_norm, query_gating;   /* CONFIG_QK_RMS_NORM / CONFIG_QUERY_GATING           */
+    int32_t dn_key_dim, dn_value_dim;/* gated delta-net per-head dims                      */
+    int32_t weight_dtype, kv_dtype;  /* mlb_dtype                                          */
+    int32_t layer_types_set;         /* override only: non-zero = layer_types[] is valid   */
+    float rope_theta, rms_eps;
+    uint8_t layer_types[MLB_MAX_LAYERS]; /* execution order (file block N-1 runs first)   */
+} mlb_config;
+
+typedef struct mlb_sampling {
+    int32_t mode;            /* 0 = greedy (argmax of logits, lowest index on ties), 1 = top-k */
+    int32_t top_k;           /* 1..1024 */
+    float temperature;       /* > 0 */
+    const uint64_t* seeds;   /* [batch] Philox keys, or NULL: key = sequence index */
+} mlb_sampling;
+
+typedef struct mlb_model mlb_model;     /* device weights of ONE GPU                     */
+typedef struct mlb_session mlb_session; /* KV pages, delta-net state, stream for B seqs  */
+
+/* One row per kernel kind launched by a decode step, filled by mlb_profile_decode. */
+typedef struct mlb_kernel_stat {
+    char name[48];
+    int32_t launches;
+    float total_ms;          /* CUDA-event time on the session's stream, summed           */
+    uint64_t bytes;          /* algorithmic bytes moved, summed over the launches         */
+    uint64_t flops;          /* algorithmic flops, summed                                 */
+} mlb_kernel_stat;
+
+void mlb_config_init(mlb_config* cfg);  /* fills every field with "unset" */
+
+/* Replaces loadModel (load_model.h:6, load_model.cu:286-481) + the weight half of
+ * allocateMemory (memory_allocation.cu:354-499): parses the container, uploads the
+ * matrices in their file order (row-major [out][in] is the streaming layout; the
+ * reference's host transpose is not needed) and rounds them to `weight_dtype`. */
+int mlb_model_load(const char* path, int device, const mlb_config* override_or_null, mlb_model** out);
+int mlb_model_get_config(const mlb_model* m, mlb_config* out);
+/* Bytes of every tensor a decode step streams once (projections, tied embedding/LM head,
+ * gains, scales), the W term of the per-step roofline. */
+uint64_t mlb_model_weight_bytes(const mlb_model* m);
+void mlb_model_free(mlb_model* m);
+
+/* Host-only: parse the header of a model file (no GPU needed). */
+int mlb_file_inspect(const char* path, const mlb_config* override_or_null, mlb_config* out,
+                     uint64_t* n_params);
+
+/* Replaces the activation half of allocateMemory (memory_allocation.cu:500-552): instead of
+ * maxL-sized scratch per op it owns a paged KV cache (pages of kv_block positions),
+ * fp32 delta-net state and one decode step's scratch. kv_pages = 0 sizes the pool for
+ * batch * max_context. */
+int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_block, int kv_pages,
+                    mlb_session** out);
+int mlb_session_reset(mlb_session* s);
+void mlb_session_free(mlb_session* s);
+
+/* Replaces loadStoryContext's upload (main.cu:166) and the prompt part of the reference's
+ * recompute-everything loop: ingests tokens[b*stride .. +lens[b]) for every sequence. After
+ * it, position lens[b]-1 holds the last prompt token as the pending input of the next step. */
+int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride);
+
+/* Replaces one iteration of the while loop of runInferenceLoop
+ * (inference_orchestrator.cu:64-160): forward for the pending token of every sequence, pick
+ * the next token on the device, append it. in_tokens (nullable) overrides the pending tokens
+ * from the host first, as the reference's per-step upload does (:154). out_tokens receives
+ * [batch] ids (-1 for a sequence that is at max_context). */
+int mlb_decode_step(mlb_session* s, const mlb_sampling* sampling, const int32_t* in_tokens,
+                    int32_t* out_tokens);
+/* n steps back to back without host round trips; out_tokens is [batch][n]. */
+int mlb_decode_n(mlb_session* s, const mlb_sampling* sampling, int n, int32_t* out_tokens);
+/* As mlb_decode_n, timing each step with CUDA events on the session's stream; flush_l2
+ * writes a buffer larger than L2 before each step, outside the timed bracket. */
+int mlb_decode_timed(mlb_session* s, const mlb_sampling* sampling, int n, int flush_l2,
+                     float* step_ms, int32_t* out_tokens);
+/* Runs n steps kernel by kernel with events around every launch. */
+int mlb_profile_decode(mlb_session* s, const mlb_sampling* sampling, int n, int flush_l2,
+                       mlb_kernel_stat* stats, int max_stats, int* n_stats);
+
+/* Parity probes, off the timed path. Logits of the LAST executed step, fp32 [batch][vocab]
+ * (the reference keeps them in vocabScores_DEVICE, inference.cu:738). */
+int mlb_get_logits(mlb_session* s, float* out);
+/* Column L-1 of the reference's vocabScores_postSoftmax_DEVICE (inference.cu:745-749) for
+ * one sequence: softmax of the last step's logits, [vocab]. */
+int mlb_get_probs_col(mlb_session* s, int seq, float* out);
+int mlb_session_positions(mlb_session* s, int32_t* out /* [batch] */);
+/* Algorithmic bytes of the NEXT decode step at the current positions: weights once, KV read
+ * + append, delta-net state read + write, embedding/PLE rows. */
+int mlb_session_step_bytes(mlb_session* s, uint64_t* weights, uint64_t* kv, uint64_t* state,
+                           uint64_t* rows);
+/* Kernels launched per decode step by the current configuration. */
+int mlb_session_launches_per_step(mlb_session* s);
+
+/* Host-only page allocator of the KV cache, exposed so that its failure paths can be
+ * tested without a device. */
+typedef struct mlb_kv_alloc mlb_kv_alloc;
+int mlb_kv_alloc_new(int num_pages, int batch, int max_pages_per_seq, mlb_kv_alloc** out);
+int mlb_kv_alloc_ensure(mlb_kv_alloc* a, int seq, int n_positions, int block);
+int mlb_kv_alloc_table(const mlb_kv_alloc* a, int seq, int32_t* out, int max_entries);
+int mlb_kv_alloc_free_pages(const mlb_kv_alloc* a);
+void mlb_kv_alloc_release(mlb_kv_alloc* a, int seq);
+void mlb_kv_alloc_free(mlb_kv_alloc* a);
+
+/* RoPE table exactly as getPreComputedRopeTheta builds it (inference.h:4,
+ * inference.cu:364-374): [max_len][head_dim] interleaved (cos, sin), host float math. */
+void mlb_rope_table(float* table, int max_len, int head_dim, float base);
+
+const char* mlb_last_error(void);
+const char* mlb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLB_H_ */

@@ -1,0 +1,1048 @@
+// Host side of the decode path: model upload, session state (paged KV cache, delta-net
+// state, step scratch), the launch chain of one decode step, CUDA-graph replay, and the C ABI
+// declared in include/mlb.h.
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../../include/mlb.h"
+#include "kernels.cuh"
+#include "model_file.h"
+
+namespace mlb {
+
+// --------------------------------------------------------------------------------------
+// errors
+// --------------------------------------------------------------------------------------
+static thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+#define CU(expr)                                                                              \
+    do {                                                                                      \
+        cudaError_t e__ = (expr);                                                             \
+        if (e__ != cudaSuccess)                                                               \
+            return fail(MLB_E_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
+    } while (0)
+
+static size_t elt_size(int dt) { return dt == MLB_DT_F32 ? 4 : (dt == MLB_DT_BF16 ? 2 : 1); }
+static int ple_dtype(int wdt) { return wdt == MLB_DT_FP8_E4M3 ? MLB_DT_BF16 : wdt; }
+
+// --------------------------------------------------------------------------------------
+// KV page allocator (host only)
+// --------------------------------------------------------------------------------------
+}  // namespace mlb
+
+struct mlb_kv_alloc {
+    std::vector<int> free_list;                 // stack; back() is handed out next
+    std::vector<std::vector<int>> seq_pages;
+    int max_pages_per_seq = 0;
+    int num_pages = 0;
+};
+
+namespace mlb {
+
+static int kv_ensure(mlb_kv_alloc* a, int seq, int n_positions, int block) {
+    if (!a || seq < 0 || seq >= (int)a->seq_pages.size() || block <= 0 || n_positions < 0)
+        return fail(MLB_E_INVALID, "kv allocator: bad argument");
+    int need = (n_positions + block - 1) / block;
+    if (need > a->max_pages_per_seq)
+        return fail(MLB_E_CONTEXT_FULL, "sequence %d needs %d pages, the page table holds %d", seq, need, a->max_pages_per_seq);
+    auto& pages = a->seq_pages[seq];
+    while ((int)pages.size() < need) {
+        if (a->free_list.empty())
+            return fail(MLB_E_KV_FULL, "KV page pool exhausted (%d pages) while growing sequence %d", a->num_pages, seq);
+        pages.push_back(a->free_list.back());
+        a->free_list.pop_back();
+    }
+    return MLB_OK;
+}
+
+// --------------------------------------------------------------------------------------
+// model
+// --------------------------------------------------------------------------------------
+struct DevLayer {
+    int type = MLB_LAYER_ATTENTION;
+    float *g1 = nullptr, *g2 = nullptr, *gq = nullptr, *gk = nullptr;
+    void* Wqkv = nullptr; float* Sqkv = nullptr; int n_qkv = 0;
+    int nq = 0, nk = 0, nv = 0, ng = 0;
+    void* Wo = nullptr; float* So = nullptr; int o_in = 0;
+    void *W1a = nullptr, *W1b = nullptr, *W2 = nullptr;
+    float *S1a = nullptr, *S1b = nullptr, *S2 = nullptr;
+    void *pleT = nullptr, *pleP = nullptr;
+};
+
+}  // namespace mlb
+
+struct mlb_model {
+    mlb_config cfg;
+    int device = 0;
+    void* E = nullptr; float* Es = nullptr; float* g_final = nullptr; float* rope = nullptr;
+    std::vector<mlb::DevLayer> layers;      // execution order
+    uint64_t weight_bytes = 0;
+    std::vector<void*> allocs;
+};
+
+namespace mlb {
+
+struct Uploader {
+    mlb_model* m;
+    const std::vector<unsigned char>* file;
+    std::vector<float> hbuf;
+    float* dstage = nullptr;
+    size_t dstage_elems = 0;
+
+    int dev_alloc(void** p, size_t bytes) {
+        cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+        if (e != cudaSuccess) return fail(MLB_E_NOMEM, "cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+        m->allocs.push_back(*p);
+        return MLB_OK;
+    }
+    // file tensor -> float32 on the device staging buffer
+    int stage(const TensorDesc& t) {
+        size_t n = (size_t)t.rows * t.cols;
+        const unsigned char* src = file->data() + t.offset;
+        const float* hsrc;
+        if (t.dtype == FD_F32) {
+            hsrc = reinterpret_cast<const float*>(src);
+        } else {
+            hbuf.resize(n);
+            convert_to_f32(src, t.dtype, n, hbuf.data());
+            hsrc = hbuf.data();
+        }
+        CU(cudaMemcpy(dstage, hsrc, n * 4, cudaMemcpyHostToDevice));
+        return MLB_OK;
+    }
+    // staged float32 [rows][cols] -> typed matrix rows [row_off, row_off+rows) of dst
+    int emit(const TensorDesc& t, int dt, void* dst, size_t row_off, float* scale) {
+        size_t n = (size_t)t.rows * t.cols;
+        size_t off = row_off * (size_t)t.cols;
+        if (dt == MLB_DT_F32) {
+            CU(cudaMemcpy(static_cast<float*>(dst) + off, dstage, n * 4, cudaMemcpyDeviceToDevice));
+        } else if (dt == MLB_DT_BF16) {
+            cvt_f32_to_bf16_kernel<<<1024, 256>>>(dstage, static_cast<bf16_t*>(dst) + off, n);
+            CU(cudaGetLastError());
+        } else {
+            int warps = 8;
+            quant_fp8_rows_kernel<<<(t.rows + warps - 1) / warps, warps * 32>>>(dstage, static_cast<fp8_t*>(dst) + off,
+                                                                              scale + row_off, t.rows, t.cols);
+            CU(cudaGetLastError());
+        }
+        CU(cudaDeviceSynchronize());
+        return MLB_OK;
+    }
+    int vec(const TensorDesc* t, float** out) {
+        int rc = dev_alloc(reinterpret_cast<void**>(out), (size_t)t->rows * 4);
+        if (rc) return rc;
+        if ((rc = stage(*t))) return rc;
+        CU(cudaMemcpy(*out, dstage, (size_t)t->rows * 4, cudaMemcpyDeviceToDevice));
+        m->weight_bytes += (uint64_t)t->rows * 4;
+        return MLB_OK;
+    }
+    // a matrix made of several file tensors stacked by rows
+    int stacked(const std::vector<const TensorDesc*>& parts, int dt, void** W, float** S, int* total_rows) {
+        int rows = 0, cols = parts[0]->cols;
+        for (auto* t : parts) rows += t->rows;
+        int rc = dev_alloc(W, (size_t)rows * cols * elt_size(dt));
+        if (rc) return rc;
+        *S = nullptr;
+        if (dt == MLB_DT_FP8_E4M3 && (rc = dev_alloc(reinterpret_cast<void**>(S), (size_t)rows * 4))) return rc;
+        size_t off = 0;
+        for (auto* t : parts) {
+            if ((rc = stage(*t))) return rc;
+            if ((rc = emit(*t, dt, *W, off, *S))) return rc;
+            off += t->rows;
+        }
+        if (total_rows) *total_rows = rows;
+        m->weight_bytes += (uint64_t)rows * cols * elt_size(dt) + (dt == MLB_DT_FP8_E4M3 ? (uint64_t)rows * 4 : 0);
+        return MLB_OK;
+    }
+};
+
+static int validate_for_kernels(const mlb_config& c) {
+    const int gran = c.weight_dtype == MLB_DT_FP8_E4M3 ? 16 : (c.weight_dtype == MLB_DT_BF16 ? 8 : 4);
+    if (c.dim % gran || c.ffn_dim % gran) return fail(MLB_E_UNSUPPORTED, "dim and ffn_dim must be multiples of %d for this weight type", gran);
+    if (c.ple_dim % 8) return fail(MLB_E_UNSUPPORTED, "ple_dim must be a multiple of 8");
+    bool has_attn = false, has_dn = false;
+    for (int i = 0; i < c.layers; ++i) (c.layer_types[i] == MLB_LAYER_ATTENTION ? has_attn : has_dn) = true;
+    if (has_attn) {
+        if (c.head_dim != 64 && c.head_dim != 128) return fail(MLB_E_UNSUPPORTED, "attention head_dim must be 64 or 128 (got %d)", c.head_dim);
+        int g = c.heads / c.kv_heads;
+        if (g != 1 && g != 2 && g != 4 && g != 8) return fail(MLB_E_UNSUPPORTED, "heads/kv_heads must be 1, 2, 4 or 8 (got %d)", g);
+        if ((c.heads * c.head_dim) % gran) return fail(MLB_E_UNSUPPORTED, "heads*head_dim must be a multiple of %d", gran);
+    }
+    if (has_dn) {
+        if (c.dn_key_dim != 64 && c.dn_key_dim != 128) return fail(MLB_E_UNSUPPORTED, "delta-net key dim must be 64 or 128 (got %d)", c.dn_key_dim);
+        if ((c.heads * c.dn_value_dim) % gran) return fail(MLB_E_UNSUPPORTED, "heads*dn_value_dim must be a multiple of %d", gran);
+    }
+    if (c.vocab < 2) return fail(MLB_E_INVALID, "vocabulary too small");
+    return MLB_OK;
+}
+
+static void free_model(mlb_model* m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    for (void* p : m->allocs) cudaFree(p);
+    delete m;
+}
+
+}  // namespace mlb
+
+using namespace mlb;
+
+extern "C" void mlb_rope_table(float* table, int max_len, int head_dim, float base) {
+    // Same host arithmetic as getPreComputedRopeTheta (inference.cu:364-374): float powf,
+    // integer position times the float frequency, cosf / sinf.
+    const int pairs = head_dim / 2;
+    for (int pos = 0; pos < max_len; ++pos) {
+        for (int i = 0; i < pairs; ++i) {
+            float theta = pos * powf(base, (-2.0f * i / head_dim));
+            table[(size_t)pos * head_dim + 2 * i] = cosf(theta);
+            table[(size_t)pos * head_dim + 2 * i + 1] = sinf(theta);
+        }
+    }
+}
+
+extern "C" int mlb_file_inspect(const char* path, const mlb_config* ov, mlb_config* out, uint64_t* n_params) {
+    if (!path || !out) return fail(MLB_E_INVALID, "null argument");
+    std::vector<unsigned char> buf;
+    std::string err;
+    int rc = read_file(path, &buf, &err);
+    if (rc) return fail(rc, "%s", err.c_str());
+    ParsedModel pm;
+    rc = parse_model_header(buf.data(), buf.size(), buf.size(), ov, &pm, &err);
+    if (rc) return fail(rc, "%s", err.c_str());
+    *out = pm.cfg;
+    if (n_params) *n_params = pm.n_params;
+    return MLB_OK;
+}
+
+extern "C" int mlb_model_load(const char* path, int device, const mlb_config* ov, mlb_model** out) {
+    if (!path || !out) return fail(MLB_E_INVALID, "null argument");
+    *out = nullptr;
+    std::vector<unsigned char> buf;
+    std::string err;
+    int rc = read_file(path, &buf, &err);
+    if (rc) return fail(rc, "%s", err.c_str());
+    ParsedModel pm;
+    rc = parse_model_header(buf.data(), buf.size(), buf.size(), ov, &pm, &err);
+    if (rc) return fail(rc, "%s", err.c_str());
+    if ((rc = validate_for_kernels(pm.cfg))) return rc;
+    int ndev = 0;
+    cudaError_t ce = cudaGetDeviceCount(&ndev);
+    if (ce != cudaSuccess || ndev == 0)
+        return fail(MLB_E_CUDA, "no CUDA device available (%s); this library has no CPU path", cudaGetErrorString(ce));
+    if (device < 0 || device >= ndev) return fail(MLB_E_INVALID, "device %d out of range (0..%d)", device, ndev - 1);
+    CU(cudaSetDevice(device));
+
+    mlb_model* m = new mlb_model();
+    m->cfg = pm.cfg;
+    m->device = device;
+    const mlb_config& c = m->cfg;
+    const int wdt = c.weight_dtype, pdt = ple_dtype(wdt);
+    Uploader up;
+    up.m = m;
+    up.file = &buf;
+    size_t max_elems = 0;
+    for (auto& t : pm.tensors) max_elems = std::max(max_elems, (size_t)t.rows * t.cols);
+    up.dstage_elems = max_elems;
+    if (cudaMalloc(reinterpret_cast<void**>(&up.dstage), max_elems * 4) != cudaSuccess) {
+        free_model(m);
+        return fail(MLB_E_NOMEM, "cudaMalloc of the %zu-byte staging buffer failed", max_elems * 4);
+    }
+#define UP(expr) do { int r__ = (expr); if (r__) { cudaFree(up.dstage); free_model(m); return r__; } } while (0)
+    UP(up.stacked({pm.find(-1, "tokenEmbeddings")}, wdt, &m->E, &m->Es, nullptr));
+    UP(up.vec(pm.find(-1, "finalRMSNormGamma"), &m->g_final));
+    m->layers.resize(c.layers);
+    for (int i = 0; i < c.layers; ++i) {
+        const int blk = c.layers - 1 - i;               // block N-1 runs first (inference.cu:384-385)
+        DevLayer& L = m->layers[i];
+        L.type = c.layer_types[i];
+        UP(up.vec(pm.find(blk, "rmsGamma"), &L.g1));
+        UP(up.vec(pm.find(blk, "rmsGamma2"), &L.g2));
+        std::vector<const TensorDesc*> parts = {pm.find(blk, "queryWeights"), pm.find(blk, "keyWeights"), pm.find(blk, "valueWeights")};
+        L.nq = parts[0]->rows; L.nk = parts[1]->rows; L.nv = parts[2]->rows; L.ng = 0;
+        if (L.type == MLB_LAYER_ATTENTION) {
+            if (c.query_gating) { parts.push_back(pm.find(blk, "gatedQueryWeights")); L.ng = parts.back()->rows; }
+            if (c.qk_norm) {
+                UP(up.vec(pm.find(blk, "queryRMSGamma"), &L.gq));
+                UP(up.vec(pm.find(blk, "keyRMSGamma"), &L.gk));
+            }
+        } else {
+            parts.push_back(pm.find(blk, "betaWeights"));
+            parts.push_back(pm.find(blk, "decayWeights"));
+        }
+        UP(up.stacked(parts, wdt, &L.Wqkv, &L.Sqkv, &L.n_qkv));
+        const TensorDesc* wo = pm.find(blk, "outputProjectionWeights");
+        L.o_in = wo->cols;
+        UP(up.stacked({wo}, wdt, &L.Wo, &L.So, nullptr));
+        UP(up.stacked({pm.find(blk, "feedForwardWeights1A")}, wdt, &L.W1a, &L.S1a, nullptr));
+        UP(up.stacked({pm.find(blk, "feedForwardWeights1B")}, wdt, &L.W1b, &L.S1b, nullptr));
+        UP(up.stacked({pm.find(blk, "feedForwardWeights2")}, wdt, &L.W2, &L.S2, nullptr));
+        if (c.ple_dim > 0) {
+            float* unused = nullptr;
+            UP(up.stacked({pm.find(blk, "pleTable")}, pdt, &L.pleT, &unused, nullptr));
+            UP(up.stacked({pm.find(blk, "pleProjection")}, pdt, &L.pleP, &unused, nullptr));
+            // only one table row per sequence is read per step, not the whole table
+            m->weight_bytes -= (uint64_t)c.vocab * c.ple_dim * elt_size(pdt);
+        }
+    }
+    {
+        std::vector<float> tab((size_t)c.max_context * c.head_dim);
+        mlb_rope_table(tab.data(), c.max_context, c.head_dim, c.rope_theta);
+        UP(up.dev_alloc(reinterpret_cast<void**>(&m->rope), tab.size() * 4));
+        cudaError_t e = cudaMemcpy(m->rope, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) { cudaFree(up.dstage); free_model(m); return fail(MLB_E_CUDA, "rope table upload: %s", cudaGetErrorString(e)); }
+    }
+#undef UP
+    cudaFree(up.dstage);
+    *out = m;
+    return MLB_OK;
+}
+
+extern "C" int mlb_model_get_config(const mlb_model* m, mlb_config* out) {
+    if (!m || !out) return fail(MLB_E_INVALID, "null argument");
+    *out = m->cfg;
+    return MLB_OK;
+}
+extern "C" uint64_t mlb_model_weight_bytes(const mlb_model* m) { return m ? m->weight_bytes : 0; }
+extern "C" void mlb_model_free(mlb_model* m) { free_model(m); }
+
+// --------------------------------------------------------------------------------------
+// session
+// --------------------------------------------------------------------------------------
+namespace mlb {
+enum ChainKind { CHAIN_PREFILL = 0, CHAIN_GREEDY = 1, CHAIN_TOPK = 2 };
+
+struct LaunchRec {
+    const char* name;
+    uint64_t bytes, flops;
+    cudaEvent_t e0, e1;
+};
+struct Recorder {
+    cudaStream_t st;
+    std::vector<LaunchRec> recs;
+    int begin(const char* name, uint64_t bytes, uint64_t flops) {
+        LaunchRec r{name, bytes, flops, nullptr, nullptr};
+        CU(cudaEventCreate(&r.e0));
+        CU(cudaEventCreate(&r.e1));
+        CU(cudaEventRecord(r.e0, st));
+        recs.push_back(r);
+        return MLB_OK;
+    }
+    int end() {
+        CU(cudaEventRecord(recs.back().e1, st));
+        return MLB_OK;
+    }
+};
+}  // namespace mlb
+
+struct mlb_session {
+    mlb_model* m = nullptr;
+    int B = 0, max_ctx = 0, max_pages = 0, kv_pages = 0;
+    cudaStream_t stream = nullptr;
+    int *pos = nullptr, *tok = nullptr, *limit_prefill = nullptr, *limit_decode = nullptr;
+    int *prompt = nullptr, *out_ring = nullptr, *out_idx = nullptr, *page_table = nullptr;
+    unsigned long long* seeds = nullptr;
+    float *x = nullptr, *qbuf = nullptr, *gbuf = nullptr, *abuf = nullptr, *hbuf = nullptr, *raw = nullptr;
+    float *logits = nullptr, *part = nullptr, *part_val = nullptr, *probe = nullptr;
+    int *part_idx = nullptr, *attn_ticket = nullptr, *lm_ticket = nullptr;
+    std::vector<void*> kpool, vpool;
+    std::vector<float*> state;
+    std::vector<void*> allocs;
+    // host mirrors
+    std::vector<int> h_pos;
+    std::vector<int> h_table;
+    bool table_dirty = true;
+    bool have_logits = false;
+    mlb_kv_alloc alloc;
+    int splits = 1, lm_rows = 32, lm_parts = 1, raw_stride = 0, max_q = 0;
+    // graphs
+    cudaGraphExec_t graphs[3] = {nullptr, nullptr, nullptr};
+    int g_topk = -1; float g_temp = 0.f;
+    int cur_topk = 50; float cur_temp = 1.f;
+    int launches_per_step[3] = {0, 0, 0};
+    float4* flush_buf = nullptr; size_t flush_n = 0;
+    int* pinned_tok = nullptr;
+};
+
+namespace mlb {
+
+static int sess_alloc(mlb_session* s, void** p, size_t bytes, bool zero) {
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+    if (e != cudaSuccess) return fail(MLB_E_NOMEM, "cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    s->allocs.push_back(*p);
+    if (zero) CU(cudaMemset(*p, 0, bytes ? bytes : 16));
+    return MLB_OK;
+}
+
+static void free_session(mlb_session* s) {
+    if (!s) return;
+    cudaSetDevice(s->m->device);
+    if (s->stream) cudaStreamSynchronize(s->stream);
+    for (auto& g : s->graphs) if (g) cudaGraphExecDestroy(g);
+    for (void* p : s->allocs) cudaFree(p);
+    if (s->pinned_tok) cudaFreeHost(s->pinned_tok);
+    if (s->stream) cudaStreamDestroy(s->stream);
+    delete s;
+}
+
+static StepCtl make_ctl(mlb_session* s, int kind) {
+    StepCtl c;
+    c.B = s->B;
+    c.pos = s->pos;
+    c.tok = s->tok;
+    c.limit = kind == CHAIN_PREFILL ? s->limit_prefill : s->limit_decode;
+    c.prompt = kind == CHAIN_PREFILL ? s->prompt : nullptr;
+    c.prompt_stride = s->max_ctx;
+    c.out_ring = s->out_ring;
+    c.out_idx = s->out_idx;
+    c.out_cap = s->max_ctx;
+    return c;
+}
+
+static int pick_bt(int B, size_t per_seq_floats) {
+    int bt = B >= 8 ? 8 : (B >= 4 ? 4 : (B >= 2 ? 2 : 1));
+    while (bt > 1 && (size_t)bt * per_seq_floats * 4 > 200 * 1024) bt >>= 1;
+    return bt;
+}
+
+template <typename T, typename T2, typename KVT>
+struct Chain {
+    template <int MODE>
+    static int gemv(mlb_session* s, const StepCtl& c, GemvParams p, int R, Recorder* rec, const char* name) {
+        constexpr int RW = (MODE == GEMV_SWIGLU) ? 2 : 4;
+        p.R = R;
+        const size_t per_seq = (size_t)p.K + p.Kp + R + 1;
+        const int BT = pick_bt(s->B, per_seq);
+        if (per_seq * 4 > 200 * 1024) return fail(MLB_E_UNSUPPORTED, "projection input of %d floats does not fit shared memory", p.K);
+        const int warps = std::max(1, std::min(8, R / RW));
+        dim3 grid((p.N + R - 1) / R, (s->B + BT - 1) / BT);
+        const size_t smem = (size_t)BT * per_seq * 4;
+        if (rec) {
+            const uint64_t wbytes = (uint64_t)p.N * p.K * sizeof(T) * (MODE == GEMV_SWIGLU ? 2 : 1) +
+                                    (uint64_t)p.N * p.Kp * sizeof(T2) + (p.wscale ? (uint64_t)p.N * 4 : 0);
+            const uint64_t abytes = (uint64_t)s->B * ((uint64_t)p.K + p.N) * 4;
+            int rc = rec->begin(name, wbytes + abytes, 2ull * p.N * (p.K + p.Kp) * s->B * (MODE == GEMV_SWIGLU ? 2 : 1));
+            if (rc) return rc;
+        }
+        switch (BT) {
+            case 1: gemv_kernel<T, T2, KVT, 1, MODE><<<grid, warps * 32, smem, s->stream>>>(c, p); break;
+            case 2: gemv_kernel<T, T2, KVT, 2, MODE><<<grid, warps * 32, smem, s->stream>>>(c, p); break;
+            case 4: gemv_kernel<T, T2, KVT, 4, MODE><<<grid, warps * 32, smem, s->stream>>>(c, p); break;
+            default: gemv_kernel<T, T2, KVT, 8, MODE><<<grid, warps * 32, smem, s->stream>>>(c, p); break;
+        }
+        CU(cudaGetLastError());
+        if (rec) return rec->end();
+        return MLB_OK;
+    }
+
+    template <int MODE>
+    static int configure_mode() {
+        const int big = 200 * 1024;
+        CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 1, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 2, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 4, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 8, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        return MLB_OK;
+    }
+    static int configure() {
+        int rc;
+        if ((rc = configure_mode<GEMV_RAW>())) return rc;
+        if ((rc = configure_mode<GEMV_RESID>())) return rc;
+        if ((rc = configure_mode<GEMV_SWIGLU>())) return rc;
+        if ((rc = configure_mode<GEMV_QKV>())) return rc;
+        if ((rc = configure_mode<GEMV_LMHEAD>())) return rc;
+        return MLB_OK;
+    }
+
+    template <int HD>
+    static int attn_g(mlb_session* s, const StepCtl& c, const AttnParams& p, int G) {
+        dim3 grid(s->splits, p.kv_heads, s->B);
+        switch (G) {
+            case 1: attn_decode_kernel<KVT, HD, 1><<<grid, 128, 0, s->stream>>>(c, p); break;
+            case 2: attn_decode_kernel<KVT, HD, 2><<<grid, 128, 0, s->stream>>>(c, p); break;
+            case 4: attn_decode_kernel<KVT, HD, 4><<<grid, 128, 0, s->stream>>>(c, p); break;
+            default: attn_decode_kernel<KVT, HD, 8><<<grid, 128, 0, s->stream>>>(c, p); break;
+        }
+        CU(cudaGetLastError());
+        return MLB_OK;
+    }
+
+    // One decode (or prefill) step as a chain of launches on the session's stream.
+    static int run(mlb_session* s, int kind, Recorder* rec, int* n_launches) {
+        const mlb_model* m = s->m;
+        const mlb_config& cfg = m->cfg;
+        const StepCtl c = make_ctl(s, kind);
+        const int d = cfg.dim, F = cfg.ffn_dim, B = s->B, p = cfg.ple_dim;
+        int launches = 0, rc;
+
+        if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * (d * sizeof(T) + (uint64_t)p * sizeof(T2) + (uint64_t)d * 4) + (uint64_t)d * p * sizeof(T2), 0))) return rc;
+        embed_kernel<T, T2><<<B, 256, (size_t)p * 4, s->stream>>>(c, static_cast<const T*>(m->E), m->Es, d,
+                                                                 static_cast<const T2*>(m->layers[0].pleT),
+                                                                 static_cast<const T2*>(m->layers[0].pleP), p, s->x);
+        CU(cudaGetLastError());
+        if (rec && (rc = rec->end())) return rc;
+        ++launches;
+
+        for (int i = 0; i < cfg.layers; ++i) {
+            const DevLayer& L = m->layers[i];
+            GemvParams g;
+            std::memset(&g, 0, sizeof g);
+            g.W = L.Wqkv; g.wscale = L.Sqkv; g.N = L.n_qkv; g.K = d;
+            g.xin = s->x; g.gain = L.g1; g.eps = cfg.rms_eps; g.do_norm = 1;
+            if (L.type == MLB_LAYER_ATTENTION) {
+                g.nq = L.nq; g.nk = L.nk; g.nv = L.nv; g.ng = L.ng;
+                g.hd = cfg.head_dim; g.kv_heads = cfg.kv_heads; g.qk_norm = cfg.qk_norm;
+                g.gq = L.gq; g.gk = L.gk; g.rope = m->rope;
+                g.kpool = s->kpool[i]; g.vpool = s->vpool[i];
+                g.page_table = s->page_table; g.pt_stride = s->max_pages;
+                g.qbuf = s->qbuf; g.gbuf = s->gbuf;
+                const int R = cfg.qk_norm ? cfg.head_dim : 16;
+                if ((rc = gemv<GEMV_QKV>(s, c, g, R, rec, "qkv_gemv_norm_rope_kvappend"))) return rc;
+                ++launches;
+                AttnParams a;
+                a.kpool = s->kpool[i]; a.vpool = s->vpool[i];
+                a.page_table = s->page_table; a.pt_stride = s->max_pages;
+                a.qbuf = s->qbuf; a.gbuf = L.ng ? s->gbuf : nullptr; a.abuf = s->abuf;
+                a.part = s->part; a.ticket = s->attn_ticket;
+                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads;
+                if (rec) {
+                    uint64_t kvb = 0, fl = 0;
+                    for (int b = 0; b < B; ++b) {
+                        if (s->h_pos[b] >= s->max_ctx) continue;
+                        kvb += 2ull * cfg.kv_heads * cfg.head_dim * sizeof(KVT) * (s->h_pos[b] + 1);
+                        fl += 4ull * cfg.heads * cfg.head_dim * (s->h_pos[b] + 1);
+                    }
+                    if ((rc = rec->begin("attn_flash_decode_paged", kvb, fl))) return rc;
+                }
+                const int G = cfg.heads / cfg.kv_heads;
+                if (cfg.head_dim == 64) rc = attn_g<64>(s, c, a, G); else rc = attn_g<128>(s, c, a, G);
+                if (rc) return rc;
+                if (rec && (rc = rec->end())) return rc;
+                ++launches;
+            } else {
+                g.y = s->raw;
+                if ((rc = gemv<GEMV_RAW>(s, c, g, 16, rec, "deltanet_proj_gemv_norm"))) return rc;
+                ++launches;
+                const int dk = cfg.dn_key_dim, dv = cfg.dn_value_dim, H = cfg.heads;
+                if (rec && (rc = rec->begin("deltanet_state_update", (uint64_t)B * 2ull * H * dk * dv * 4, (uint64_t)B * 6ull * H * dk * dv))) return rc;
+                dim3 grid((dv + 31) / 32, H, B);
+                if (dk == 64) delta_net_kernel<64><<<grid, 256, 0, s->stream>>>(c, s->raw, s->raw_stride, s->state[i], H, dv, s->abuf, 1e-6f);
+                else delta_net_kernel<128><<<grid, 256, 0, s->stream>>>(c, s->raw, s->raw_stride, s->state[i], H, dv, s->abuf, 1e-6f);
+                CU(cudaGetLastError());
+                if (rec && (rc = rec->end())) return rc;
+                ++launches;
+            }
+            // output projection + residual (in place on the residual stream)
+            std::memset(&g, 0, sizeof g);
+            g.W = L.Wo; g.wscale = L.So; g.N = d; g.K = L.o_in;
+            g.xin = s->abuf; g.y = s->x; g.resid = s->x;
+            if ((rc = gemv<GEMV_RESID>(s, c, g, d <= 1024 ? 8 : 16, rec, "oproj_gemv_residual"))) return rc;
+            ++launches;
+            // FFN gate/up with RMS norm prologue and SwiGLU epilogue
+            std::memset(&g, 0, sizeof g);
+            g.W = L.W1a; g.Wb = L.W1b; g.wscale = L.S1a; g.wscale_b = L.S1b; g.N = F; g.K = d;
+            g.xin = s->x; g.gain = L.g2; g.eps = cfg.rms_eps; g.do_norm = 1; g.y = s->hbuf;
+            if ((rc = gemv<GEMV_SWIGLU>(s, c, g, 8, rec, "ffn_gateup_gemv_norm_swiglu"))) return rc;
+            ++launches;
+            // FFN down + residual (+ the next layer's per-layer embedding)
+            std::memset(&g, 0, sizeof g);
+            g.W = L.W2; g.wscale = L.S2; g.N = d; g.K = F;
+            g.xin = s->hbuf; g.y = s->x; g.resid = s->x;
+            if (p > 0 && i + 1 < cfg.layers) { g.P = m->layers[i + 1].pleP; g.Ptab = m->layers[i + 1].pleT; g.Kp = p; }
+            if ((rc = gemv<GEMV_RESID>(s, c, g, d <= 1024 ? 8 : 16, rec, "ffn_down_gemv_residual_ple"))) return rc;
+            ++launches;
+        }
+        if (kind == CHAIN_PREFILL) {
+            if (rec && (rc = rec->begin("advance_prompt", (uint64_t)B * 12, 0))) return rc;
+            advance_kernel<<<(B + 127) / 128, 128, 0, s->stream>>>(c);
+            CU(cudaGetLastError());
+            if (rec && (rc = rec->end())) return rc;
+            ++launches;
+        } else {
+            GemvParams g;
+            std::memset(&g, 0, sizeof g);
+            g.W = m->E; g.wscale = m->Es; g.N = cfg.vocab; g.K = d;
+            g.xin = s->x; g.gain = m->g_final; g.eps = cfg.rms_eps; g.do_norm = 1; g.y = s->logits;
+            g.part_val = s->part_val; g.part_idx = s->part_idx; g.ticket = s->lm_ticket;
+            g.do_pick = kind == CHAIN_GREEDY ? 1 : 0;
+            if ((rc = gemv<GEMV_LMHEAD>(s, c, g, s->lm_rows, rec, "lmhead_gemv_norm_argmax"))) return rc;
+            ++launches;
+            if (kind == CHAIN_TOPK) {
+                SampleParams sp;
+                sp.logits = s->logits; sp.V = cfg.vocab; sp.top_k = s->cur_topk; sp.temperature = s->cur_temp; sp.seeds = s->seeds;
+                if (rec && (rc = rec->begin("sample_topk_philox", (uint64_t)B * cfg.vocab * 4 * 5, 0))) return rc;
+                sample_topk_kernel<<<B, 256, 0, s->stream>>>(c, sp);
+                CU(cudaGetLastError());
+                if (rec && (rc = rec->end())) return rc;
+                ++launches;
+            }
+        }
+        if (n_launches) *n_launches = launches;
+        return MLB_OK;
+    }
+};
+
+static int chain_run(mlb_session* s, int kind, Recorder* rec, int* n_launches) {
+    const int w = s->m->cfg.weight_dtype, k = s->m->cfg.kv_dtype;
+    if (w == MLB_DT_F32 && k == MLB_DT_F32) return Chain<float, float, float>::run(s, kind, rec, n_launches);
+    if (w == MLB_DT_F32 && k == MLB_DT_BF16) return Chain<float, float, bf16_t>::run(s, kind, rec, n_launches);
+    if (w == MLB_DT_BF16 && k == MLB_DT_F32) return Chain<bf16_t, bf16_t, float>::run(s, kind, rec, n_launches);
+    if (w == MLB_DT_BF16 && k == MLB_DT_BF16) return Chain<bf16_t, bf16_t, bf16_t>::run(s, kind, rec, n_launches);
+    if (w == MLB_DT_FP8_E4M3 && k == MLB_DT_F32) return Chain<fp8_t, bf16_t, float>::run(s, kind, rec, n_launches);
+    return Chain<fp8_t, bf16_t, bf16_t>::run(s, kind, rec, n_launches);
+}
+static int chain_configure(mlb_session* s) {
+    const int w = s->m->cfg.weight_dtype, k = s->m->cfg.kv_dtype;
+    if (w == MLB_DT_F32 && k == MLB_DT_F32) return Chain<float, float, float>::configure();
+    if (w == MLB_DT_F32 && k == MLB_DT_BF16) return Chain<float, float, bf16_t>::configure();
+    if (w == MLB_DT_BF16 && k == MLB_DT_F32) return Chain<bf16_t, bf16_t, float>::configure();
+    if (w == MLB_DT_BF16 && k == MLB_DT_BF16) return Chain<bf16_t, bf16_t, bf16_t>::configure();
+    if (w == MLB_DT_FP8_E4M3 && k == MLB_DT_F32) return Chain<fp8_t, bf16_t, float>::configure();
+    return Chain<fp8_t, bf16_t, bf16_t>::configure();
+}
+
+// Capture the chain once per kind; sampling parameters are baked into the top-k graph.
+static int ensure_graph(mlb_session* s, int kind) {
+    if (kind == CHAIN_TOPK && s->graphs[kind] && (s->g_topk != s->cur_topk || s->g_temp != s->cur_temp)) {
+        cudaGraphExecDestroy(s->graphs[kind]);
+        s->graphs[kind] = nullptr;
+    }
+    if (s->graphs[kind]) return MLB_OK;
+    cudaGraph_t graph = nullptr;
+    CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+    int n = 0;
+    int rc = chain_run(s, kind, nullptr, &n);
+    cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
+    if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (e != cudaSuccess) return fail(MLB_E_CUDA, "cudaStreamEndCapture failed: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&s->graphs[kind], graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return fail(MLB_E_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+    s->launches_per_step[kind] = n;
+    if (kind == CHAIN_TOPK) { s->g_topk = s->cur_topk; s->g_temp = s->cur_temp; }
+    return MLB_OK;
+}
+
+static int sync_page_table(mlb_session* s) {
+    if (!s->table_dirty) return MLB_OK;
+    for (int b = 0; b < s->B; ++b) {
+        const auto& pg = s->alloc.seq_pages[b];
+        for (size_t i = 0; i < pg.size(); ++i) s->h_table[(size_t)b * s->max_pages + i] = pg[i];
+    }
+    CU(cudaMemcpyAsync(s->page_table, s->h_table.data(), s->h_table.size() * 4, cudaMemcpyHostToDevice, s->stream));
+    CU(cudaStreamSynchronize(s->stream));      // h_table may be rewritten by the next call
+    s->table_dirty = false;
+    return MLB_OK;
+}
+
+static int grow_pages(mlb_session* s, int extra_steps) {
+    bool has_attn = false;
+    for (auto* p : s->kpool) if (p) has_attn = true;
+    if (!has_attn) return MLB_OK;
+    for (int b = 0; b < s->B; ++b) {
+        int want = std::min(s->h_pos[b] + extra_steps, s->max_ctx);
+        size_t before = s->alloc.seq_pages[b].size();
+        int rc = kv_ensure(&s->alloc, b, want, kKvBlock);
+        if (s->alloc.seq_pages[b].size() != before) s->table_dirty = true;
+        if (rc) return rc;
+    }
+    return sync_page_table(s);
+}
+
+static int apply_sampling(mlb_session* s, const mlb_sampling* sp, int* kind) {
+    *kind = CHAIN_GREEDY;
+    if (!sp || sp->mode == 0) return MLB_OK;
+    if (sp->mode != 1) return fail(MLB_E_INVALID, "unknown sampling mode %d", sp->mode);
+    if (sp->top_k < 1 || sp->top_k > kSampleCap) return fail(MLB_E_INVALID, "top_k must be in 1..%d", kSampleCap);
+    if (!(sp->temperature > 0.f)) return fail(MLB_E_INVALID, "temperature must be > 0");
+    s->cur_topk = sp->top_k;
+    s->cur_temp = sp->temperature;
+    std::vector<unsigned long long> seeds(s->B);
+    for (int b = 0; b < s->B; ++b) seeds[b] = sp->seeds ? sp->seeds[b] : (unsigned long long)b;
+    CU(cudaMemcpyAsync(s->seeds, seeds.data(), (size_t)s->B * 8, cudaMemcpyHostToDevice, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    *kind = CHAIN_TOPK;
+    return MLB_OK;
+}
+
+}  // namespace mlb
+
+extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_block, int kv_pages, mlb_session** out) {
+    if (!m || !out) return fail(MLB_E_INVALID, "null argument");
+    *out = nullptr;
+    if (batch < 1) return fail(MLB_E_INVALID, "batch must be >= 1");
+    if (kv_block != 0 && kv_block != kKvBlock) return fail(MLB_E_UNSUPPORTED, "kv_block must be %d", kKvBlock);
+    if (max_context <= 0) max_context = m->cfg.max_context;
+    if (max_context > m->cfg.max_context) return fail(MLB_E_INVALID, "max_context %d exceeds the model's %d (RoPE table size)", max_context, m->cfg.max_context);
+    CU(cudaSetDevice(m->device));
+    const mlb_config& c = m->cfg;
+    mlb_session* s = new mlb_session();
+    s->m = m;
+    s->B = batch;
+    s->max_ctx = max_context;
+    s->max_pages = (max_context + kKvBlock - 1) / kKvBlock;
+    s->kv_pages = kv_pages > 0 ? kv_pages : batch * s->max_pages;
+#define SA(expr) do { int r__ = (expr); if (r__) { free_session(s); return r__; } } while (0)
+#define SCU(expr) do { cudaError_t e__ = (expr); if (e__ != cudaSuccess) { free_session(s); return fail(MLB_E_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)); } } while (0)
+    SCU(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+    const size_t B = batch;
+    SA(sess_alloc(s, (void**)&s->pos, B * 4, true));
+    SA(sess_alloc(s, (void**)&s->tok, B * 4, true));
+    SA(sess_alloc(s, (void**)&s->limit_prefill, B * 4, true));
+    SA(sess_alloc(s, (void**)&s->limit_decode, B * 4, true));
+    SA(sess_alloc(s, (void**)&s->prompt, B * max_context * 4, true));
+    SA(sess_alloc(s, (void**)&s->out_ring, B * max_context * 4, true));
+    SA(sess_alloc(s, (void**)&s->out_idx, B * 4, true));
+    SA(sess_alloc(s, (void**)&s->page_table, B * s->max_pages * 4, true));
+    SA(sess_alloc(s, (void**)&s->seeds, B * 8, true));
+    const int nq = c.heads * c.head_dim;
+    const int a_dim = std::max(nq, c.heads * c.dn_value_dim);
+    s->max_q = nq;
+    s->raw_stride = 2 * c.heads * c.dn_key_dim + c.heads * c.dn_value_dim + 2 * c.heads;
+    SA(sess_alloc(s, (void**)&s->x, B * c.dim * 4, true));
+    SA(sess_alloc(s, (void**)&s->qbuf, B * nq * 4, true));
+    SA(sess_alloc(s, (void**)&s->gbuf, B * nq * 4, true));
+    SA(sess_alloc(s, (void**)&s->abuf, B * a_dim * 4, true));
+    SA(sess_alloc(s, (void**)&s->hbuf, B * c.ffn_dim * 4, true));
+    SA(sess_alloc(s, (void**)&s->raw, B * s->raw_stride * 4, true));
+    SA(sess_alloc(s, (void**)&s->logits, B * c.vocab * 4, true));
+    SA(sess_alloc(s, (void**)&s->probe, (size_t)c.vocab * 4, true));
+    // split count of the flash-decode: enough CTAs to cover the GPU at small batch, at least
+    // four pages of work per split at full context
+    int sm_count = 148;
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, m->device);
+    int want = (2 * sm_count + c.kv_heads * batch - 1) / (c.kv_heads * batch);
+    s->splits = std::max(1, std::min(std::min(want, 32), std::max(1, s->max_pages / 4)));
+    SA(sess_alloc(s, (void**)&s->part, B * c.heads * s->splits * (c.head_dim + 2) * 4, true));
+    SA(sess_alloc(s, (void**)&s->attn_ticket, B * c.kv_heads * 4, true));
+    s->lm_rows = 32;
+    s->lm_parts = (c.vocab + s->lm_rows - 1) / s->lm_rows;
+    SA(sess_alloc(s, (void**)&s->part_val, B * s->lm_parts * 4, true));
+    SA(sess_alloc(s, (void**)&s->part_idx, B * s->lm_parts * 4, true));
+    SA(sess_alloc(s, (void**)&s->lm_ticket, (B + 7) / 1 * 4, true));
+    s->kpool.assign(c.layers, nullptr);
+    s->vpool.assign(c.layers, nullptr);
+    s->state.assign(c.layers, nullptr);
+    const size_t kv_elt = elt_size(c.kv_dtype);
+    for (int i = 0; i < c.layers; ++i) {
+        if (c.layer_types[i] == MLB_LAYER_ATTENTION) {
+            size_t bytes = (size_t)s->kv_pages * c.kv_heads * kKvBlock * c.head_dim * kv_elt;
+            SA(sess_alloc(s, &s->kpool[i], bytes, true));
+            SA(sess_alloc(s, &s->vpool[i], bytes, true));
+        } else {
+            SA(sess_alloc(s, (void**)&s->state[i], B * c.heads * c.dn_value_dim * c.dn_key_dim * 4, true));
+        }
+    }
+    s->flush_n = (192ull << 20) / 16;
+    SA(sess_alloc(s, (void**)&s->flush_buf, s->flush_n * 16, false));
+    SCU(cudaMallocHost((void**)&s->pinned_tok, B * 4));
+    s->alloc.num_pages = s->kv_pages;
+    s->alloc.max_pages_per_seq = s->max_pages;
+    s->alloc.seq_pages.assign(batch, {});
+    for (int p = s->kv_pages - 1; p >= 0; --p) s->alloc.free_list.push_back(p);
+    s->h_pos.assign(batch, 0);
+    s->h_table.assign(B * s->max_pages, 0);
+    std::vector<int> lim(batch, max_context);
+    SCU(cudaMemcpy(s->limit_decode, lim.data(), B * 4, cudaMemcpyHostToDevice));
+    SA(chain_configure(s));
+#undef SA
+#undef SCU
+    *out = s;
+    return MLB_OK;
+}
+
+extern "C" int mlb_session_reset(mlb_session* s) {
+    if (!s) return fail(MLB_E_INVALID, "null session");
+    CU(cudaSetDevice(s->m->device));
+    CU(cudaStreamSynchronize(s->stream));
+    const size_t B = s->B;
+    CU(cudaMemsetAsync(s->pos, 0, B * 4, s->stream));
+    CU(cudaMemsetAsync(s->tok, 0, B * 4, s->stream));
+    CU(cudaMemsetAsync(s->limit_prefill, 0, B * 4, s->stream));
+    CU(cudaMemsetAsync(s->out_idx, 0, B * 4, s->stream));
+    const mlb_config& c = s->m->cfg;
+    for (int i = 0; i < c.layers; ++i)
+        if (s->state[i]) CU(cudaMemsetAsync(s->state[i], 0, B * c.heads * c.dn_value_dim * c.dn_key_dim * 4, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    for (int b = 0; b < s->B; ++b) {
+        for (int pg : s->alloc.seq_pages[b]) s->alloc.free_list.push_back(pg);
+        s->alloc.seq_pages[b].clear();
+        s->h_pos[b] = 0;
+    }
+    s->table_dirty = true;
+    s->have_logits = false;
+    return MLB_OK;
+}
+
+extern "C" void mlb_session_free(mlb_session* s) { free_session(s); }
+
+extern "C" int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride) {
+    if (!s || !tokens || !lens) return fail(MLB_E_INVALID, "null argument");
+    CU(cudaSetDevice(s->m->device));
+    const int B = s->B, V = s->m->cfg.vocab;
+    int max_len = 0;
+    for (int b = 0; b < B; ++b) {
+        if (lens[b] < 1) return fail(MLB_E_INVALID, "sequence %d: prompt length must be >= 1 (got %d)", b, lens[b]);
+        if (lens[b] > s->max_ctx) return fail(MLB_E_CONTEXT_FULL, "sequence %d: prompt of %d tokens exceeds max_context %d", b, lens[b], s->max_ctx);
+        if (lens[b] > stride) return fail(MLB_E_INVALID, "sequence %d: length %d exceeds stride %d", b, lens[b], stride);
+        for (int i = 0; i < lens[b]; ++i) {
+            int t = tokens[(size_t)b * stride + i];
+            if (t < 0 || t >= V) return fail(MLB_E_INVALID, "sequence %d: token %d at position %d is outside the vocabulary (%d)", b, t, i, V);
+        }
+        max_len = std::max(max_len, lens[b]);
+    }
+    int rc = mlb_session_reset(s);
+    if (rc) return rc;
+    std::vector<int> hp((size_t)B * s->max_ctx, 0), first(B), lim(B);
+    for (int b = 0; b < B; ++b) {
+        std::memcpy(&hp[(size_t)b * s->max_ctx], &tokens[(size_t)b * stride], (size_t)lens[b] * 4);
+        first[b] = tokens[(size_t)b * stride];
+        lim[b] = lens[b] - 1;
+    }
+    // pages for the whole prompt before any launch
+    for (int b = 0; b < B; ++b) s->h_pos[b] = 0;
+    bool has_attn = false;
+    for (auto* p : s->kpool) if (p) has_attn = true;
+    if (has_attn) {
+        for (int b = 0; b < B; ++b) {
+            if ((rc = kv_ensure(&s->alloc, b, lens[b], kKvBlock))) return rc;
+        }
+        s->table_dirty = true;
+        if ((rc = sync_page_table(s))) return rc;
+    }
+    CU(cudaMemcpyAsync(s->prompt, hp.data(), hp.size() * 4, cudaMemcpyHostToDevice, s->stream));
+    CU(cudaMemcpyAsync(s->tok, first.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
+    CU(cudaMemcpyAsync(s->limit_prefill, lim.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    if (max_len > 1) {
+        if ((rc = ensure_graph(s, CHAIN_PREFILL))) return rc;
+        for (int t = 0; t < max_len - 1; ++t) CU(cudaGraphLaunch(s->graphs[CHAIN_PREFILL], s->stream));
+    }
+    CU(cudaStreamSynchronize(s->stream));
+    for (int b = 0; b < B; ++b) s->h_pos[b] = lens[b] - 1;
+    return MLB_OK;
+}
+
+namespace mlb {
+// Shared body of the decode entry points. step_ms != null times each step.
+static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int32_t* in_tokens, int32_t* out_tokens,
+                       float* step_ms, int flush_l2) {
+    if (!s || !out_tokens) return fail(MLB_E_INVALID, "null argument");
+    if (n < 1) return fail(MLB_E_INVALID, "n must be >= 1");
+    CU(cudaSetDevice(s->m->device));
+    const int B = s->B;
+    bool any = false;
+    for (int b = 0; b < B; ++b) any = any || s->h_pos[b] < s->max_ctx;
+    if (!any) return fail(MLB_E_CONTEXT_FULL, "every sequence is at max_context %d", s->max_ctx);
+    if (n > s->max_ctx) n = std::min(n, s->max_ctx);
+    int kind, rc;
+    if ((rc = apply_sampling(s, sp, &kind))) return rc;
+    if ((rc = grow_pages(s, n))) return rc;
+    if ((rc = ensure_graph(s, kind))) return rc;
+    if (in_tokens) {
+        const int V = s->m->cfg.vocab;
+        for (int b = 0; b < B; ++b) {
+            if (in_tokens[b] < 0 || in_tokens[b] >= V) return fail(MLB_E_INVALID, "sequence %d: token %d is outside the vocabulary", b, in_tokens[b]);
+            s->pinned_tok[b] = in_tokens[b];
+        }
+        CU(cudaMemcpyAsync(s->tok, s->pinned_tok, (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
+    }
+    CU(cudaMemsetAsync(s->out_idx, 0, (size_t)B * 4, s->stream));
+    std::vector<cudaEvent_t> ev;
+    if (step_ms) {
+        ev.resize(2 * (size_t)n);
+        for (auto& e : ev) CU(cudaEventCreate(&e));
+    }
+    for (int i = 0; i < n; ++i) {
+        if (step_ms) {
+            if (flush_l2) {
+                l2_flush_kernel<<<1184, 256, 0, s->stream>>>(s->flush_buf, s->flush_n, (float)i);
+                CU(cudaGetLastError());
+            }
+            CU(cudaEventRecord(ev[2 * i], s->stream));
+        }
+        CU(cudaGraphLaunch(s->graphs[kind], s->stream));
+        if (step_ms) CU(cudaEventRecord(ev[2 * i + 1], s->stream));
+    }
+    // result: ring [B][max_ctx] -> out [B][n]
+    std::vector<int> ring((size_t)B * s->max_ctx);
+    if (n == 1) {
+        // one id per sequence: gather through the pinned buffer
+        CU(cudaMemcpy2DAsync(s->pinned_tok, 4, s->out_ring, (size_t)s->max_ctx * 4, 4, B, cudaMemcpyDeviceToHost, s->stream));
+        CU(cudaStreamSynchronize(s->stream));
+        for (int b = 0; b < B; ++b) out_tokens[b] = s->h_pos[b] < s->max_ctx ? s->pinned_tok[b] : -1;
+    } else {
+        CU(cudaMemcpy2DAsync(ring.data(), (size_t)n * 4, s->out_ring, (size_t)s->max_ctx * 4, (size_t)n * 4, B, cudaMemcpyDeviceToHost, s->stream));
+        CU(cudaStreamSynchronize(s->stream));
+        for (int b = 0; b < B; ++b) {
+            int room = std::max(0, s->max_ctx - s->h_pos[b]);
+            for (int i = 0; i < n; ++i) out_tokens[(size_t)b * n + i] = i < room ? ring[(size_t)b * n + i] : -1;
+        }
+    }
+    if (step_ms) {
+        for (int i = 0; i < n; ++i) CU(cudaEventElapsedTime(&step_ms[i], ev[2 * i], ev[2 * i + 1]));
+        for (auto& e : ev) cudaEventDestroy(e);
+    }
+    for (int b = 0; b < B; ++b) s->h_pos[b] = std::min(s->h_pos[b] + n, s->max_ctx);
+    s->have_logits = true;
+    return MLB_OK;
+}
+}  // namespace mlb
+
+extern "C" int mlb_decode_step(mlb_session* s, const mlb_sampling* sp, const int32_t* in_tokens, int32_t* out_tokens) {
+    return decode_impl(s, sp, 1, in_tokens, out_tokens, nullptr, 0);
+}
+extern "C" int mlb_decode_n(mlb_session* s, const mlb_sampling* sp, int n, int32_t* out_tokens) {
+    return decode_impl(s, sp, n, nullptr, out_tokens, nullptr, 0);
+}
+extern "C" int mlb_decode_timed(mlb_session* s, const mlb_sampling* sp, int n, int flush_l2, float* step_ms, int32_t* out_tokens) {
+    if (!step_ms) return fail(MLB_E_INVALID, "null step_ms");
+    return decode_impl(s, sp, n, nullptr, out_tokens, step_ms, flush_l2);
+}
+
+extern "C" int mlb_profile_decode(mlb_session* s, const mlb_sampling* sp, int n, int flush_l2, mlb_kernel_stat* stats,
+                                  int max_stats, int* n_stats) {
+    if (!s || !stats || !n_stats) return fail(MLB_E_INVALID, "null argument");
+    CU(cudaSetDevice(s->m->device));
+    int kind, rc;
+    if ((rc = apply_sampling(s, sp, &kind))) return rc;
+    if ((rc = grow_pages(s, n))) return rc;
+    CU(cudaMemsetAsync(s->out_idx, 0, (size_t)s->B * 4, s->stream));
+    Recorder rec;
+    rec.st = s->stream;
+    for (int i = 0; i < n; ++i) {
+        bool any = false;
+        for (int b = 0; b < s->B; ++b) any = any || s->h_pos[b] < s->max_ctx;
+        if (!any) break;
+        if (flush_l2) {
+            l2_flush_kernel<<<1184, 256, 0, s->stream>>>(s->flush_buf, s->flush_n, (float)i);
+            CU(cudaGetLastError());
+        }
+        if ((rc = chain_run(s, kind, &rec, nullptr))) return rc;
+        for (int b = 0; b < s->B; ++b) s->h_pos[b] = std::min(s->h_pos[b] + 1, s->max_ctx);
+    }
+    CU(cudaStreamSynchronize(s->stream));
+    s->have_logits = true;
+    int count = 0;
+    for (auto& r : rec.recs) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, r.e0, r.e1);
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+        int j = 0;
+        for (; j < count; ++j) if (std::strcmp(stats[j].name, r.name) == 0) break;
+        if (j == count) {
+            if (count >= max_stats) continue;
+            std::memset(&stats[j], 0, sizeof stats[j]);
+            std::strncpy(stats[j].name, r.name, sizeof(stats[j].name) - 1);
+            ++count;
+        }
+        stats[j].launches += 1;
+        stats[j].total_ms += ms;
+        stats[j].bytes += r.bytes;
+        stats[j].flops += r.flops;
+    }
+    *n_stats = count;
+    return MLB_OK;
+}
+
+extern "C" int mlb_get_logits(mlb_session* s, float* out) {
+    if (!s || !out) return fail(MLB_E_INVALID, "null argument");
+    if (!s->have_logits) return fail(MLB_E_INVALID, "no decode step has run since the last prefill/reset");
+    CU(cudaSetDevice(s->m->device));
+    CU(cudaMemcpyAsync(out, s->logits, (size_t)s->B * s->m->cfg.vocab * 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    return MLB_OK;
+}
+
+extern "C" int mlb_get_probs_col(mlb_session* s, int seq, float* out) {
+    if (!s || !out) return fail(MLB_E_INVALID, "null argument");
+    if (seq < 0 || seq >= s->B) return fail(MLB_E_INVALID, "sequence index out of range");
+    if (!s->have_logits) return fail(MLB_E_INVALID, "no decode step has run since the last prefill/reset");
+    CU(cudaSetDevice(s->m->device));
+    const int V = s->m->cfg.vocab;
+    softmax_probe_kernel<<<1, 256, 0, s->stream>>>(s->logits + (size_t)seq * V, V, s->probe);
+    CU(cudaGetLastError());
+    CU(cudaMemcpyAsync(out, s->probe, (size_t)V * 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    return MLB_OK;
+}
+
+extern "C" int mlb_session_positions(mlb_session* s, int32_t* out) {
+    if (!s || !out) return fail(MLB_E_INVALID, "null argument");
+    CU(cudaSetDevice(s->m->device));
+    CU(cudaMemcpyAsync(out, s->pos, (size_t)s->B * 4, cudaMemcpyDeviceToHost, s->stream));
+    CU(cudaStreamSynchronize(s->stream));
+    return MLB_OK;
+}
+
+extern "C" int mlb_session_step_bytes(mlb_session* s, uint64_t* weights, uint64_t* kv, uint64_t* state, uint64_t* rows) {
+    if (!s) return fail(MLB_E_INVALID, "null session");
+    const mlb_config& c = s->m->cfg;
+    uint64_t kvb = 0, st = 0, rw = 0;
+    const uint64_t kv_elt = elt_size(c.kv_dtype), w_elt = elt_size(c.weight_dtype), p_elt = elt_size(ple_dtype(c.weight_dtype));
+    for (int b = 0; b < s->B; ++b) {
+        if (s->h_pos[b] >= s->max_ctx) continue;
+        for (int i = 0; i < c.layers; ++i) {
+            if (c.layer_types[i] == MLB_LAYER_ATTENTION) kvb += 2ull * c.kv_heads * c.head_dim * kv_elt * (s->h_pos[b] + 1);
+            else st += 2ull * c.heads * c.dn_key_dim * c.dn_value_dim * 4;
+        }
+        rw += (uint64_t)c.dim * w_elt + (uint64_t)c.layers * c.ple_dim * p_elt;
+    }
+    if (weights) *weights = s->m->weight_bytes;   // the tied table is streamed once (LM head)
+    if (kv) *kv = kvb;
+    if (state) *state = st;
+    if (rows) *rows = rw;
+    return MLB_OK;
+}
+
+extern "C" int mlb_session_launches_per_step(mlb_session* s) {
+    if (!s) return fail(MLB_E_INVALID, "null session");
+    int rc = ensure_graph(s, CHAIN_GREEDY);
+    if (rc) return rc;
+    return s->launches_per_step[CHAIN_GREEDY];
+}
+
+// ---- host-only allocator entry points --------------------------------------------------
+extern "C" int mlb_kv_alloc_new(int num_pages, int batch, int max_pages_per_seq, mlb_kv_alloc** out) {
+    if (!out || num_pages < 0 || batch < 1 || max_pages_per_seq < 1) return fail(MLB_E_INVALID, "kv allocator: bad argument");
+    mlb_kv_alloc* a = new mlb_kv_alloc();
+    a->num_pages = num_pages;
+    a->max_pages_per_seq = max_pages_per_seq;
+    a->seq_pages.assign(batch, {});
+    for (int p = num_pages - 1; p >= 0; --p) a->free_list.push_back(p);
+    *out = a;
+    return MLB_OK;
+}
+extern "C" int mlb_kv_alloc_ensure(mlb_kv_alloc* a, int seq, int n_positions, int block) { return kv_ensure(a, seq, n_positions, block); }
+extern "C" int mlb_kv_alloc_table(const mlb_kv_alloc* a, int seq, int32_t* out, int max_entries) {
+    if (!a || !out || seq < 0 || seq >= (int)a->seq_pages.size()) return fail(MLB_E_INVALID, "kv allocator: bad argument");
+    const auto& pg = a->seq_pages[seq];
+    int n = std::min((int)pg.size(), max_entries);
+    for (int i = 0; i < n; ++i) out[i] = pg[i];
+    return (int)pg.size();
+}
+extern "C" int mlb_kv_alloc_free_pages(const mlb_kv_alloc* a) { return a ? (int)a->free_list.size() : fail(MLB_E_INVALID, "null allocator"); }
+extern "C" void mlb_kv_alloc_release(mlb_kv_alloc* a, int seq) {
+    if (!a || seq < 0 || seq >= (int)a->seq_pages.size()) return;
+    for (int pg : a->seq_pages[seq]) a->free_list.push_back(pg);
+    a->seq_pages[seq].clear();
+}
+extern "C" void mlb_kv_alloc_free(mlb_kv_alloc* a) { delete a; }
+
+extern "C" const char* mlb_last_error(void) { return g_err.c_str(); }
+extern "C" const char* mlb_version(void) { return "mini-llm-b200 0.1 (sm_100a)"; }

@@ -1,0 +1,916 @@
+// Decode-step kernels for sm_100a. One decode step of B independent sequences is a short
+// chain of HBM-streaming kernels; every per-sequence quantity that changes between steps
+// (position, pending token, page table) lives in device memory so that the chain can be
+// replayed as a CUDA graph.
+//
+// Reference ops each kernel folds together are cited at the kernel.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mlb {
+
+typedef __nv_bfloat16 bf16_t;
+struct fp8_t { uint8_t v; };   // e4m3 storage
+
+constexpr int kKvBlock = 16;           // positions per KV page
+constexpr float kNegBig = -1.0e30f;    // running-max seed (the reference seeds with -1e20, inference.cu:167)
+
+// ------------------------------------------------------------------------------------
+// Element / 16-byte vector access per storage type
+// ------------------------------------------------------------------------------------
+template <typename T> struct Elem;
+
+template <> struct Elem<float> {
+    static constexpr int EPV = 4;
+    __device__ __forceinline__ static void load_vec(const float* p, float* o) {
+        float4 v = __ldg(reinterpret_cast<const float4*>(p));
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    }
+    __device__ __forceinline__ static void load_vec_cg(const float* p, float* o) {
+        float4 v = __ldcg(reinterpret_cast<const float4*>(p));
+        o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+    }
+    __device__ __forceinline__ static float get(const float* p, size_t i) { return p[i]; }
+    __device__ __forceinline__ static void put(float* p, size_t i, float v) { p[i] = v; }
+};
+
+template <> struct Elem<bf16_t> {
+    static constexpr int EPV = 8;
+    __device__ __forceinline__ static void unpack(const uint4& v, float* o) {
+        o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
+        o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
+        o[4] = __uint_as_float(v.z << 16); o[5] = __uint_as_float(v.z & 0xffff0000u);
+        o[6] = __uint_as_float(v.w << 16); o[7] = __uint_as_float(v.w & 0xffff0000u);
+    }
+    __device__ __forceinline__ static void load_vec(const bf16_t* p, float* o) {
+        unpack(__ldg(reinterpret_cast<const uint4*>(p)), o);
+    }
+    __device__ __forceinline__ static void load_vec_cg(const bf16_t* p, float* o) {
+        unpack(__ldcg(reinterpret_cast<const uint4*>(p)), o);
+    }
+    __device__ __forceinline__ static float get(const bf16_t* p, size_t i) { return __bfloat162float(p[i]); }
+    __device__ __forceinline__ static void put(bf16_t* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+};
+
+template <> struct Elem<fp8_t> {
+    static constexpr int EPV = 16;
+    __device__ __forceinline__ static void unpack_word(uint32_t w, float* o) {
+        __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w & 0xffffu), __NV_E4M3);
+        __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w >> 16), __NV_E4M3);
+        float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
+        float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
+        o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+    }
+    __device__ __forceinline__ static void load_vec(const fp8_t* p, float* o) {
+        uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+        unpack_word(v.x, o); unpack_word(v.y, o + 4); unpack_word(v.z, o + 8); unpack_word(v.w, o + 12);
+    }
+    __device__ __forceinline__ static float get(const fp8_t* p, size_t i) {
+        __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(p[i].v), __NV_E4M3);
+        return __half2float(*reinterpret_cast<__half*>(&h));
+    }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ------------------------------------------------------------------------------------
+// Per-step control block shared by all kernels of a step
+// ------------------------------------------------------------------------------------
+struct StepCtl {
+    int B;
+    int* pos;            // [B] position of the pending token == tokens consumed so far
+    int* tok;            // [B] pending token
+    const int* limit;    // [B] a sequence takes part in the step iff pos < limit
+    // prompt forcing (prefill chain) and output ring (decode chain)
+    const int* prompt;   // [B][prompt_stride] or null
+    int prompt_stride;
+    int* out_ring;       // [B][out_cap]
+    int* out_idx;        // [B]
+    int out_cap;
+};
+
+__device__ __forceinline__ bool seq_active(const StepCtl& c, int b) {
+    return b < c.B && c.pos[b] < c.limit[b];
+}
+
+// End of a step for one sequence: append the picked token (decode) or take the next prompt
+// token (prefill). Stands in for inference_orchestrator.cu:149-154.
+__device__ __forceinline__ void advance_seq(const StepCtl& c, int b, int sampled) {
+    int p = c.pos[b];
+    if (c.prompt != nullptr) {
+        c.tok[b] = c.prompt[(size_t)b * c.prompt_stride + p + 1];
+    } else {
+        int oi = c.out_idx[b];
+        if (oi < c.out_cap) c.out_ring[(size_t)b * c.out_cap + oi] = sampled;
+        c.out_idx[b] = oi + 1;
+        c.tok[b] = sampled;
+    }
+    c.pos[b] = p + 1;
+}
+
+// Prefill chain has no LM head: a one-thread-per-sequence advance.
+__global__ void advance_kernel(StepCtl c) {
+    int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < c.B && seq_active(c, b)) advance_seq(c, b, -1);
+}
+
+// ------------------------------------------------------------------------------------
+// Token-embedding + first-layer PLE gather.   x[b] = E[tok] (+ P0 . T0[tok])
+// Reference: setInputSeqEmbeddings, inference.cu:9-22 (gathers all L columns each step;
+// here one row per sequence). PLE has no counterpart in the reference.
+// ------------------------------------------------------------------------------------
+template <typename T, typename T2>
+__global__ void embed_kernel(StepCtl c, const T* __restrict__ E, const float* __restrict__ escale, int d,
+                             const T2* __restrict__ pleT, const T2* __restrict__ pleP, int p,
+                             float* __restrict__ x) {
+    int b = blockIdx.x;
+    if (!seq_active(c, b)) return;
+    int t = c.tok[b];
+    extern __shared__ float trow[];
+    if (p > 0) {
+        for (int j = threadIdx.x; j < p; j += blockDim.x) trow[j] = Elem<T2>::get(pleT, (size_t)t * p + j);
+        __syncthreads();
+    }
+    float sc = escale ? escale[t] : 1.0f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = Elem<T>::get(E, (size_t)t * d + i) * sc;
+        if (p > 0) {
+            float a = 0.f;
+            for (int j = 0; j < p; ++j) a += Elem<T2>::get(pleP, (size_t)i * p + j) * trow[j];
+            v += a;
+        }
+        x[(size_t)b * d + i] = v;
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Batched GEMV  y[b][row] = sum_k W[row][k] * xin[b][k]  with fused prologue / epilogue.
+//
+// A CTA owns R consecutive output rows and a tile of BT sequences. The (optionally
+// RMS-normalised) activations of the tile are staged once in shared memory; each warp
+// streams RW weight rows at a time with 16-byte loads, every lane striding over K, and
+// warp-shuffle-reduces the partial dot products. Results land in shared memory so that the
+// epilogue can work on whole heads / pairs.
+// ------------------------------------------------------------------------------------
+enum GemvMode : int {
+    GEMV_RAW = 0,      // y = acc
+    GEMV_RESID = 1,    // y = acc + resid   (O projection / FFN down; optional PLE segment)
+    GEMV_SWIGLU = 2,   // y = silu(Wa x) * (Wb x)
+    GEMV_QKV = 3,      // per-head RMS norm, RoPE, KV-cache append, sigmoid gate
+    GEMV_LMHEAD = 4    // logits + argmax partials + last-CTA pick
+};
+
+struct GemvParams {
+    const void* W;         // [N][K]
+    const void* Wb;        // SWIGLU: the up matrix
+    const float* wscale;   // fp8: per-row scale (null otherwise)
+    const float* wscale_b;
+    int N, K, R;
+    const float* xin;      // [B][K]
+    const float* gain;     // [K] when do_norm
+    float eps;
+    int do_norm;
+    // second K segment: per-layer embedding of the NEXT layer folded into the down projection
+    const void* P;         // [N][Kp] (type T2)
+    const void* Ptab;      // [vocab][Kp] (type T2)
+    int Kp;
+    float* y;              // [B][N]
+    const float* resid;    // [B][N]
+    // QKV epilogue
+    int nq, nk, nv, ng;    // rows of the q | k | v | gate segments
+    int hd, kv_heads, qk_norm;
+    const float* gq; const float* gk;
+    const float* rope;     // [max_context][hd] interleaved (cos, sin)
+    void* kpool; void* vpool;          // this layer's pages: [page][kv_heads][16][hd]
+    const int* page_table; int pt_stride;
+    float* qbuf; float* gbuf;          // [B][nq]
+    // LM head epilogue
+    float* part_val; int* part_idx;    // [B][gridDim.x]
+    int* ticket;                       // [gridDim.y]
+    int do_pick;                       // greedy pick + advance in the last CTA
+};
+
+template <typename T, int BT, int RW>
+__device__ __forceinline__ void warp_rows_dot(const T* __restrict__ W, int N, int K, int row0,
+                                              const float* __restrict__ xs, int xs_stride, int lane,
+                                              float (&acc)[RW][BT]) {
+    constexpr int EPV = Elem<T>::EPV;
+    const int nvec = K / EPV;
+    const T* wrow[RW];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+        int row = row0 + r;
+        if (row > N - 1) row = N - 1;     // tail rows are computed on a duplicate and not stored
+        wrow[r] = W + (size_t)row * K;
+    }
+#pragma unroll 2
+    for (int v = lane; v < nvec; v += 32) {
+        float w[RW][EPV];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) Elem<T>::load_vec(wrow[r] + (size_t)v * EPV, w[r]);
+#pragma unroll
+        for (int b = 0; b < BT; ++b) {
+            const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)b * xs_stride + (size_t)v * EPV);
+            float xv[EPV];
+#pragma unroll
+            for (int q = 0; q < EPV / 4; ++q) {
+                float4 t = xp[q];
+                xv[4 * q] = t.x; xv[4 * q + 1] = t.y; xv[4 * q + 2] = t.z; xv[4 * q + 3] = t.w;
+            }
+#pragma unroll
+            for (int r = 0; r < RW; ++r)
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) acc[r][b] = fmaf(w[r][e], xv[e], acc[r][b]);
+        }
+    }
+}
+
+template <typename T, typename T2, typename KVT, int BT, int MODE>
+__global__ void __launch_bounds__(256) gemv_kernel(StepCtl c, GemvParams p) {
+    constexpr int RW = (MODE == GEMV_SWIGLU) ? 2 : 4;
+    extern __shared__ __align__(16) float smem[];
+    const int K = p.K, Kp = p.Kp, R = p.R;
+    float* xs = smem;                                  // [BT][K]
+    float* xs2 = xs + (size_t)BT * K;                  // [BT][Kp]
+    float* outs = xs2 + (size_t)BT * Kp;               // [BT][R]
+    float* rs = outs + (size_t)BT * R;                 // [BT]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    const int b0 = blockIdx.y * BT;
+    const int row0 = blockIdx.x * R;
+
+    // ---- prologue: stage (and RMS-normalise) the activations of the tile -------------
+    // Reference: getRMSColSums + applyRMSNorm, inference.cu:24-50, :83-95 -
+    // r = sqrt(mean(x^2) + eps); x / r, then times the gain.
+    for (int b = warp; b < BT; b += nw) {
+        int bg = min(b0 + b, c.B - 1);
+        const float* xr = p.xin + (size_t)bg * K;
+        float ss = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            float v = xr[k];
+            xs[(size_t)b * K + k] = v;
+            ss = fmaf(v, v, ss);
+        }
+        if (p.do_norm) {
+            ss = warp_sum(ss);
+            float r = sqrtf(ss / (float)K + p.eps);
+            for (int k = lane; k < K; k += 32) xs[(size_t)b * K + k] = (xs[(size_t)b * K + k] / r) * p.gain[k];
+        }
+        if (Kp > 0) {
+            int t = c.tok[bg];
+            const T2* trow = reinterpret_cast<const T2*>(p.Ptab) + (size_t)t * Kp;
+            for (int k = lane; k < Kp; k += 32) xs2[(size_t)b * Kp + k] = Elem<T2>::get(trow, k);
+        }
+    }
+    __syncthreads();
+
+    // ---- main loop: RW rows per warp pass ---------------------------------------------
+    const T* W = reinterpret_cast<const T*>(p.W);
+    for (int rb = warp * RW; rb < R; rb += nw * RW) {
+        float acc[RW][BT];
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[r][b] = 0.f;
+        warp_rows_dot<T, BT, RW>(W, p.N, K, row0 + rb, xs, K, lane, acc);
+        if (MODE == GEMV_SWIGLU) {
+            float accb[RW][BT];
+#pragma unroll
+            for (int r = 0; r < RW; ++r)
+#pragma unroll
+                for (int b = 0; b < BT; ++b) accb[r][b] = 0.f;
+            warp_rows_dot<T, BT, RW>(reinterpret_cast<const T*>(p.Wb), p.N, K, row0 + rb, xs, K, lane, accb);
+#pragma unroll
+            for (int r = 0; r < RW; ++r) {
+                int row = min(row0 + rb + r, p.N - 1);
+                float sa = p.wscale ? p.wscale[row] : 1.f, sb = p.wscale_b ? p.wscale_b[row] : 1.f;
+#pragma unroll
+                for (int b = 0; b < BT; ++b) {
+                    float g = warp_sum(acc[r][b]) * sa;
+                    float u = warp_sum(accb[r][b]) * sb;
+                    // applySiluToFFN + hadamardMultiplyFFN, inference.cu:262-281
+                    if (lane == 0 && rb + r < R) outs[(size_t)b * R + rb + r] = (g / (1.0f + expf(-g))) * u;
+                }
+            }
+        } else {
+            if (Kp > 0) {
+                float acc2[RW][BT];
+#pragma unroll
+                for (int r = 0; r < RW; ++r)
+#pragma unroll
+                    for (int b = 0; b < BT; ++b) acc2[r][b] = 0.f;
+                warp_rows_dot<T2, BT, RW>(reinterpret_cast<const T2*>(p.P), p.N, Kp, row0 + rb, xs2, Kp, lane, acc2);
+#pragma unroll
+                for (int r = 0; r < RW; ++r) {
+                    int row = min(row0 + rb + r, p.N - 1);
+                    float sa = p.wscale ? p.wscale[row] : 1.f;
+#pragma unroll
+                    for (int b = 0; b < BT; ++b) acc[r][b] = acc[r][b] * sa + acc2[r][b];
+                }
+            } else if (p.wscale) {
+#pragma unroll
+                for (int r = 0; r < RW; ++r) {
+                    float sa = p.wscale[min(row0 + rb + r, p.N - 1)];
+#pragma unroll
+                    for (int b = 0; b < BT; ++b) acc[r][b] *= sa;
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RW; ++r)
+#pragma unroll
+                for (int b = 0; b < BT; ++b) {
+                    float v = warp_sum(acc[r][b]);
+                    if (lane == 0 && rb + r < R) outs[(size_t)b * R + rb + r] = v;
+                }
+        }
+    }
+    __syncthreads();
+
+    // ---- epilogues -----------------------------------------------------------------------
+    if (MODE == GEMV_RAW || MODE == GEMV_SWIGLU || MODE == GEMV_RESID) {
+        for (int i = tid; i < BT * R; i += blockDim.x) {
+            int b = i / R, r = i - b * R;
+            int bg = b0 + b, row = row0 + r;
+            if (row < p.N && seq_active(c, bg)) {
+                float v = outs[(size_t)b * R + r];
+                // addResidualToOutputProj / addResidualToFFN, inference.cu:252-260, :283-291
+                if (MODE == GEMV_RESID) v += p.resid[(size_t)bg * p.N + row];
+                p.y[(size_t)bg * p.N + row] = v;
+            }
+        }
+    } else if (MODE == GEMV_QKV) {
+        // Segment of this CTA (R divides every segment and the head size).
+        const int seg_q = p.nq, seg_k = p.nq + p.nk, seg_v = seg_k + p.nv;
+        const int hd = p.hd;
+        int seg = row0 < seg_q ? 0 : (row0 < seg_k ? 1 : (row0 < seg_v ? 2 : 3));
+        if (p.qk_norm && seg < 2) {
+            // getRMSColSumsAcrossHeads + applyRMSNormAcrossHeads, inference.cu:52-81, :97-111
+            // (R == hd here: the CTA holds one whole head)
+            for (int b = warp; b < BT; b += nw) {
+                float ss = 0.f;
+                for (int r = lane; r < R; r += 32) { float v = outs[(size_t)b * R + r]; ss = fmaf(v, v, ss); }
+                ss = warp_sum(ss);
+                if (lane == 0) rs[b] = sqrtf(ss / (float)hd + p.eps);
+            }
+            __syncthreads();
+        }
+        KVT* kpool = reinterpret_cast<KVT*>(p.kpool);
+        KVT* vpool = reinterpret_cast<KVT*>(p.vpool);
+        for (int i = tid; i < BT * (R / 2); i += blockDim.x) {
+            int b = i / (R / 2), pr = i - b * (R / 2);
+            int bg = b0 + b;
+            if (!seq_active(c, bg)) continue;
+            int r = 2 * pr, row = row0 + r;
+            float a = outs[(size_t)b * R + r], cc = outs[(size_t)b * R + r + 1];
+            int pos = c.pos[bg];
+            if (seg < 2) {
+                int srow = (seg == 0) ? row : row - seg_q;          // row inside q or k
+                if (p.qk_norm) {
+                    const float* g = (seg == 0) ? p.gq : p.gk;
+                    a = (a / rs[b]) * g[srow];
+                    cc = (cc / rs[b]) * g[srow + 1];
+                }
+                // applyRoPE, inference.cu:113-134: adjacent pair, table row = position
+                int e = srow % hd;
+                float cs = p.rope[(size_t)pos * hd + e], sn = p.rope[(size_t)pos * hd + e + 1];
+                float ra = cs * a - sn * cc, rc = sn * a + cs * cc;
+                if (seg == 0) {
+                    p.qbuf[(size_t)bg * p.nq + srow] = ra;
+                    p.qbuf[(size_t)bg * p.nq + srow + 1] = rc;
+                } else {
+                    int kvh = srow / hd;
+                    int page = p.page_table[(size_t)bg * p.pt_stride + pos / kKvBlock];
+                    size_t off = (((size_t)page * p.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * hd + e;
+                    Elem<KVT>::put(kpool, off, ra);
+                    Elem<KVT>::put(kpool, off + 1, rc);
+                }
+            } else if (seg == 2) {
+                int srow = row - seg_k;
+                int kvh = srow / hd, e = srow % hd;
+                int page = p.page_table[(size_t)bg * p.pt_stride + pos / kKvBlock];
+                size_t off = (((size_t)page * p.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * hd + e;
+                Elem<KVT>::put(vpool, off, a);
+                Elem<KVT>::put(vpool, off + 1, cc);
+            } else {
+                // sigmoid of the gate projection, inference.cu:248
+                int srow = row - seg_v;
+                p.gbuf[(size_t)bg * p.ng + srow] = 1.0f / (1.0f + expf(-a));
+                p.gbuf[(size_t)bg * p.ng + srow + 1] = 1.0f / (1.0f + expf(-cc));
+            }
+        }
+    } else if (MODE == GEMV_LMHEAD) {
+        // Logits (vocabScores_DEVICE, inference.cu:720-743) and the greedy pick that the
+        // reference does on the host with qsort (inference_orchestrator.cu:77-84, :112).
+        for (int i = tid; i < BT * R; i += blockDim.x) {
+            int b = i / R, r = i - b * R;
+            int bg = b0 + b, row = row0 + r;
+            if (row < p.N && seq_active(c, bg)) p.y[(size_t)bg * p.N + row] = outs[(size_t)b * R + r];
+        }
+        const int nparts = gridDim.x;
+        for (int b = warp; b < BT; b += nw) {
+            int bg = b0 + b;
+            float bv = -INFINITY; int bi = 0x7fffffff;
+            for (int r = lane; r < R; r += 32) {
+                int row = row0 + r;
+                if (row < p.N) {
+                    float v = outs[(size_t)b * R + r];
+                    if (v > bv || (v == bv && row < bi)) { bv = v; bi = row; }
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (lane == 0 && bg < c.B) {
+                p.part_val[(size_t)bg * nparts + blockIdx.x] = bv;
+                p.part_idx[(size_t)bg * nparts + blockIdx.x] = bi;
+            }
+        }
+        // Last CTA of this batch tile reduces the partials (ticket pattern; no spinning).
+        __shared__ int is_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            int t = atomicAdd(&p.ticket[blockIdx.y], 1);
+            is_last = (t == nparts - 1);
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            for (int b = warp; b < BT; b += nw) {
+                int bg = b0 + b;
+                if (!seq_active(c, bg)) continue;          // warp-uniform
+                float bv = -INFINITY; int bi = 0x7fffffff;
+                for (int q = lane; q < nparts; q += 32) {
+                    float v = __ldcg(&p.part_val[(size_t)bg * nparts + q]);
+                    int ix = __ldcg(&p.part_idx[(size_t)bg * nparts + q]);
+                    if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+                }
+                if (lane == 0 && p.do_pick) advance_seq(c, bg, bi);
+            }
+            if (tid == 0) p.ticket[blockIdx.y] = 0;        // ready for the next step
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Split-K flash-decode over the paged KV cache, with the split combine and the query
+// gating folded into the last-arriving CTA of each (sequence, kv head).
+//
+// Reference ops replaced: K^T Q GEMM, getHeadDimScaledMaskedAttn, the max / sum / apply
+// softmax kernels, V P GEMM, applyGatingToValueScaledAttnPostSoftmax
+// (inference.cu:510-579, kernels :136-250). Scores are divided by sqrtf(head_dim) as there.
+// grid = (splits, kv_heads, B), block = 128.
+// ------------------------------------------------------------------------------------
+struct AttnParams {
+    const void* kpool; const void* vpool;     // [page][kv_heads][16][hd]
+    const int* page_table; int pt_stride;
+    const float* qbuf;      // [B][heads*hd]
+    const float* gbuf;      // [B][heads*hd] sigmoid gates or null
+    float* abuf;            // [B][heads*hd]
+    float* part;            // [B][heads][splits][hd+2]
+    int* ticket;            // [B*kv_heads]
+    int heads, kv_heads;
+};
+
+template <typename KVT, int HD, int G>
+__global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams p) {
+    constexpr int EPL = 16 / sizeof(KVT);          // elements per lane per row
+    constexpr int LPR = HD / EPL;                  // lanes per row
+    constexpr int PPI = 32 / LPR;                  // positions per warp iteration
+    constexpr int NW = 4;
+    static_assert(LPR <= 32 && PPI >= 1, "head_dim too large for one warp row");
+    const int b = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x, S = gridDim.x;
+    if (!seq_active(c, b)) return;                 // uniform for all CTAs of this sequence
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lr = lane % LPR, grp = lane / LPR;
+    const int pos = c.pos[b];
+    const int ctx = pos + 1;
+    const int npages = (ctx + kKvBlock - 1) / kKvBlock;
+    const int pps = (npages + S - 1) / S;
+    const int pg_begin = split * pps, pg_end = min(npages, pg_begin + pps);
+
+    __shared__ float sq[G][HD];
+    __shared__ float sred[NW][G][HD + 2];
+    const int h0 = kvh * G;
+    for (int i = tid; i < G * HD; i += blockDim.x)
+        sq[i / HD][i % HD] = p.qbuf[((size_t)b * p.heads + h0) * HD + i];
+    __syncthreads();
+
+    float q[G][EPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) q[g][e] = sq[g][lr * EPL + e];
+
+    float m[G], l[G], acc[G][EPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = kNegBig; l[g] = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
+    }
+    const float inv_div = sqrtf((float)HD);
+    const KVT* kpool = reinterpret_cast<const KVT*>(p.kpool);
+    const KVT* vpool = reinterpret_cast<const KVT*>(p.vpool);
+
+    for (int pg = pg_begin + warp; pg < pg_end; pg += NW) {
+        const int page = p.page_table[(size_t)b * p.pt_stride + pg];
+        const int cnt = min(kKvBlock, ctx - pg * kKvBlock);
+        const size_t base = ((size_t)page * p.kv_heads + kvh) * kKvBlock * HD;
+#pragma unroll
+        for (int j0 = 0; j0 < kKvBlock; j0 += PPI) {
+            const int j = j0 + grp;
+            const bool valid = j < cnt;
+            float kv[EPL], vv[EPL];
+            if (valid) {
+                Elem<KVT>::load_vec_cg(kpool + base + (size_t)j * HD + lr * EPL, kv);
+                Elem<KVT>::load_vec_cg(vpool + base + (size_t)j * HD + lr * EPL, vv);
+            } else {
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) { kv[e] = 0.f; vv[e] = 0.f; }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float s = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) s = fmaf(q[g][e], kv[e], s);
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                s = s / inv_div;
+                if (valid) {
+                    float mn = fmaxf(m[g], s);
+                    float sc = expf(m[g] - mn), pe = expf(s - mn);
+                    l[g] = l[g] * sc + pe;
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * sc + pe * vv[e];
+                    m[g] = mn;
+                }
+            }
+        }
+    }
+    // merge the PPI lane groups of the warp
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = LPR; o < 32; o <<= 1) {
+            float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
+            float lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+            float mn = fmaxf(m[g], mo);
+            float sa = expf(m[g] - mn), sb = expf(mo - mn);
+            l[g] = l[g] * sa + lo * sb;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                float ao = __shfl_xor_sync(0xffffffffu, acc[g][e], o);
+                acc[g][e] = acc[g][e] * sa + ao * sb;
+            }
+            m[g] = mn;
+        }
+        if (grp == 0) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) sred[warp][g][lr * EPL + e] = acc[g][e];
+            if (lr == 0) { sred[warp][g][HD] = m[g]; sred[warp][g][HD + 1] = l[g]; }
+        }
+    }
+    __syncthreads();
+    // merge the warps; thread t < HD owns output dim t
+    for (int i = tid; i < G * HD; i += blockDim.x) {
+        int g = i / HD, e = i % HD;
+        float mn = kNegBig;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) mn = fmaxf(mn, sred[w][g][HD]);
+        float lt = 0.f, at = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            float sc = expf(sred[w][g][HD] - mn);
+            lt += sred[w][g][HD + 1] * sc;
+            at += sred[w][g][e] * sc;
+        }
+        int h = h0 + g;
+        if (S == 1) {
+            float o = at / lt;
+            if (p.gbuf) o *= p.gbuf[((size_t)b * p.heads + h) * HD + e];
+            p.abuf[((size_t)b * p.heads + h) * HD + e] = o;
+        } else {
+            float* pp = p.part + (((size_t)b * p.heads + h) * S + split) * (HD + 2);
+            pp[e] = at;
+            if (e == 0) { pp[HD] = mn; pp[HD + 1] = lt; }
+        }
+    }
+    if (S == 1) return;
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int t = atomicAdd(&p.ticket[b * p.kv_heads + kvh], 1);
+        is_last = (t == S - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int i = tid; i < G * HD; i += blockDim.x) {
+        int g = i / HD, e = i % HD, h = h0 + g;
+        const float* pp = p.part + ((size_t)b * p.heads + h) * S * (HD + 2);
+        float mn = kNegBig;
+        for (int s = 0; s < S; ++s) mn = fmaxf(mn, __ldcg(pp + (size_t)s * (HD + 2) + HD));
+        float lt = 0.f, at = 0.f;
+        for (int s = 0; s < S; ++s) {
+            float sc = expf(__ldcg(pp + (size_t)s * (HD + 2) + HD) - mn);
+            lt += __ldcg(pp + (size_t)s * (HD + 2) + HD + 1) * sc;
+            at += __ldcg(pp + (size_t)s * (HD + 2) + e) * sc;
+        }
+        float o = at / lt;
+        if (p.gbuf) o *= p.gbuf[((size_t)b * p.heads + h) * HD + e];
+        p.abuf[((size_t)b * p.heads + h) * HD + e] = o;
+    }
+    if (tid == 0) p.ticket[b * p.kv_heads + kvh] = 0;
+}
+
+// ------------------------------------------------------------------------------------
+// Gated delta-net recurrent update (no counterpart in the reference):
+//   S <- alpha S ; u = S k^ ; S <- S + beta (v - u) k^T ; o = S q^
+// done row by row: a warp owns rows of S (dk floats each, spread over its lanes), so the
+// state is read once and written once per step; the two dot products per row are
+// warp-shuffle reductions. q^,k^ (L2-normalised), beta, alpha are prepared per CTA in
+// shared memory from the raw projection outputs.
+// raw layout per sequence: [q (H*dk) | k (H*dk) | v (H*dv) | beta (H) | alpha (H)]
+// grid = (dv / rows_per_cta, H, B), block = 256 (8 warps x 4 rows).
+// ------------------------------------------------------------------------------------
+template <int DK>
+__global__ void __launch_bounds__(256) delta_net_kernel(StepCtl c, const float* __restrict__ raw, int raw_stride,
+                                                        float* __restrict__ state, int H, int dv,
+                                                        float* __restrict__ abuf, float l2_eps) {
+    constexpr int EPL = DK / 32;
+    constexpr int ROWS_PER_WARP = 4;
+    const int b = blockIdx.z, h = blockIdx.y;
+    if (!seq_active(c, b)) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ float sq[DK], sk[DK];
+    __shared__ float sgate[2];
+    const float* r = raw + (size_t)b * raw_stride;
+    const float* rq = r + (size_t)h * DK;
+    const float* rk = r + (size_t)H * DK + (size_t)h * DK;
+    const float* rv = r + (size_t)2 * H * DK + (size_t)h * dv;
+    if (warp < 2) {
+        const float* src = warp == 0 ? rq : rk;
+        float v[EPL], ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { v[e] = src[lane * EPL + e]; ss = fmaf(v[e], v[e], ss); }
+        ss = warp_sum(ss);
+        float n = sqrtf(ss + l2_eps);
+        float* dst = warp == 0 ? sq : sk;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) dst[lane * EPL + e] = v[e] / n;
+    } else if (warp == 2 && lane < 2) {
+        float g = r[(size_t)2 * H * DK + (size_t)H * dv + (size_t)lane * H + h];
+        sgate[lane] = 1.0f / (1.0f + expf(-g));
+    }
+    __syncthreads();
+    const float beta = sgate[0], alpha = sgate[1];
+    float qn[EPL], kn[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) { qn[e] = sq[lane * EPL + e]; kn[e] = sk[lane * EPL + e]; }
+    const int row0 = blockIdx.x * (8 * ROWS_PER_WARP) + warp * ROWS_PER_WARP;
+    float* Sh = state + ((size_t)b * H + h) * (size_t)dv * DK;
+    float s[ROWS_PER_WARP][EPL];
+#pragma unroll
+    for (int i = 0; i < ROWS_PER_WARP; ++i) {
+        int row = row0 + i;
+        if (row < dv) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) s[i][e] = Sh[(size_t)row * DK + lane * EPL + e];
+        } else {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) s[i][e] = 0.f;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < ROWS_PER_WARP; ++i) {
+        int row = row0 + i;
+        float d1 = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { s[i][e] *= alpha; d1 = fmaf(s[i][e], kn[e], d1); }
+        d1 = warp_sum(d1);
+        float vi = row < dv ? rv[row] : 0.f;
+        float cf = beta * (vi - d1);
+        float d2 = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { s[i][e] = fmaf(cf, kn[e], s[i][e]); d2 = fmaf(s[i][e], qn[e], d2); }
+        d2 = warp_sum(d2);
+        if (row < dv) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) Sh[(size_t)row * DK + lane * EPL + e] = s[i][e];
+            if (lane == 0) abuf[((size_t)b * H + h) * dv + row] = d2;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// Temperature / top-k / Philox sampler (no counterpart in the reference). One CTA per
+// sequence over the fp32 logits the LM head wrote: 4-pass radix select of the k-th largest
+// value, candidates gathered and bitonic-sorted by (value desc, index asc), softmax over the
+// kept set accumulated sequentially in that order, inverse CDF with one Philox4x32-10 draw
+// keyed by the sequence seed at counter = position of the token being drawn.
+// ------------------------------------------------------------------------------------
+struct SampleParams {
+    const float* logits; int V;
+    int top_k; float temperature;
+    const unsigned long long* seeds;   // [B]
+};
+
+__device__ __forceinline__ uint32_t philox_first_word(uint32_t c0, uint32_t k0, uint32_t k1) {
+    uint32_t c[4] = {c0, 0u, 0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 10; ++i) {
+        uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+        uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+        uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
+        c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    return c[0];
+}
+
+__device__ __forceinline__ uint32_t float_order_key(float f) {
+    uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);   // larger float -> larger key
+}
+
+constexpr int kSampleCap = 1024;       // max candidates kept in shared memory
+
+__global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, SampleParams p) {
+    const int b = blockIdx.x;
+    if (!seq_active(c, b)) return;
+    const int tid = threadIdx.x;
+    const float* lg = p.logits + (size_t)b * p.V;
+    const float T = p.temperature;
+    const int k = min(p.top_k, min(p.V, kSampleCap));
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t s_prefix, s_mask, s_need;
+    __shared__ float cval[kSampleCap];
+    __shared__ int cidx[kSampleCap];
+    __shared__ int s_count, s_overflow;
+    if (tid == 0) { s_prefix = 0; s_mask = 0; s_need = (uint32_t)k; }
+    __syncthreads();
+    // radix select, most significant byte first: after the passes s_prefix is the key of the
+    // k-th largest element.
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix, mask = s_mask;
+        for (int i = tid; i < p.V; i += blockDim.x) {
+            uint32_t key = float_order_key(lg[i] / T);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t need = s_need, bin = 255;
+            for (;; --bin) {
+                uint32_t h = hist[bin];
+                if (h >= need || bin == 0) break;
+                need -= h;
+            }
+            s_need = need;
+            s_prefix = prefix | (bin << shift);
+            s_mask = mask | (0xffu << shift);
+        }
+        __syncthreads();
+    }
+    const uint32_t kth = s_prefix;
+    if (tid == 0) { s_count = 0; s_overflow = 0; }
+    __syncthreads();
+    for (int i = tid; i < p.V; i += blockDim.x) {
+        float v = lg[i] / T;
+        if (float_order_key(v) >= kth) {
+            int slot = atomicAdd(&s_count, 1);
+            if (slot < kSampleCap) { cval[slot] = v; cidx[slot] = i; } else s_overflow = 1;
+        }
+    }
+    __syncthreads();
+    int n = min(s_count, kSampleCap);
+    if (s_overflow) {
+        // More than kSampleCap values tie at the threshold: keep the strictly larger ones and
+        // refill ties in index order with one thread (degenerate inputs only).
+        if (tid == 0) {
+            int w = 0;
+            for (int i = 0; i < p.V && w < kSampleCap; ++i) {
+                float v = lg[i] / T;
+                if (float_order_key(v) > kth) { cval[w] = v; cidx[w] = i; ++w; }
+            }
+            for (int i = 0; i < p.V && w < kSampleCap; ++i) {
+                float v = lg[i] / T;
+                if (float_order_key(v) == kth) { cval[w] = v; cidx[w] = i; ++w; }
+            }
+            s_count = w;
+        }
+        __syncthreads();
+        n = s_count;
+    }
+    // pad to a power of two and bitonic sort: value descending, index ascending
+    int np2 = 1;
+    while (np2 < n) np2 <<= 1;
+    for (int i = n + tid; i < np2; i += blockDim.x) { cval[i] = -INFINITY; cidx[i] = 0x7fffffff; }
+    __syncthreads();
+    for (int sz = 2; sz <= np2; sz <<= 1) {
+        for (int st = sz >> 1; st > 0; st >>= 1) {
+            for (int i = tid; i < np2; i += blockDim.x) {
+                int j = i ^ st;
+                if (j > i) {
+                    bool up = ((i & sz) == 0);
+                    float vi = cval[i], vj = cval[j];
+                    int ii = cidx[i], ij = cidx[j];
+                    bool i_first = (vi > vj) || (vi == vj && ii < ij);   // i belongs before j
+                    if (i_first != up) { cval[i] = vj; cval[j] = vi; cidx[i] = ij; cidx[j] = ii; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (tid == 0) {
+        int kk = min(k, n);
+        float v0 = cval[0], total = 0.f;
+        for (int j = 0; j < kk; ++j) total += expf(cval[j] - v0);
+        unsigned long long seed = p.seeds[b];
+        uint32_t w0 = philox_first_word((uint32_t)(c.pos[b] + 1), (uint32_t)(seed & 0xffffffffull), (uint32_t)(seed >> 32));
+        float u = (float)(w0 >> 8) * (1.0f / 16777216.0f);
+        float target = u * total, cum = 0.f;
+        int pick = kk - 1;
+        for (int j = 0; j < kk; ++j) {
+            cum += expf(cval[j] - v0);
+            if (cum > target) { pick = j; break; }
+        }
+        advance_seq(c, b, cidx[pick]);
+    }
+}
+
+// Column softmax of the logits for the probability probe (getVocabMaxByCol_softmax,
+// getVocabSumByCol_softmax, applySoftmaxToVocab, inference.cu:293-362). One CTA.
+__global__ void __launch_bounds__(256) softmax_probe_kernel(const float* __restrict__ logits, int V, float* __restrict__ out) {
+    __shared__ float red[256];
+    const int tid = threadIdx.x;
+    float mx = -1.0e20f;
+    for (int i = tid; i < V; i += blockDim.x) mx = fmaxf(mx, logits[i]);
+    red[tid] = mx;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) { if (tid < s) red[tid] = fmaxf(red[tid], red[tid + s]); __syncthreads(); }
+    mx = red[0];
+    __syncthreads();
+    float sum = 0.f;
+    for (int i = tid; i < V; i += blockDim.x) { float e = expf(logits[i] - mx); out[i] = e; sum += e; }
+    red[tid] = sum;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) { if (tid < s) red[tid] += red[tid + s]; __syncthreads(); }
+    sum = red[0];
+    for (int i = tid; i < V; i += blockDim.x) out[i] = out[i] / sum;
+}
+
+// ------------------------------------------------------------------------------------
+// Load-time conversions
+// ------------------------------------------------------------------------------------
+__global__ void cvt_f32_to_bf16_kernel(const float* __restrict__ src, bf16_t* __restrict__ dst, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
+}
+
+// One warp per row: scale = max|row| / 448 (1 when the row is all zero), code = e4m3(w / scale).
+__global__ void quant_fp8_rows_kernel(const float* __restrict__ src, fp8_t* __restrict__ dst,
+                                      float* __restrict__ scale, int rows, int cols) {
+    int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* s = src + (size_t)row * cols;
+    float amax = 0.f;
+    for (int i = lane; i < cols; i += 32) amax = fmaxf(amax, fabsf(s[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float sc = amax > 0.f ? amax / 448.0f : 1.0f;
+    if (lane == 0) scale[row] = sc;
+    for (int i = lane; i < cols; i += 32)
+        dst[(size_t)row * cols + i].v = (uint8_t)__nv_cvt_float_to_fp8(s[i] / sc, __NV_SATFINITE, __NV_E4M3);
+}
+
+// Writes a buffer larger than L2 so that the next timed step starts cold.
+__global__ void l2_flush_kernel(float4* __restrict__ buf, size_t n, float v) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) buf[i] = make_float4(v, v, v, v);
+}
+
+}  // namespace mlb

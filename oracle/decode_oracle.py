@@ -54,16 +54,35 @@ def quantize_fp8_rows(w: torch.Tensor):
     return codes.to(torch.float32), scale
 
 
+_libm = None
+
+
+def _libm_f32(name):
+    """float32 libm entry (powf / cosf / sinf): the reference builds its table with these on
+    the host (inference.cu:369-371); numpy's own float32 routines differ by an ulp or two."""
+    global _libm
+    import ctypes
+    import ctypes.util
+    if _libm is None:
+        _libm = ctypes.CDLL(ctypes.util.find_library("m") or "libm.so.6")
+    fn = getattr(_libm, name)
+    fn.restype = ctypes.c_float
+    fn.argtypes = [ctypes.c_float] * (2 if name == "powf" else 1)
+    return fn
+
+
 def rope_table(max_len: int, head_dim: int, base: float) -> np.ndarray:
     """[max_len, head_dim] interleaved (cos, sin) - inference.cu:364-374 in float32."""
-    pairs = np.arange(head_dim // 2, dtype=np.float32)
-    expo = (np.float32(-2.0) * pairs) / np.float32(head_dim)
-    inv = np.power(np.float32(base), expo).astype(np.float32)
+    powf, cosf, sinf = _libm_f32("powf"), _libm_f32("cosf"), _libm_f32("sinf")
+    pairs = head_dim // 2
+    inv = np.array([powf(float(base), float(np.float32(-2.0) * np.float32(i) / np.float32(head_dim)))
+                    for i in range(pairs)], dtype=np.float32)
     pos = np.arange(max_len, dtype=np.float32)[:, None]
     theta = (pos * inv[None, :]).astype(np.float32)
     tab = np.empty((max_len, head_dim), dtype=np.float32)
-    tab[:, 0::2] = np.cos(theta)
-    tab[:, 1::2] = np.sin(theta)
+    flat = theta.ravel()
+    tab[:, 0::2] = np.array([cosf(float(t)) for t in flat], dtype=np.float32).reshape(max_len, pairs)
+    tab[:, 1::2] = np.array([sinf(float(t)) for t in flat], dtype=np.float32).reshape(max_len, pairs)
     return tab
 
 
@@ -94,7 +113,9 @@ class OracleWeights:
             for k, v in blk.items():
                 o[k] = _t(v) if v.ndim == 1 else self._mat(v)
             for k, v in model["ext"][b].items():
-                o[k] = self._mat(v, small=True)
+                # per-layer-embedding tensors stay bf16 under FP8 weights; the delta-net gate
+                # rows are part of the fused projection and follow the main weight type
+                o[k] = self._mat(v, small=k in ("pleTable", "pleProjection"))
             self.blocks.append(o)
 
     def _mat(self, a, small: bool = False) -> torch.Tensor:

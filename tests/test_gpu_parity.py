@@ -1,0 +1,374 @@
+"""GPU parity: the CUDA decode path, called through the C ABI, against the CPU oracle and
+against the logits of the reference's own PyTorch script. Integer results (token ids) must be
+identical; logits within 1e-3 (fp32) / 2e-2 (bf16, FP8) of the oracle, in the metric of
+helpers.logits_error."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import (TOL_FP32, TOL_LOWP, load_oracle, logits_error, oracle_rollout, random_prompts,
+                     write_model)
+from mini_llm_cuda_b200.model_file import ModelSpec, named_spec, periodic_layer_types
+from oracle.decode_oracle import sample_top_k
+
+pytestmark = pytest.mark.gpu
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+from make_reference_golden import SEED_WEIGHTS, golden_spec  # noqa: E402
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "reference_pytorch_logits.npz")
+
+
+@pytest.fixture(scope="module")
+def api(built_lib):
+    from mini_llm_cuda_b200 import api as _api
+    return _api
+
+
+def small(**kw) -> ModelSpec:
+    base = dict(dim=128, layers=3, heads=2, head_dim=64, ffn_dim=256, vocab=512, max_context=128, rms_eps=1e-5)
+    base.update(kw)
+    return ModelSpec(**base)
+
+
+SPECS = {
+    "attn_fp32": small(),
+    "qknorm_gating": small(qk_norm=True, query_gating=True, rms_eps=1e-8),
+    "ple": small(ple_dim=32),
+    "delta_only": small(layer_types=periodic_layer_types(3, 1)),
+    "mixed_ple": small(layers=4, ple_dim=32, layer_types=periodic_layer_types(4, 2)),
+    "gqa": small(dim=256, heads=4, kv_heads=2, query_gating=True),
+    "gqa8": small(dim=256, heads=8, kv_heads=1, qk_norm=True),
+    "hd128": small(dim=256, heads=2, head_dim=128, qk_norm=True),
+    "dn128": small(dim=256, heads=2, head_dim=128, layer_types=periodic_layer_types(3, 1)),
+    "dn_kv_mixed_dims": small(dim=256, heads=2, head_dim=64, dn_key_dim=128, dn_value_dim=64,
+                              layer_types=periodic_layer_types(3, 3)),
+    "bf16": small(ple_dim=32, layers=4, layer_types=periodic_layer_types(4, 2), weight_dtype="bfloat16",
+                  kv_dtype="bfloat16"),
+    "bf16_w_f32_kv": small(weight_dtype="bfloat16", kv_dtype="float32", query_gating=True),
+    "fp8": small(dim=256, heads=4, kv_heads=2, ple_dim=32, layers=4, layer_types=periodic_layer_types(4, 4),
+                 weight_dtype="float8_e4m3", kv_dtype="bfloat16"),
+}
+
+
+def tol_of(spec):
+    return TOL_FP32 if spec.weight_dtype == "float32" and spec.kv_dtype == "float32" else TOL_LOWP
+
+
+@pytest.mark.parametrize("name", list(SPECS))
+def test_greedy_rollout_matches_oracle(api, tmp_path, name):
+    """Batch 1: 20-token prompt, 48 greedy tokens: identical ids, logits within tolerance at
+    every step (context crosses three KV pages)."""
+    spec = SPECS[name]
+    path = write_model(tmp_path, spec, seed=3)
+    oracle = load_oracle(path)
+    prompt = random_prompts(spec.vocab, [20], seed=11)[0]
+    want_tok, want_logits = oracle_rollout(oracle, prompt, 48)
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    sess.prefill([prompt])
+    got = []
+    worst = 0.0
+    for i in range(48):
+        t = sess.decode_step()
+        got.append(int(t[0]))
+        worst = max(worst, logits_error(sess.logits()[0], want_logits[i]))
+        if got[-1] != want_tok[i]:
+            break
+    assert worst < tol_of(spec), f"{name}: logits error {worst}"
+    assert got == want_tok[:len(got)].tolist() and len(got) == 48
+    sess.close()
+    model.close()
+
+
+@pytest.mark.parametrize("name,batch", [("attn_fp32", 3), ("mixed_ple", 9), ("bf16", 5), ("gqa", 17)])
+def test_ragged_batch_matches_oracle(api, tmp_path, name, batch):
+    """Ragged prompts (1 .. 37 tokens) in one batch, decode_n in one call: every sequence
+    equals its own batch-1 oracle roll-out."""
+    spec = SPECS[name]
+    path = write_model(tmp_path, spec, seed=4)
+    oracle = load_oracle(path)
+    lens = [1 + (7 * i) % 37 for i in range(batch)]
+    prompts = random_prompts(spec.vocab, lens, seed=5)
+    model = api.Model(path)
+    sess = api.Session(model, batch)
+    sess.prefill(prompts)
+    got = sess.decode(24)
+    last = sess.logits()
+    for b in range(batch):
+        want_tok, want_logits = oracle_rollout(oracle, prompts[b], 24)
+        assert got[b].tolist() == want_tok.tolist(), f"sequence {b}"
+        assert logits_error(last[b], want_logits[-1]) < tol_of(spec)
+    assert sess.positions().tolist() == [l - 1 + 24 for l in lens]
+    sess.close()
+    model.close()
+
+
+def test_reference_script_golden_logits(api, tmp_path):
+    """Column L-1 of the reference's [V x L] logits (its PyTorch script, run unchanged) against a
+    KV-cached decode of the same 256 tokens: logits within 1e-3, identical argmax at all 256
+    positions."""
+    g = np.load(GOLDEN)
+    spec = golden_spec()
+    path = write_model(tmp_path, spec, seed=SEED_WEIGHTS, random_gains=True)
+    tokens = g["tokens"].tolist()
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    sess.prefill([tokens[:1]])
+    cols = g["columns"].tolist()
+    picks = []
+    for i, t in enumerate(tokens):
+        out = sess.decode_step(in_tokens=[t])
+        picks.append(int(out[0]))
+        if i in cols:
+            err = logits_error(sess.logits()[0], g["logits_columns"][cols.index(i)])
+            assert err < TOL_FP32, f"column {i}: {err}"
+    assert picks == g["argmax"].tolist()
+    # probabilities of the last column: softmax as the reference's vocab softmax kernels
+    probs = sess.probs_col(0)
+    lg = g["logits_columns"][cols.index(255)].astype(np.float64)
+    want = np.exp(lg - lg.max())
+    want /= want.sum()
+    assert np.abs(probs - want).max() < 1e-6 and abs(probs.sum() - 1.0) < 1e-4
+    # the prompt path (prefill of all 256 tokens at once) reaches the same state
+    sess.prefill([tokens])
+    out = sess.decode_step()
+    assert int(out[0]) == int(g["argmax"][255])
+    assert logits_error(sess.logits()[0], g["logits_columns"][cols.index(255)]) < TOL_FP32
+    sess.close()
+    model.close()
+
+
+def test_base_file_without_config_needs_override(api, tmp_path):
+    """A file in the reference's plain format (no config key): heads/head_dim come from the
+    caller, as they come from network_meta.h in the reference."""
+    spec = small(qk_norm=True, query_gating=True, rms_eps=1e-8)
+    path = write_model(tmp_path, spec, seed=8, with_config=False)
+    with pytest.raises(api.MlbError) as e:
+        api.Model(path)
+    assert e.value.status == api.MLB_E_INVALID
+    ov = api.make_override(heads=2, head_dim=64, max_context=128)
+    model = api.Model(path, override=ov)
+    assert model.config.qk_norm == 1 and model.config.query_gating == 1     # inferred from the keys present
+    oracle = load_oracle(path, {"heads": 2, "head_dim": 64, "max_context": 128})
+    prompt = random_prompts(spec.vocab, [9], seed=2)[0]
+    want_tok, _ = oracle_rollout(oracle, prompt, 16)
+    sess = api.Session(model, 1)
+    sess.prefill([prompt])
+    assert sess.decode(16)[0].tolist() == want_tok.tolist()
+    sess.close()
+    model.close()
+
+
+def test_file_dtypes_float64_and_bfloat16(api, tmp_path):
+    spec = small()
+    prompt = random_prompts(spec.vocab, [6], seed=2)[0]
+    p32 = write_model(tmp_path, spec, seed=9, name="f32.bin")
+    p64 = write_model(tmp_path, spec, seed=9, file_dtype="float64", name="f64.bin")
+    pbf = write_model(tmp_path, spec, seed=9, file_dtype="bfloat16", name="bf.bin")
+    outs = {}
+    for key, p in (("f32", p32), ("f64", p64), ("bf", pbf)):
+        model = api.Model(p)
+        sess = api.Session(model, 1)
+        sess.prefill([prompt])
+        outs[key] = (sess.decode(8)[0].tolist(), sess.logits()[0].copy())
+        sess.close()
+        model.close()
+    assert outs["f32"][0] == outs["f64"][0] and np.array_equal(outs["f32"][1], outs["f64"][1])
+    want_tok, want_logits = oracle_rollout(load_oracle(pbf), prompt, 8)
+    assert outs["bf"][0] == want_tok.tolist()
+    assert logits_error(outs["bf"][1], want_logits[-1]) < TOL_FP32
+
+
+def test_context_limit_and_errors(api, tmp_path):
+    spec = small(max_context=48)
+    path = write_model(tmp_path, spec, seed=10)
+    model = api.Model(path)
+    sess = api.Session(model, 2)
+    prompts = random_prompts(spec.vocab, [40, 10], seed=1)
+    sess.prefill(prompts)
+    out = sess.decode(12)            # sequence 0 has room for 48-39 = 9 more steps
+    assert (out[0, :9] >= 0).all() and (out[0, 9:] == -1).all() and (out[1] >= 0).all()
+    oracle = load_oracle(path)
+    want0, _ = oracle_rollout(oracle, prompts[0], 9)
+    want1, _ = oracle_rollout(oracle, prompts[1], 12)
+    assert out[0, :9].tolist() == want0.tolist() and out[1].tolist() == want1.tolist()
+    with pytest.raises(api.MlbError) as e:
+        sess.prefill([list(range(49)), [1]])
+    assert e.value.status == api.MLB_E_CONTEXT_FULL
+    with pytest.raises(api.MlbError) as e:
+        sess.prefill([[spec.vocab], [1]])
+    assert e.value.status == api.MLB_E_INVALID
+    with pytest.raises(api.MlbError) as e:
+        sess.prefill([[], [1]])
+    assert e.value.status == api.MLB_E_INVALID
+    # a pool too small for the batch: the allocator reports it, nothing is launched
+    tiny = api.Session(model, 2, kv_pages=3)
+    with pytest.raises(api.MlbError) as e:
+        tiny.prefill(random_prompts(spec.vocab, [40, 40], seed=1))
+    assert e.value.status == api.MLB_E_KV_FULL
+    tiny.close()
+    # run to the very end of the context: the last position is usable, then CONTEXT_FULL
+    sess.prefill([prompts[1], prompts[1]])
+    out = sess.decode(48)
+    assert (out[:, :39] >= 0).all() and (out[:, 39:] == -1).all()
+    with pytest.raises(api.MlbError) as e:
+        sess.decode_step()
+    assert e.value.status == api.MLB_E_CONTEXT_FULL
+    sess.close()
+    model.close()
+
+
+def test_topk_sampler_matches_oracle_on_device_logits(api, tmp_path):
+    """Teacher-forced: at every step the device's draw must equal the oracle's draw from the
+    device's own logits (same Philox counter), except where the uniform lands within 1e-5 of a
+    CDF boundary."""
+    spec = small(vocab=2048)
+    path = write_model(tmp_path, spec, seed=12)
+    model = api.Model(path)
+    batch = 4
+    sess = api.Session(model, batch)
+    prompts = random_prompts(spec.vocab, [5, 9, 2, 16], seed=3)
+    sess.prefill(prompts)
+    seeds = [0, 1, 2, 2**40 + 5]
+    samp = {"mode": "top_k", "top_k": 50, "temperature": 0.8, "seeds": seeds}
+    pos = [len(p) for p in prompts]       # position of the token being drawn
+    close_calls = 0
+    distinct = set()
+    for step in range(40):
+        out = sess.decode_step(samp)
+        lg = sess.logits()
+        for b in range(batch):
+            want, margin = sample_top_k(lg[b], 0.8, 50, seeds[b], pos[b] + step, return_margin=True)
+            distinct.add(int(out[b]))
+            if int(out[b]) != want:
+                assert margin < 1e-5, f"step {step} seq {b}: got {out[b]} want {want} margin {margin}"
+                close_calls += 1
+    assert close_calls <= 2 and len(distinct) > 20
+    # k = 1 equals greedy
+    sess.prefill(prompts)
+    a = sess.decode(8, {"mode": "top_k", "top_k": 1, "temperature": 1.0})
+    sess.prefill(prompts)
+    b = sess.decode(8)
+    assert np.array_equal(a, b)
+    sess.close()
+    model.close()
+
+
+def test_sampler_degenerate_ties(api, tmp_path):
+    """All-equal logits (zero embedding table): greedy picks id 0, top-k draws stay inside the
+    k lowest ids."""
+    from mini_llm_cuda_b200.model_file import synth_weights, write_model_bin
+    spec = small(vocab=1536)
+    w = synth_weights(spec, seed=1)
+    w["tokenEmbeddings"][:] = 0.0
+    path = os.path.join(str(tmp_path), "z.bin")
+    write_model_bin(path, spec, w)
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    sess.prefill([[3, 4]])
+    assert sess.decode(3)[0].tolist() == [0, 0, 0]
+    sess.prefill([[3, 4]])
+    out = sess.decode(32, {"mode": "top_k", "top_k": 8, "temperature": 1.0, "seeds": [9]})
+    assert set(out[0].tolist()) <= set(range(8)) and len(set(out[0].tolist())) > 2
+    sess.close()
+    model.close()
+
+
+def test_cfg1_latency_config_bf16(api, tmp_path):
+    """The bench configuration (d=512, 8 layers, 2 of them delta-net, PLE 64, V=8192, bf16):
+    128-token prompt, 64 greedy tokens."""
+    spec = named_spec("cfg1")
+    path = write_model(tmp_path, spec, seed=0, random_gains=False)
+    oracle = load_oracle(path)
+    prompt = random_prompts(spec.vocab, [128], seed=1)[0]
+    want_tok, want_logits = oracle_rollout(oracle, prompt, 64)
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    sess.prefill([prompt])
+    got = sess.decode(64)[0]
+    assert got.tolist() == want_tok.tolist()
+    assert logits_error(sess.logits()[0], want_logits[-1]) < TOL_LOWP
+    nbytes = sess.step_bytes()
+    assert nbytes["weights"] == model.weight_bytes and nbytes["kv"] > 0 and nbytes["state"] > 0
+    ms, _ = sess.decode_timed(4, True)
+    assert (ms > 0).all()
+    stats = sess.profile(2, False)
+    assert {s["name"] for s in stats} >= {"qkv_gemv_norm_rope_kvappend", "attn_flash_decode_paged",
+                                          "deltanet_state_update", "lmhead_gemv_norm_argmax"}
+    sess.close()
+    model.close()
+
+
+def test_cfg0_fp32_64_greedy(api, tmp_path):
+    """Config 0 (the CPU-runnable case): d=256, 4 layers alternating attention / delta-net,
+    PLE 32, V=4096, fp32; 32-token prompt from seed 1, 64 greedy tokens, max context 256."""
+    spec = named_spec("cfg0")
+    path = write_model(tmp_path, spec, seed=0, random_gains=False)
+    oracle = load_oracle(path)
+    prompt = random_prompts(spec.vocab, [32], seed=1)[0]
+    want_tok, want_logits = oracle_rollout(oracle, prompt, 64)
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    sess.prefill([prompt])
+    got = []
+    for i in range(64):
+        got.append(int(sess.decode_step()[0]))
+        assert logits_error(sess.logits()[0], want_logits[i]) < TOL_FP32
+    assert got == want_tok.tolist()
+    sess.close()
+    model.close()
+
+
+def test_compat_entry_points(api, tmp_path, capfd):
+    """The reference's entry points (loadModel / loadVocab / runInferenceLoop / runInference)
+    through their C-linkage twins."""
+    import ctypes as C
+    import json
+    spec = small(qk_norm=True, query_gating=True, rms_eps=1e-8, max_context=64, vocab=600)
+    os.makedirs(os.path.join(str(tmp_path), "model"))
+    path = write_model(os.path.join(str(tmp_path), "model"), spec, seed=21, name="tiny.bin")
+    vocab = [f"w{i}" for i in range(600)]
+    vocab[5] = "\n"
+    with open(os.path.join(str(tmp_path), "vocab.json"), "w") as f:
+        json.dump(vocab, f)
+    prompt = random_prompts(600, [30], seed=4)[0]
+    with open(os.path.join(str(tmp_path), "stories.json"), "w") as f:
+        json.dump([["w1", "w2"], [vocab[t] for t in prompt]], f)
+    L = api.lib()
+    cwd = os.getcwd()
+    os.chdir(str(tmp_path))
+    try:
+        assert L.mlb_compat_load_model(b"missing") == 0                      # 1 = ok, 0 = failure
+        assert L.mlb_compat_load_model(b"tiny") == 1
+        assert L.mlb_compat_load_vocab(b"./vocab.json") == 1
+        assert L.mlb_compat_vocab_lookup(b"w17") == 17 and L.mlb_compat_vocab_lookup(b"nope") == -1
+        assert L.mlb_compat_vocab_token(17) == b"w17" and L.mlb_compat_vocab_token(600) is None
+        assert L.mlb_compat_load_story_context(b"./stories.json", 5, 100) == 0
+        # 50 % of a 30-token story = 15 context tokens; the loop then runs to max context
+        rc = L.mlb_compat_run_inference_loop(b"./stories.json", 1, 50, 1, 0)
+        assert rc == 0                                                       # 0 = ok
+        toks = np.ctypeslib.as_array(L.mlb_compat_tokens(), shape=(64,)).copy()
+        oracle = load_oracle(path)
+        want, _ = oracle_rollout(oracle, prompt[:15], 64 - 15)
+        assert toks[:15].tolist() == prompt[:15] and toks[15:].tolist() == want.tolist()
+        # token-at-a-time form of the same loop (verbose prints the top 10 each step)
+        rc = L.mlb_compat_run_inference_loop(b"./stories.json", 1, 50, 1, 1)
+        assert rc == 0
+        toks2 = np.ctypeslib.as_array(L.mlb_compat_tokens(), shape=(64,)).copy()
+        assert np.array_equal(toks, toks2)
+        # runInference(L): probabilities of column L-1
+        assert L.mlb_compat_run_inference(15) == 0
+        probs = np.ctypeslib.as_array(L.mlb_compat_last_probs(), shape=(600,)).copy()
+        st = oracle.new_state()
+        for t in prompt[:15]:
+            lg = oracle.step(st, t).numpy().astype(np.float64)
+        want_p = np.exp(lg - lg.max())
+        want_p /= want_p.sum()
+        assert np.abs(probs - want_p).max() < 1e-6 and int(probs.argmax()) == int(want[0])
+    finally:
+        os.chdir(cwd)
+        L.mlb_compat_shutdown()
+    assert "Generation took" in capfd.readouterr().out

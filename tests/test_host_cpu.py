@@ -1,0 +1,169 @@
+"""CPU: the host side of the library - model.bin container, C ABI surface, KV page allocator."""
+import json
+import os
+import re
+import struct
+
+import numpy as np
+import pytest
+
+from helpers import write_model
+from mini_llm_cuda_b200.model_file import (ModelSpec, named_spec, periodic_layer_types, synth_weights,
+                                           write_model_bin)
+from oracle.model_bin import read_model_bin
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def api(built_lib):
+    from mini_llm_cuda_b200 import api as _api
+    return _api
+
+
+def declared_functions(header):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mlb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(api):
+    L = api.lib()
+    names = declared_functions("mlb.h") + declared_functions("mini_llm_compat.h")
+    assert len(names) > 40
+    for n in names:
+        assert hasattr(L, n), f"{n} is declared in include/ but not exported"
+    assert b"sm_100a" in L.mlb_version()
+
+
+def test_reference_named_entry_points_are_exported_with_cxx_linkage():
+    """runInferenceLoop & co keep the reference's C++ linkage so that a main written against the
+    reference's headers links: check the mangled names in the dynamic symbol table."""
+    import subprocess
+    from mini_llm_cuda_b200.build import LIB_PATH
+    out = subprocess.run(["nm", "-D", "--defined-only", LIB_PATH], capture_output=True, text=True).stdout
+    for mangled in ("_Z16runInferenceLoopPKciibb", "_Z12runInferencei", "_Z9loadModelPKc", "_Z9loadVocabPKc",
+                    "_Z11vocabLookupPKc", "_Z13vocabGetTokeni", "_Z14allocateMemoryb",
+                    "_Z16loadStoryContextPKcii", "_Z23getPreComputedRopeThetaPfi", "seqTokenIndices"):
+        assert mangled in out, mangled
+
+
+def test_no_compute_without_gpu_fails_loudly(api, tmp_path):
+    import ctypes as C
+    n = C.c_int(0)
+    # cudaGetDeviceCount is the first CUDA call of mlb_model_load
+    path = write_model(tmp_path, ModelSpec(dim=64, layers=1, heads=1, head_dim=64, ffn_dim=64, vocab=32))
+    try:
+        m = api.Model(path)
+    except api.MlbError as e:
+        assert e.status == api.MLB_E_CUDA and "no CPU path" in e.message
+    else:
+        m.close()      # a GPU is present: loading simply works
+
+
+def test_writer_reader_round_trip_and_layout(tmp_path):
+    spec = named_spec("cfg0")
+    w = synth_weights(spec, seed=0)
+    path = os.path.join(str(tmp_path), "m.bin")
+    write_model_bin(path, spec, w)
+    raw = open(path, "rb").read()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + hlen])
+    assert list(header)[:3] == ["tokenEmbeddings", "finalRMSNormGamma", "transformerBlocks"]
+    assert list(header["transformerBlocks"][0])[:9] == [
+        "rmsGamma", "queryWeights", "keyWeights", "valueWeights", "outputProjectionWeights", "rmsGamma2",
+        "feedForwardWeights1A", "feedForwardWeights1B", "feedForwardWeights2"]
+    data_off = 8 + hlen + (8 - (8 + hlen) % 8) % 8
+    first = np.frombuffer(raw, dtype="<f4", count=4, offset=data_off)
+    assert np.array_equal(first, w["tokenEmbeddings"].ravel()[:4])       # row-major, token row contiguous
+    m = read_model_bin(path)
+    assert np.array_equal(m["tokenEmbeddings"], w["tokenEmbeddings"])
+    for b in range(spec.layers):
+        for k, v in w["blocks"][b].items():
+            assert np.array_equal(m["blocks"][b][k], v), (b, k)
+        for k, v in w["ext"][b].items():
+            assert np.array_equal(m["ext"][b][k], v), (b, k)
+    # execution order N-1 .. 0: block 0 is the last layer, a delta-net one for cfg0
+    assert spec.block_type(0) == "delta_net" and "betaWeights" in m["ext"][0]
+    assert m["config"]["layer_types"] == ["attention", "delta_net", "attention", "delta_net"]
+
+
+def test_bf16_file_rounding_is_nearest_even(tmp_path):
+    import torch
+    spec = ModelSpec(dim=64, layers=1, heads=1, head_dim=64, ffn_dim=64, vocab=32)
+    w = synth_weights(spec, seed=3)
+    path = os.path.join(str(tmp_path), "b.bin")
+    write_model_bin(path, spec, w, file_dtype="bfloat16")
+    m = read_model_bin(path)
+    want = torch.from_numpy(w["tokenEmbeddings"]).to(torch.bfloat16).float().numpy()
+    assert np.array_equal(m["tokenEmbeddings"], want)
+
+
+def test_file_inspect_and_format_errors(api, tmp_path):
+    spec = named_spec("cfg0")
+    path = write_model(tmp_path, spec, seed=0)
+    cfg, n = api.inspect_file(path)
+    assert (cfg.dim, cfg.layers, cfg.heads, cfg.head_dim, cfg.ffn_dim, cfg.vocab) == (256, 4, 4, 64, 768, 4096)
+    assert cfg.ple_dim == 32 and list(cfg.layer_types[:4]) == [0, 1, 0, 1] and abs(cfg.rms_eps - 1e-5) < 1e-12
+    m = read_model_bin(path)
+    n_want = m["tokenEmbeddings"].size + m["finalRMSNormGamma"].size + \
+        sum(v.size for b in m["blocks"] for v in b.values()) + sum(v.size for b in m["ext"] for v in b.values())
+    assert n == n_want
+    raw = open(path, "rb").read()
+
+    def expect(blob, status, name):
+        p = os.path.join(str(tmp_path), name)
+        open(p, "wb").write(blob)
+        with pytest.raises(api.MlbError) as e:
+            api.inspect_file(p)
+        assert e.value.status == status, e.value
+
+    with pytest.raises(api.MlbError) as e:
+        api.inspect_file(os.path.join(str(tmp_path), "absent.bin"))
+    assert e.value.status == api.MLB_E_IO
+    expect(b"", api.MLB_E_FORMAT, "empty.bin")
+    expect(raw[:4], api.MLB_E_FORMAT, "short.bin")
+    expect(struct.pack("<Q", 10 ** 12) + raw[8:], api.MLB_E_FORMAT, "hugeheader.bin")
+    expect(raw[:len(raw) - 100], api.MLB_E_FORMAT, "truncated.bin")                 # data runs past the end
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    bad = raw[8:8 + hlen].replace(b'"float32"', b'"float16"', 1)
+    expect(struct.pack("<Q", len(bad)) + bad + raw[8 + hlen:], api.MLB_E_FORMAT, "dtype.bin")
+    expect(struct.pack("<Q", 5) + b"{oops" + b"\0" * 3, api.MLB_E_FORMAT, "json.bin")
+    # a reference-format file says nothing about heads: an override is required
+    base = write_model(tmp_path, ModelSpec(dim=128, layers=2, heads=2, head_dim=64, ffn_dim=128, vocab=64),
+                       name="base.bin", with_config=False)
+    with pytest.raises(api.MlbError) as e:
+        api.inspect_file(base)
+    assert e.value.status == api.MLB_E_INVALID
+    cfg, _ = api.inspect_file(base, api.make_override(heads=2, head_dim=64))
+    assert cfg.kv_heads == 2 and cfg.qk_norm == 0 and abs(cfg.rms_eps - 1e-8) < 1e-15
+    # wrong head count for the tensor shapes
+    with pytest.raises(api.MlbError) as e:
+        api.inspect_file(base, api.make_override(heads=3, head_dim=64))
+    assert e.value.status == api.MLB_E_FORMAT
+
+
+def test_kv_page_allocator(api):
+    a = api.KvAllocator(num_pages=6, batch=3, max_pages_per_seq=4)
+    assert a.ensure(0, 0) == 0 and a.table(0) == []
+    assert a.ensure(0, 1) == 0 and a.table(0) == [0]
+    assert a.ensure(1, 17) == 0 and a.table(1) == [1, 2]
+    assert a.ensure(0, 33) == 0 and a.table(0) == [0, 3, 4]       # pages of a sequence need not be contiguous
+    assert a.free_pages() == 1
+    assert a.ensure(2, 32) == api.MLB_E_KV_FULL                   # needs two, one left: fails, keeps what it got
+    assert b"exhausted" in api.lib().mlb_last_error()
+    assert a.free_pages() == 0 and a.table(2) == [5]
+    assert a.ensure(1, 65) == api.MLB_E_CONTEXT_FULL              # beyond the page table
+    a.release(0)
+    assert a.free_pages() == 3 and a.table(0) == []
+    assert a.ensure(2, 32) == 0 and len(a.table(2)) == 2
+    assert a.ensure(5, 1) == api.MLB_E_INVALID
+
+
+def test_rope_table_bitwise_equals_oracle(api):
+    from oracle.decode_oracle import rope_table
+    for L, hd, base in ((256, 64, 10000.0), (1024, 128, 10000.0), (64, 64, 500000.0)):
+        assert np.array_equal(api.rope_table(L, hd, base), rope_table(L, hd, base))
+    t = api.rope_table(4, 64, 10000.0)
+    assert np.all(t[0, 0::2] == 1.0) and np.all(t[0, 1::2] == 0.0)      # position 0: cos 1, sin 0
+    assert abs(t[1, 0] - np.cos(1.0)) < 1e-7 and abs(t[1, 1] - np.sin(1.0)) < 1e-7
