@@ -402,6 +402,7 @@ static void free_session(mlb_session* s) {
 static StepCtl make_ctl(mlb_session* s, int kind) {
     StepCtl c;
     c.B = s->B;
+    c.vocab = s->m->cfg.vocab;
     c.pos = s->pos;
     c.tok = s->tok;
     c.limit = kind == CHAIN_PREFILL ? s->limit_prefill : s->limit_decode;

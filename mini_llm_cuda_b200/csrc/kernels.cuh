@@ -86,6 +86,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ------------------------------------------------------------------------------------
 struct StepCtl {
     int B;
+    int vocab;
     int* pos;            // [B] position of the pending token == tokens consumed so far
     int* tok;            // [B] pending token
     const int* limit;    // [B] a sequence takes part in the step iff pos < limit
@@ -108,6 +109,7 @@ __device__ __forceinline__ void advance_seq(const StepCtl& c, int b, int sampled
     if (c.prompt != nullptr) {
         c.tok[b] = c.prompt[(size_t)b * c.prompt_stride + p + 1];
     } else {
+        if ((unsigned)sampled >= (unsigned)c.vocab) sampled = 0;   // NaN logits leave no valid pick
         int oi = c.out_idx[b];
         if (oi < c.out_cap) c.out_ring[(size_t)b * c.out_cap + oi] = sampled;
         c.out_idx[b] = oi + 1;
