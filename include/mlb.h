@@ -117,9 +117,10 @@ int mlb_decode_step(mlb_session* s, const mlb_sampling* sampling, const int32_t*
 /* n steps back to back without host round trips; out_tokens is [batch][n]. */
 int mlb_decode_n(mlb_session* s, const mlb_sampling* sampling, int n, int32_t* out_tokens);
 /* As mlb_decode_n, timing each step with CUDA events on the session's stream; flush_l2
- * writes a buffer larger than L2 before each step, outside the timed bracket. */
+ * writes a buffer larger than L2 before each step, outside the per-step bracket. total_ms
+ * (nullable) is first start to last end, flushes included when they are on. */
 int mlb_decode_timed(mlb_session* s, const mlb_sampling* sampling, int n, int flush_l2,
-                     float* step_ms, int32_t* out_tokens);
+                     float* step_ms, float* total_ms, int32_t* out_tokens);
 /* Runs n steps kernel by kernel with events around every launch. */
 int mlb_profile_decode(mlb_session* s, const mlb_sampling* sampling, int n, int flush_l2,
                        mlb_kernel_stat* stats, int max_stats, int* n_stats);

@@ -77,7 +77,7 @@ def lib() -> C.CDLL:
         "mlb_prefill": (C.c_int, [vp, i32p, i32p, C.c_int]),
         "mlb_decode_step": (C.c_int, [vp, samp, i32p, i32p]),
         "mlb_decode_n": (C.c_int, [vp, samp, C.c_int, i32p]),
-        "mlb_decode_timed": (C.c_int, [vp, samp, C.c_int, C.c_int, f32p, i32p]),
+        "mlb_decode_timed": (C.c_int, [vp, samp, C.c_int, C.c_int, f32p, f32p, i32p]),
         "mlb_profile_decode": (C.c_int, [vp, samp, C.c_int, C.c_int, C.POINTER(KernelStat), C.c_int, C.POINTER(C.c_int)]),
         "mlb_get_logits": (C.c_int, [vp, f32p]),
         "mlb_get_probs_col": (C.c_int, [vp, C.c_int, f32p]),
@@ -243,8 +243,10 @@ class Session:
         out = np.empty((self.batch, n), dtype=np.int32)
         ms = np.empty(n, dtype=np.float32)
         sp, keep = _sampling(sampling, self.batch)
+        total = C.c_float(0.0)
         check(lib().mlb_decode_timed(self._h, C.byref(sp) if sp else None, n, 1 if flush_l2 else 0,
-                                     _ptr(ms, C.c_float), _ptr(out, C.c_int32)))
+                                     _ptr(ms, C.c_float), C.byref(total), _ptr(out, C.c_int32)))
+        self.last_total_ms = float(total.value)
         return ms, out
 
     def profile(self, n: int, flush_l2: bool, sampling: Optional[dict] = None) -> List[dict]:

@@ -841,7 +841,7 @@ extern "C" int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t*
 namespace mlb {
 // Shared body of the decode entry points. step_ms != null times each step.
 static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int32_t* in_tokens, int32_t* out_tokens,
-                       float* step_ms, int flush_l2) {
+                       float* step_ms, float* total_ms, int flush_l2) {
     if (!s || !out_tokens) return fail(MLB_E_INVALID, "null argument");
     if (n < 1) return fail(MLB_E_INVALID, "n must be >= 1");
     CU(cudaSetDevice(s->m->device));
@@ -880,13 +880,13 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
         if (step_ms) CU(cudaEventRecord(ev[2 * i + 1], s->stream));
     }
     // result: ring [B][max_ctx] -> out [B][n]
-    std::vector<int> ring((size_t)B * s->max_ctx);
     if (n == 1) {
         // one id per sequence: gather through the pinned buffer
         CU(cudaMemcpy2DAsync(s->pinned_tok, 4, s->out_ring, (size_t)s->max_ctx * 4, 4, B, cudaMemcpyDeviceToHost, s->stream));
         CU(cudaStreamSynchronize(s->stream));
         for (int b = 0; b < B; ++b) out_tokens[b] = s->h_pos[b] < s->max_ctx ? s->pinned_tok[b] : -1;
     } else {
+        std::vector<int> ring((size_t)B * n);
         CU(cudaMemcpy2DAsync(ring.data(), (size_t)n * 4, s->out_ring, (size_t)s->max_ctx * 4, (size_t)n * 4, B, cudaMemcpyDeviceToHost, s->stream));
         CU(cudaStreamSynchronize(s->stream));
         for (int b = 0; b < B; ++b) {
@@ -896,6 +896,7 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
     }
     if (step_ms) {
         for (int i = 0; i < n; ++i) CU(cudaEventElapsedTime(&step_ms[i], ev[2 * i], ev[2 * i + 1]));
+        if (total_ms) CU(cudaEventElapsedTime(total_ms, ev[0], ev[2 * (size_t)n - 1]));
         for (auto& e : ev) cudaEventDestroy(e);
     }
     for (int b = 0; b < B; ++b) s->h_pos[b] = std::min(s->h_pos[b] + n, s->max_ctx);
@@ -905,14 +906,15 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
 }  // namespace mlb
 
 extern "C" int mlb_decode_step(mlb_session* s, const mlb_sampling* sp, const int32_t* in_tokens, int32_t* out_tokens) {
-    return decode_impl(s, sp, 1, in_tokens, out_tokens, nullptr, 0);
+    return decode_impl(s, sp, 1, in_tokens, out_tokens, nullptr, nullptr, 0);
 }
 extern "C" int mlb_decode_n(mlb_session* s, const mlb_sampling* sp, int n, int32_t* out_tokens) {
-    return decode_impl(s, sp, n, nullptr, out_tokens, nullptr, 0);
+    return decode_impl(s, sp, n, nullptr, out_tokens, nullptr, nullptr, 0);
 }
-extern "C" int mlb_decode_timed(mlb_session* s, const mlb_sampling* sp, int n, int flush_l2, float* step_ms, int32_t* out_tokens) {
+extern "C" int mlb_decode_timed(mlb_session* s, const mlb_sampling* sp, int n, int flush_l2, float* step_ms, float* total_ms,
+                                int32_t* out_tokens) {
     if (!step_ms) return fail(MLB_E_INVALID, "null step_ms");
-    return decode_impl(s, sp, n, nullptr, out_tokens, step_ms, flush_l2);
+    return decode_impl(s, sp, n, nullptr, out_tokens, step_ms, total_ms, flush_l2);
 }
 
 extern "C" int mlb_profile_decode(mlb_session* s, const mlb_sampling* sp, int n, int flush_l2, mlb_kernel_stat* stats,
