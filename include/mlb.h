@@ -14,6 +14,7 @@
 #ifndef MLB_H_
 #define MLB_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -148,6 +149,21 @@ int mlb_kv_alloc_table(const mlb_kv_alloc* a, int seq, int32_t* out, int max_ent
 int mlb_kv_alloc_free_pages(const mlb_kv_alloc* a);
 void mlb_kv_alloc_release(mlb_kv_alloc* a, int seq);
 void mlb_kv_alloc_free(mlb_kv_alloc* a);
+
+/* Stand-alone split-K flash-decode attention over a paged KV cache - the kernel that replaces
+ * the reference's K^T Q GEMM, mask/scale, softmax kernels and V P GEMM (inference.cu:510-579)
+ * inside a decode step - on DEVICE pointers owned by the caller:
+ *   kpool/vpool [page][kv_heads][16][head_dim] (kv_dtype float32 or bfloat16), page_table
+ *   [batch][pt_stride] int32, positions [batch] int32 (sequence b attends to positions
+ *   0..positions[b], which must already be in the cache), q [batch][heads*head_dim] fp32
+ *   (normalised and rotated), gate (nullable) [batch][heads*head_dim] sigmoid gates,
+ *   out [batch][heads*head_dim] fp32. `stream` is a cudaStream_t (NULL = default stream).
+ * Allocates its split-combine scratch with cudaMalloc for the call and returns after the
+ * stream has finished. */
+int mlb_op_attn_decode(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table,
+                       int pt_stride, const int32_t* positions, const float* q, const float* gate_or_null,
+                       float* out, int batch, int heads, int kv_heads, int head_dim, int splits,
+                       void* stream);
 
 /* RoPE table exactly as getPreComputedRopeTheta builds it (inference.h:4,
  * inference.cu:364-374): [max_len][head_dim] interleaved (cos, sin), host float math. */

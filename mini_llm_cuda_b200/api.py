@@ -91,6 +91,8 @@ def lib() -> C.CDLL:
         "mlb_kv_alloc_release": (None, [vp, C.c_int]),
         "mlb_kv_alloc_free": (None, [vp]),
         "mlb_rope_table": (None, [f32p, C.c_int, C.c_int, C.c_float]),
+        "mlb_op_attn_decode": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int,
+                                         C.c_int, C.c_int, vp]),
         "mlb_last_error": (C.c_char_p, []),
         "mlb_version": (C.c_char_p, []),
         "mlb_compat_configure": (C.c_int, [cfgp, C.c_int]),

@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "../../include/mlb.h"
+#include "errors.h"
 #include "kernels.cuh"
 #include "model_file.h"
 

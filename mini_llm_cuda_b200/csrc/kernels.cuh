@@ -119,7 +119,7 @@ __device__ __forceinline__ void advance_seq(const StepCtl& c, int b, int sampled
 }
 
 // Prefill chain has no LM head: a one-thread-per-sequence advance.
-__global__ void advance_kernel(StepCtl c) {
+static __global__ void advance_kernel(StepCtl c) {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < c.B && seq_active(c, b)) advance_seq(c, b, -1);
 }
@@ -755,7 +755,7 @@ __device__ __forceinline__ uint32_t float_order_key(float f) {
 
 constexpr int kSampleCap = 1024;       // max candidates kept in shared memory
 
-__global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, SampleParams p) {
+static __global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, SampleParams p) {
     const int b = blockIdx.x;
     if (!seq_active(c, b)) return;
     const int tid = threadIdx.x;
@@ -863,7 +863,7 @@ __global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, SampleParam
 
 // Column softmax of the logits for the probability probe (getVocabMaxByCol_softmax,
 // getVocabSumByCol_softmax, applySoftmaxToVocab, inference.cu:293-362). One CTA.
-__global__ void __launch_bounds__(256) softmax_probe_kernel(const float* __restrict__ logits, int V, float* __restrict__ out) {
+static __global__ void __launch_bounds__(256) softmax_probe_kernel(const float* __restrict__ logits, int V, float* __restrict__ out) {
     __shared__ float red[256];
     const int tid = threadIdx.x;
     float mx = -1.0e20f;
@@ -885,14 +885,14 @@ __global__ void __launch_bounds__(256) softmax_probe_kernel(const float* __restr
 // ------------------------------------------------------------------------------------
 // Load-time conversions
 // ------------------------------------------------------------------------------------
-__global__ void cvt_f32_to_bf16_kernel(const float* __restrict__ src, bf16_t* __restrict__ dst, size_t n) {
+static __global__ void cvt_f32_to_bf16_kernel(const float* __restrict__ src, bf16_t* __restrict__ dst, size_t n) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
 }
 
 // One warp per row: scale = max|row| / 448 (1 when the row is all zero), code = e4m3(w / scale).
-__global__ void quant_fp8_rows_kernel(const float* __restrict__ src, fp8_t* __restrict__ dst,
+static __global__ void quant_fp8_rows_kernel(const float* __restrict__ src, fp8_t* __restrict__ dst,
                                       float* __restrict__ scale, int rows, int cols) {
     int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
@@ -909,7 +909,7 @@ __global__ void quant_fp8_rows_kernel(const float* __restrict__ src, fp8_t* __re
 }
 
 // Writes a buffer larger than L2 so that the next timed step starts cold.
-__global__ void l2_flush_kernel(float4* __restrict__ buf, size_t n, float v) {
+static __global__ void l2_flush_kernel(float4* __restrict__ buf, size_t n, float v) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < n; i += stride) buf[i] = make_float4(v, v, v, v);

@@ -1,0 +1,110 @@
+// Stand-alone operator entry points over DEVICE pointers: single kernels of the decode step
+// exposed for callers that own their buffers (and for kernel-level parity tests).
+#include <cstdint>
+
+#include "../../include/mlb.h"
+#include "errors.h"
+#include "kernels.cuh"
+
+using namespace mlb;
+
+#define CU(expr)                                                                              \
+    do {                                                                                      \
+        cudaError_t e__ = (expr);                                                             \
+        if (e__ != cudaSuccess)                                                               \
+            return fail(MLB_E_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
+    } while (0)
+
+namespace {
+
+// Scratch of one flash-decode launch, carved from one byte range:
+//   tickets [B*kv_heads] int (zero before the launch) | limits [B] int (never reached) |
+//   partials [B][heads][splits][hd+2] float
+struct AttnScratch {
+    int* ticket;
+    int* limit;
+    float* part;
+};
+
+size_t attn_scratch_bytes(int B, int heads, int kv_heads, int hd, int splits) {
+    size_t ints = ((size_t)B * kv_heads + (size_t)B + 63) / 64 * 64;     // keep the floats 256-byte aligned
+    return ints * 4 + (size_t)B * heads * splits * (hd + 2) * 4;
+}
+
+AttnScratch carve(void* base, int B, int kv_heads) {
+    AttnScratch s;
+    s.ticket = static_cast<int*>(base);
+    s.limit = s.ticket + (size_t)B * kv_heads;
+    size_t ints = ((size_t)B * kv_heads + (size_t)B + 63) / 64 * 64;
+    s.part = reinterpret_cast<float*>(static_cast<int*>(base) + ints);
+    return s;
+}
+
+int check_attn_args(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table, const int32_t* positions,
+                    const float* q, float* out, int batch, int heads, int kv_heads, int head_dim, int splits) {
+    if (!kpool || !vpool || !page_table || !positions || !q || !out) return fail(MLB_E_INVALID, "attention op: null pointer");
+    if (kv_dtype != MLB_DT_F32 && kv_dtype != MLB_DT_BF16) return fail(MLB_E_INVALID, "attention op: kv_dtype must be float32 or bfloat16");
+    if (batch < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads) return fail(MLB_E_INVALID, "attention op: bad batch / head counts");
+    const int g = heads / kv_heads;
+    if (g != 1 && g != 2 && g != 4 && g != 8) return fail(MLB_E_UNSUPPORTED, "attention op: heads/kv_heads must be 1, 2, 4 or 8");
+    if (head_dim != 64 && head_dim != 128) return fail(MLB_E_UNSUPPORTED, "attention op: head_dim must be 64 or 128");
+    if (splits < 1 || splits > 64) return fail(MLB_E_INVALID, "attention op: splits must be in 1..64");
+    return MLB_OK;
+}
+
+template <typename KVT, int HD>
+cudaError_t launch_attn(const StepCtl& c, const AttnParams& p, int G, int splits, int B, cudaStream_t st) {
+    dim3 grid(splits, p.kv_heads, B);
+    switch (G) {
+        case 1: attn_decode_kernel<KVT, HD, 1><<<grid, 128, 0, st>>>(c, p); break;
+        case 2: attn_decode_kernel<KVT, HD, 2><<<grid, 128, 0, st>>>(c, p); break;
+        case 4: attn_decode_kernel<KVT, HD, 4><<<grid, 128, 0, st>>>(c, p); break;
+        default: attn_decode_kernel<KVT, HD, 8><<<grid, 128, 0, st>>>(c, p); break;
+    }
+    return cudaGetLastError();
+}
+
+// Clears the part of the scratch that must start at zero, then launches. No allocation.
+int run_attn(void* scratch, const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table, int pt_stride,
+             const int32_t* positions, const float* q, const float* gate, float* out, int batch, int heads, int kv_heads,
+             int head_dim, int splits, cudaStream_t st) {
+    AttnScratch sc = carve(scratch, batch, kv_heads);
+    CU(cudaMemsetAsync(sc.ticket, 0, (size_t)batch * kv_heads * 4, st));
+    CU(cudaMemsetAsync(sc.limit, 0x7f, (size_t)batch * 4, st));          // 0x7f7f7f7f: every sequence takes part
+    StepCtl c;
+    c.B = batch; c.vocab = 0;
+    c.pos = const_cast<int*>(positions); c.tok = nullptr; c.limit = sc.limit;
+    c.prompt = nullptr; c.prompt_stride = 0; c.out_ring = nullptr; c.out_idx = nullptr; c.out_cap = 0;
+    AttnParams p;
+    p.kpool = kpool; p.vpool = vpool; p.page_table = page_table; p.pt_stride = pt_stride;
+    p.qbuf = q; p.gbuf = gate; p.abuf = out; p.part = sc.part; p.ticket = sc.ticket;
+    p.heads = heads; p.kv_heads = kv_heads;
+    const int G = heads / kv_heads;
+    cudaError_t e;
+    if (kv_dtype == MLB_DT_F32)
+        e = head_dim == 64 ? launch_attn<float, 64>(c, p, G, splits, batch, st) : launch_attn<float, 128>(c, p, G, splits, batch, st);
+    else
+        e = head_dim == 64 ? launch_attn<bf16_t, 64>(c, p, G, splits, batch, st) : launch_attn<bf16_t, 128>(c, p, G, splits, batch, st);
+    if (e != cudaSuccess) return fail(MLB_E_CUDA, "attention op launch failed: %s", cudaGetErrorString(e));
+    return MLB_OK;
+}
+
+}  // namespace
+
+extern "C" int mlb_op_attn_decode(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table, int pt_stride,
+                                  const int32_t* positions, const float* q, const float* gate_or_null, float* out, int batch,
+                                  int heads, int kv_heads, int head_dim, int splits, void* stream) {
+    int rc = check_attn_args(kpool, vpool, kv_dtype, page_table, positions, q, out, batch, heads, kv_heads, head_dim, splits);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    void* scratch = nullptr;
+    cudaError_t e = cudaMalloc(&scratch, attn_scratch_bytes(batch, heads, kv_heads, head_dim, splits));
+    if (e != cudaSuccess) return fail(MLB_E_NOMEM, "attention op: cudaMalloc of the scratch failed: %s", cudaGetErrorString(e));
+    rc = run_attn(scratch, kpool, vpool, kv_dtype, page_table, pt_stride, positions, q, gate_or_null, out, batch, heads, kv_heads,
+                  head_dim, splits, st);
+    cudaError_t se = cudaStreamSynchronize(st);       // the scratch must outlive the kernel
+    cudaFree(scratch);
+    if (rc) return rc;
+    if (se != cudaSuccess) return fail(MLB_E_CUDA, "attention op failed: %s", cudaGetErrorString(se));
+    return MLB_OK;
+}

@@ -1,0 +1,98 @@
+"""GPU: kernel-level parity of the stand-alone operator entry points (device pointers)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api(built_lib):
+    from mini_llm_cuda_b200 import api as _api
+    return _api
+
+
+def make_attention_case(torch, batch, heads, kv_heads, hd, ctx_list, dtype, seed, with_gate):
+    """Random paged KV cache with shuffled page assignment; returns device tensors + fp64 answer."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    block = 16
+    pages_per_seq = [(c + block - 1) // block for c in ctx_list]
+    pt_stride = max(pages_per_seq) + 1
+    n_pages = sum(pages_per_seq) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.zeros(batch, pt_stride, dtype=torch.int32)
+    it = iter(perm)
+    for b in range(batch):
+        for p in range(pages_per_seq[b]):
+            table[b, p] = next(it)
+    kpool = torch.randn(n_pages, kv_heads, block, hd, generator=g).to(dtype)
+    vpool = torch.randn(n_pages, kv_heads, block, hd, generator=g).to(dtype)
+    q = torch.randn(batch, heads * hd, generator=g)
+    gate = torch.rand(batch, heads * hd, generator=g) if with_gate else None
+    want = torch.zeros(batch, heads * hd, dtype=torch.float64)
+    group = heads // kv_heads
+    for b in range(batch):
+        ctx = ctx_list[b]
+        idx = table[b, :pages_per_seq[b]].long()
+        K = kpool[idx].double().permute(1, 0, 2, 3).reshape(kv_heads, -1, hd)[:, :ctx]
+        V = vpool[idx].double().permute(1, 0, 2, 3).reshape(kv_heads, -1, hd)[:, :ctx]
+        for h in range(heads):
+            qh = q[b, h * hd:(h + 1) * hd].double()
+            s = (K[h // group] @ qh) / np.sqrt(hd)
+            p = torch.softmax(s, dim=0)
+            want[b, h * hd:(h + 1) * hd] = p @ V[h // group]
+        if with_gate:
+            want[b] *= gate[b].double()
+    dev = "cuda:0"
+    pos = torch.tensor([c - 1 for c in ctx_list], dtype=torch.int32)
+    return dict(kpool=kpool.to(dev), vpool=vpool.to(dev), table=table.to(dev), pos=pos.to(dev), q=q.to(dev),
+                gate=gate.to(dev) if with_gate else None, want=want, pt_stride=pt_stride)
+
+
+def call_attention(api, torch, fn_name, case, batch, heads, kv_heads, hd, splits, dtype):
+    out = torch.full((batch, heads * hd), float("nan"), device="cuda:0")
+    kv_dt = api.DT_BF16 if dtype == torch.bfloat16 else api.DT_F32
+    fn = getattr(api.lib(), fn_name)
+    rc = fn(case["kpool"].data_ptr(), case["vpool"].data_ptr(), kv_dt, case["table"].data_ptr(), case["pt_stride"],
+            case["pos"].data_ptr(), case["q"].data_ptr(), case["gate"].data_ptr() if case["gate"] is not None else None,
+            out.data_ptr(), batch, heads, kv_heads, hd, splits, None)
+    torch.cuda.synchronize()
+    return rc, out
+
+
+@pytest.mark.parametrize("heads,kv_heads,hd,dtype_name,splits,with_gate", [
+    (4, 4, 64, "float32", 1, False),
+    (4, 4, 64, "bfloat16", 5, True),
+    (8, 2, 128, "bfloat16", 8, True),
+    (8, 1, 64, "float32", 3, False),
+    (4, 2, 128, "float32", 16, True),
+])
+def test_attention_op_matches_fp64(api, heads, kv_heads, hd, dtype_name, splits, with_gate):
+    import torch
+    dtype = getattr(torch, dtype_name)
+    ctx_list = [1, 16, 17, 250, 77]          # one position, page edges, more splits than pages
+    case = make_attention_case(torch, 5, heads, kv_heads, hd, ctx_list, dtype, 3, with_gate)
+    rc, out = call_attention(api, torch, "mlb_op_attn_decode", case, 5, heads, kv_heads, hd, splits, dtype)
+    assert rc == 0, api.lib().mlb_last_error()
+    err = (out.cpu().double() - case["want"]).abs().max().item()
+    assert err < 2e-5, err
+
+
+def test_attention_op_rejects_bad_arguments(api):
+    import torch
+    case = make_attention_case(torch, 1, 4, 4, 64, [5], torch.float32, 1, False)
+    L = api.lib()
+    args = lambda **kw: None
+    out = torch.zeros(1, 256, device="cuda:0")
+    base = [case["kpool"].data_ptr(), case["vpool"].data_ptr(), api.DT_F32, case["table"].data_ptr(), case["pt_stride"],
+            case["pos"].data_ptr(), case["q"].data_ptr(), None, out.data_ptr(), 1, 4, 4, 64, 4, None]
+    bad = list(base); bad[12] = 96
+    assert L.mlb_op_attn_decode(*bad) == api.MLB_E_UNSUPPORTED
+    bad = list(base); bad[11] = 3
+    assert L.mlb_op_attn_decode(*bad) == api.MLB_E_INVALID
+    bad = list(base); bad[6] = None
+    assert L.mlb_op_attn_decode(*bad) == api.MLB_E_INVALID
+    bad = list(base); bad[2] = api.DT_FP8
+    assert L.mlb_op_attn_decode(*bad) == api.MLB_E_INVALID
+    assert L.mlb_op_attn_decode(*base) == 0
