@@ -165,6 +165,24 @@ int mlb_op_attn_decode(const void* kpool, const void* vpool, int kv_dtype, const
                        float* out, int batch, int heads, int kv_heads, int head_dim, int splits,
                        void* stream);
 
+/* No counterpart in the reference. Same operator and arguments as mlb_op_attn_decode, for
+ * callers that cannot allocate device memory: a server that has given all free device memory
+ * to its own pool, or a token loop that must never run into the device-wide synchronisation
+ * of cudaMalloc / cudaFree. The split-combine scratch lives in a fixed 4 MiB array inside the
+ * library image (held by every GPU that loads the library until the process exits); the call
+ * makes no cudaMalloc / cudaFree and does not wait for the stream - the result is ready when
+ * `stream` reaches this point. Shapes whose scratch (about batch*heads*splits*(head_dim+2)*4
+ * bytes) exceeds mlb_op_attn_decode_static_capacity() are refused with MLB_E_UNSUPPORTED.
+ * The FIRST call on each device resolves the array's address (a one-time runtime query): make
+ * that call with the device current and before any stream capture starts. All calls on a
+ * device share the array, so calls whose kernels could overlap on the GPU (two streams, two
+ * threads) race; keep them ordered. */
+int mlb_op_attn_decode_static(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table,
+                              int pt_stride, const int32_t* positions, const float* q,
+                              const float* gate_or_null, float* out, int batch, int heads, int kv_heads,
+                              int head_dim, int splits, void* stream);
+size_t mlb_op_attn_decode_static_capacity(void);
+
 /* RoPE table exactly as getPreComputedRopeTheta builds it (inference.h:4,
  * inference.cu:364-374): [max_len][head_dim] interleaved (cos, sin), host float math. */
 void mlb_rope_table(float* table, int max_len, int head_dim, float base);

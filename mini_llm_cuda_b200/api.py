@@ -93,6 +93,9 @@ def lib() -> C.CDLL:
         "mlb_rope_table": (None, [f32p, C.c_int, C.c_int, C.c_float]),
         "mlb_op_attn_decode": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int,
                                          C.c_int, C.c_int, vp]),
+        "mlb_op_attn_decode_static": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int,
+                                                C.c_int, C.c_int, C.c_int, vp]),
+        "mlb_op_attn_decode_static_capacity": (C.c_size_t, []),
         "mlb_last_error": (C.c_char_p, []),
         "mlb_version": (C.c_char_p, []),
         "mlb_compat_configure": (C.c_int, [cfgp, C.c_int]),

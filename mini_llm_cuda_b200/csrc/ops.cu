@@ -108,3 +108,69 @@ extern "C" int mlb_op_attn_decode(const void* kpool, const void* vpool, int kv_d
     if (se != cudaSuccess) return fail(MLB_E_CUDA, "attention op failed: %s", cudaGetErrorString(se));
     return MLB_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// mlb_op_attn_decode_static: the same flash-decode launch with its scratch in a fixed
+// array that is part of the library image, for callers that must not allocate.
+//
+// Who needs this: a serving process that has handed ALL free device memory to its own pool
+// (its KV cache, typically), where a cudaMalloc from inside a library call fails or steals
+// from that budget; and a latency-critical token loop that cannot afford cudaMalloc /
+// cudaFree at all, because both may synchronise the whole device and stall unrelated streams.
+// Such callers already own q, the KV pools, the page table and the output; the only thing the
+// operator still needed from the allocator was the split-combine scratch.
+//
+// The price: every GPU that loads the library carries kAttnStaticBytes of device memory
+// until the process exits, sizes beyond it are refused, and because every call on a device
+// uses the SAME array, two calls whose kernels overlap on the GPU (different streams, or
+// different host threads) race on it - keep calls on one device ordered.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kAttnStaticBytes = 4u << 20;      // 4 MiB per device
+// In host code this name is only a handle for the runtime, NOT a device address: the address
+// that kernels can use comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kAttnStaticBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_attn_static_ptr[kMaxDevices] = {nullptr};  // per device, filled on the first call there
+
+// One-time set-up for the CURRENT device: resolve the array's device address.
+int attn_static_address(void** out) {
+    int dev = -1;
+    CU(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(MLB_E_UNSUPPORTED, "static attention op: device index %d not supported", dev);
+    if (g_attn_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail(MLB_E_CUDA, "static attention op: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_attn_static_ptr[dev] = p;
+    }
+    *out = g_attn_static_ptr[dev];
+    return MLB_OK;
+}
+
+}  // namespace
+
+extern "C" size_t mlb_op_attn_decode_static_capacity(void) { return kAttnStaticBytes; }
+
+extern "C" int mlb_op_attn_decode_static(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table,
+                                         int pt_stride, const int32_t* positions, const float* q, const float* gate_or_null,
+                                         float* out, int batch, int heads, int kv_heads, int head_dim, int splits,
+                                         void* stream) {
+    int rc = check_attn_args(kpool, vpool, kv_dtype, page_table, positions, q, out, batch, heads, kv_heads, head_dim, splits);
+    if (rc) return rc;
+    const size_t need = attn_scratch_bytes(batch, heads, kv_heads, head_dim, splits);
+    if (need > kAttnStaticBytes)
+        return fail(MLB_E_UNSUPPORTED,
+                    "static attention op: batch %d x heads %d x splits %d x head_dim %d needs %zu bytes of scratch, the "
+                    "built-in array holds %zu; lower splits or batch, or use mlb_op_attn_decode",
+                    batch, heads, splits, head_dim, need, kAttnStaticBytes);
+    void* scratch = nullptr;
+    if ((rc = attn_static_address(&scratch))) return rc;
+    // The array keeps whatever the previous call left: run_attn clears the arrival counters and
+    // rewrites the limits; the partials are fully overwritten before they are read.
+    return run_attn(scratch, kpool, vpool, kv_dtype, page_table, pt_stride, positions, q, gate_or_null, out, batch, heads,
+                    kv_heads, head_dim, splits, static_cast<cudaStream_t>(stream));
+}
