@@ -5,6 +5,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -377,6 +378,7 @@ struct mlb_session {
     int launches_per_step[3] = {0, 0, 0};
     float4* flush_buf = nullptr; size_t flush_n = 0;
     int* pinned_tok = nullptr;
+    bool use_pdl = true;
 };
 
 namespace mlb {
@@ -421,16 +423,36 @@ static int pick_bt(int B, size_t per_seq_floats) {
     return bt;
 }
 
+// Launch with the programmatic-dependent-launch attribute: the kernel may start while its
+// predecessor in the stream still runs and orders itself with griddepcontrol.wait.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_chain(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                Args... args) {
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T, typename T2, typename KVT>
 struct Chain {
     template <int MODE>
     static int gemv(mlb_session* s, const StepCtl& c, GemvParams p, int R, Recorder* rec, const char* name) {
-        constexpr int RW = (MODE == GEMV_SWIGLU) ? 2 : 4;
         p.R = R;
-        const size_t per_seq = (size_t)p.K + p.Kp + R + 1;
+        const size_t per_seq = (size_t)p.K + p.Kp + R + 1 + 8;
         const int BT = pick_bt(s->B, per_seq);
         if (per_seq * 4 > 200 * 1024) return fail(MLB_E_UNSUPPORTED, "projection input of %d floats does not fit shared memory", p.K);
-        const int warps = std::max(1, std::min(8, R / RW));
+        const int rwf = BT == 1 ? 2 : 4;                                  // GemvShape<BT>::RW
+        const int rw = MODE == GEMV_SWIGLU ? rwf / 2 : rwf;
+        const int warps = std::max(1, std::min(8, (R + rw - 1) / rw));
         dim3 grid((p.N + R - 1) / R, (s->B + BT - 1) / BT);
         const size_t smem = (size_t)BT * per_seq * 4;
         if (rec) {
@@ -440,13 +462,14 @@ struct Chain {
             int rc = rec->begin(name, wbytes + abytes, 2ull * p.N * (p.K + p.Kp) * s->B * (MODE == GEMV_SWIGLU ? 2 : 1));
             if (rc) return rc;
         }
+        cudaError_t e;
         switch (BT) {
-            case 1: gemv_kernel<T, T2, KVT, 1, MODE><<<grid, warps * 32, smem, s->stream>>>(c, p); break;
-            case 2: gemv_kernel<T, T2, KVT, 2, MODE><<<grid, warps * 32, smem, s->stream>>>(c, p); break;
-            case 4: gemv_kernel<T, T2, KVT, 4, MODE><<<grid, warps * 32, smem, s->stream>>>(c, p); break;
-            default: gemv_kernel<T, T2, KVT, 8, MODE><<<grid, warps * 32, smem, s->stream>>>(c, p); break;
+            case 1: e = launch_chain(s->use_pdl, gemv_kernel<T, T2, KVT, 1, MODE>, grid, dim3(warps * 32), smem, s->stream, c, p); break;
+            case 2: e = launch_chain(s->use_pdl, gemv_kernel<T, T2, KVT, 2, MODE>, grid, dim3(warps * 32), smem, s->stream, c, p); break;
+            case 4: e = launch_chain(s->use_pdl, gemv_kernel<T, T2, KVT, 4, MODE>, grid, dim3(warps * 32), smem, s->stream, c, p); break;
+            default: e = launch_chain(s->use_pdl, gemv_kernel<T, T2, KVT, 8, MODE>, grid, dim3(warps * 32), smem, s->stream, c, p); break;
         }
-        CU(cudaGetLastError());
+        if (e != cudaSuccess) return fail(MLB_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
         if (rec) return rec->end();
         return MLB_OK;
     }
@@ -473,13 +496,14 @@ struct Chain {
     template <int HD>
     static int attn_g(mlb_session* s, const StepCtl& c, const AttnParams& p, int G) {
         dim3 grid(s->splits, p.kv_heads, s->B);
+        cudaError_t e;
         switch (G) {
-            case 1: attn_decode_kernel<KVT, HD, 1><<<grid, 128, 0, s->stream>>>(c, p); break;
-            case 2: attn_decode_kernel<KVT, HD, 2><<<grid, 128, 0, s->stream>>>(c, p); break;
-            case 4: attn_decode_kernel<KVT, HD, 4><<<grid, 128, 0, s->stream>>>(c, p); break;
-            default: attn_decode_kernel<KVT, HD, 8><<<grid, 128, 0, s->stream>>>(c, p); break;
+            case 1: e = launch_chain(s->use_pdl, attn_decode_kernel<KVT, HD, 1>, grid, dim3(128), 0, s->stream, c, p); break;
+            case 2: e = launch_chain(s->use_pdl, attn_decode_kernel<KVT, HD, 2>, grid, dim3(128), 0, s->stream, c, p); break;
+            case 4: e = launch_chain(s->use_pdl, attn_decode_kernel<KVT, HD, 4>, grid, dim3(128), 0, s->stream, c, p); break;
+            default: e = launch_chain(s->use_pdl, attn_decode_kernel<KVT, HD, 8>, grid, dim3(128), 0, s->stream, c, p); break;
         }
-        CU(cudaGetLastError());
+        if (e != cudaSuccess) return fail(MLB_E_CUDA, "attention launch failed: %s", cudaGetErrorString(e));
         return MLB_OK;
     }
 
@@ -492,10 +516,9 @@ struct Chain {
         int launches = 0, rc;
 
         if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * (d * sizeof(T) + (uint64_t)p * sizeof(T2) + (uint64_t)d * 4) + (uint64_t)d * p * sizeof(T2), 0))) return rc;
-        embed_kernel<T, T2><<<B, 256, (size_t)p * 4, s->stream>>>(c, static_cast<const T*>(m->E), m->Es, d,
-                                                                 static_cast<const T2*>(m->layers[0].pleT),
-                                                                 static_cast<const T2*>(m->layers[0].pleP), p, s->x);
-        CU(cudaGetLastError());
+        CU(launch_chain(s->use_pdl, embed_kernel<T, T2>, dim3(B), dim3(256), (size_t)p * 4, s->stream, c,
+                        static_cast<const T*>(m->E), static_cast<const float*>(m->Es), d, static_cast<const T2*>(m->layers[0].pleT),
+                        static_cast<const T2*>(m->layers[0].pleP), p, s->x));
         if (rec && (rc = rec->end())) return rc;
         ++launches;
 
@@ -542,9 +565,8 @@ struct Chain {
                 const int dk = cfg.dn_key_dim, dv = cfg.dn_value_dim, H = cfg.heads;
                 if (rec && (rc = rec->begin("deltanet_state_update", (uint64_t)B * 2ull * H * dk * dv * 4, (uint64_t)B * 6ull * H * dk * dv))) return rc;
                 dim3 grid((dv + 31) / 32, H, B);
-                if (dk == 64) delta_net_kernel<64><<<grid, 256, 0, s->stream>>>(c, s->raw, s->raw_stride, s->state[i], H, dv, s->abuf, 1e-6f);
-                else delta_net_kernel<128><<<grid, 256, 0, s->stream>>>(c, s->raw, s->raw_stride, s->state[i], H, dv, s->abuf, 1e-6f);
-                CU(cudaGetLastError());
+                if (dk == 64) CU(launch_chain(s->use_pdl, delta_net_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, 1e-6f));
+                else CU(launch_chain(s->use_pdl, delta_net_kernel<128>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, 1e-6f));
                 if (rec && (rc = rec->end())) return rc;
                 ++launches;
             }
@@ -570,8 +592,7 @@ struct Chain {
         }
         if (kind == CHAIN_PREFILL) {
             if (rec && (rc = rec->begin("advance_prompt", (uint64_t)B * 12, 0))) return rc;
-            advance_kernel<<<(B + 127) / 128, 128, 0, s->stream>>>(c);
-            CU(cudaGetLastError());
+            CU(launch_chain(s->use_pdl, advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s->stream, c));
             if (rec && (rc = rec->end())) return rc;
             ++launches;
         } else {
@@ -587,8 +608,7 @@ struct Chain {
                 SampleParams sp;
                 sp.logits = s->logits; sp.V = cfg.vocab; sp.top_k = s->cur_topk; sp.temperature = s->cur_temp; sp.seeds = s->seeds;
                 if (rec && (rc = rec->begin("sample_topk_philox", (uint64_t)B * cfg.vocab * 4 * 5, 0))) return rc;
-                sample_topk_kernel<<<B, 256, 0, s->stream>>>(c, sp);
-                CU(cudaGetLastError());
+                CU(launch_chain(s->use_pdl, sample_topk_kernel, dim3(B), dim3(256), 0, s->stream, c, sp));
                 if (rec && (rc = rec->end())) return rc;
                 ++launches;
             }
@@ -731,7 +751,7 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     s->splits = std::max(1, std::min(std::min(want, 32), std::max(1, s->max_pages / 4)));
     SA(sess_alloc(s, (void**)&s->part, B * c.heads * s->splits * (c.head_dim + 2) * 4, true));
     SA(sess_alloc(s, (void**)&s->attn_ticket, B * c.kv_heads * 4, true));
-    s->lm_rows = 32;
+    s->lm_rows = 16;
     s->lm_parts = (c.vocab + s->lm_rows - 1) / s->lm_rows;
     SA(sess_alloc(s, (void**)&s->part_val, B * s->lm_parts * 4, true));
     SA(sess_alloc(s, (void**)&s->part_idx, B * s->lm_parts * 4, true));
@@ -760,6 +780,10 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     s->h_table.assign(B * s->max_pages, 0);
     std::vector<int> lim(batch, max_context);
     SCU(cudaMemcpy(s->limit_decode, lim.data(), B * 4, cudaMemcpyHostToDevice));
+    {
+        const char* e = std::getenv("MLB_NO_PDL");     // measurement switch: plain stream-ordered launches
+        s->use_pdl = !(e && e[0] == '1');
+    }
     SA(chain_configure(s));
 #undef SA
 #undef SCU

@@ -26,6 +26,9 @@ template <typename T> struct Elem;
 
 template <> struct Elem<float> {
     static constexpr int EPV = 4;
+    __device__ __forceinline__ static void unpack(const uint4& v, float* o) {
+        o[0] = __uint_as_float(v.x); o[1] = __uint_as_float(v.y); o[2] = __uint_as_float(v.z); o[3] = __uint_as_float(v.w);
+    }
     __device__ __forceinline__ static void load_vec(const float* p, float* o) {
         float4 v = __ldg(reinterpret_cast<const float4*>(p));
         o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
@@ -65,9 +68,11 @@ template <> struct Elem<fp8_t> {
         float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
         o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
     }
-    __device__ __forceinline__ static void load_vec(const fp8_t* p, float* o) {
-        uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+    __device__ __forceinline__ static void unpack(const uint4& v, float* o) {
         unpack_word(v.x, o); unpack_word(v.y, o + 4); unpack_word(v.z, o + 8); unpack_word(v.w, o + 12);
+    }
+    __device__ __forceinline__ static void load_vec(const fp8_t* p, float* o) {
+        unpack(__ldg(reinterpret_cast<const uint4*>(p)), o);
     }
     __device__ __forceinline__ static float get(const fp8_t* p, size_t i) {
         __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(p[i].v), __NV_E4M3);
@@ -80,6 +85,13 @@ __device__ __forceinline__ float warp_sum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+
+// Programmatic dependent launch (PDL): every kernel of the step lets its successor start
+// launching at once and waits for its predecessor's results only where it first needs them, so
+// that launch latency and the weight fetch (which depends on nothing) overlap the predecessor.
+// Both instructions are no-ops for a kernel launched without the PDL attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------
 // Per-step control block shared by all kernels of a step
@@ -120,6 +132,8 @@ __device__ __forceinline__ void advance_seq(const StepCtl& c, int b, int sampled
 
 // Prefill chain has no LM head: a one-thread-per-sequence advance.
 static __global__ void advance_kernel(StepCtl c) {
+    pdl_launch_dependents();
+    pdl_wait();
     int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < c.B && seq_active(c, b)) advance_seq(c, b, -1);
 }
@@ -133,20 +147,30 @@ template <typename T, typename T2>
 __global__ void embed_kernel(StepCtl c, const T* __restrict__ E, const float* __restrict__ escale, int d,
                              const T2* __restrict__ pleT, const T2* __restrict__ pleP, int p,
                              float* __restrict__ x) {
+    pdl_launch_dependents();
+    pdl_wait();                      // pos / tok come from the last kernel of the previous step
     int b = blockIdx.x;
     if (!seq_active(c, b)) return;
     int t = c.tok[b];
-    extern __shared__ float trow[];
+    extern __shared__ __align__(16) float trow[];
     if (p > 0) {
         for (int j = threadIdx.x; j < p; j += blockDim.x) trow[j] = Elem<T2>::get(pleT, (size_t)t * p + j);
         __syncthreads();
     }
     float sc = escale ? escale[t] : 1.0f;
+    constexpr int EPV2 = Elem<T2>::EPV;
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = Elem<T>::get(E, (size_t)t * d + i) * sc;
         if (p > 0) {
+            // one row of the projection per thread, 16-byte loads (p is a multiple of 8)
             float a = 0.f;
-            for (int j = 0; j < p; ++j) a += Elem<T2>::get(pleP, (size_t)i * p + j) * trow[j];
+            const T2* prow = pleP + (size_t)i * p;
+            for (int j = 0; j < p; j += EPV2) {
+                float w[EPV2];
+                Elem<T2>::load_vec(prow + j, w);
+#pragma unroll
+                for (int e = 0; e < EPV2; ++e) a = fmaf(w[e], trow[j + e], a);
+            }
             v += a;
         }
         x[(size_t)b * d + i] = v;
@@ -200,95 +224,191 @@ struct GemvParams {
     int do_pick;                       // greedy pick + advance in the last CTA
 };
 
-template <typename T, int BT, int RW>
-__device__ __forceinline__ void warp_rows_dot(const T* __restrict__ W, int N, int K, int row0,
-                                              const float* __restrict__ xs, int xs_stride, int lane,
-                                              float (&acc)[RW][BT]) {
-    constexpr int EPV = Elem<T>::EPV;
-    const int nvec = K / EPV;
-    const T* wrow[RW];
+// Rows a warp streams per pass and 16-byte vectors per row it fetches BEFORE waiting for the
+// predecessor kernel: 2 rows x 4 vectors at batch tile 1 (latency), 4 rows x 2 otherwise.
+template <int BT> struct GemvShape {
+    static constexpr int RW = (BT == 1) ? 2 : 4;
+    static constexpr int PRE = (BT == 1) ? 4 : 2;
+};
+
+template <typename T, int RW>
+__device__ __forceinline__ void row_pointers(const T* __restrict__ W, int N, int K, int row0, const T* (&wrow)[RW]) {
 #pragma unroll
     for (int r = 0; r < RW; ++r) {
         int row = row0 + r;
         if (row > N - 1) row = N - 1;     // tail rows are computed on a duplicate and not stored
         wrow[r] = W + (size_t)row * K;
     }
+}
+
+template <typename T, int RW, int PRE>
+__device__ __forceinline__ void preload_rows(const T* const (&wrow)[RW], int nvec, int lane, uint4 (&pre)[RW][PRE]) {
+    constexpr int EPV = Elem<T>::EPV;
+#pragma unroll
+    for (int i = 0; i < PRE; ++i) {
+        const int v = lane + 32 * i;
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+            pre[r][i] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(wrow[r] + (size_t)v * EPV)) : make_uint4(0, 0, 0, 0);
+    }
+}
+
+template <typename T, int BT, int RW>
+__device__ __forceinline__ void fma_vec(const uint4 (&raw)[RW], const float* __restrict__ xs, int xs_stride, int v,
+                                        float (&acc)[RW][BT]) {
+    constexpr int EPV = Elem<T>::EPV;
+    float w[RW][EPV];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) Elem<T>::unpack(raw[r], w[r]);
+#pragma unroll
+    for (int b = 0; b < BT; ++b) {
+        const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)b * xs_stride + (size_t)v * EPV);
+        float xv[EPV];
+#pragma unroll
+        for (int q = 0; q < EPV / 4; ++q) {
+            float4 t = xp[q];
+            xv[4 * q] = t.x; xv[4 * q + 1] = t.y; xv[4 * q + 2] = t.z; xv[4 * q + 3] = t.w;
+        }
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) acc[r][b] = fmaf(w[r][e], xv[e], acc[r][b]);
+    }
+}
+
+// acc[r][b] += W[row r] . xs[b] over vectors [first_vec*32 + lane, nvec) of the rows
+template <typename T, int BT, int RW>
+__device__ __forceinline__ void warp_rows_dot(const T* const (&wrow)[RW], int nvec, int first_iter,
+                                              const float* __restrict__ xs, int xs_stride, int lane,
+                                              float (&acc)[RW][BT]) {
+    constexpr int EPV = Elem<T>::EPV;
 #pragma unroll 2
-    for (int v = lane; v < nvec; v += 32) {
-        float w[RW][EPV];
+    for (int v = lane + 32 * first_iter; v < nvec; v += 32) {
+        uint4 raw[RW];
 #pragma unroll
-        for (int r = 0; r < RW; ++r) Elem<T>::load_vec(wrow[r] + (size_t)v * EPV, w[r]);
+        for (int r = 0; r < RW; ++r) raw[r] = __ldg(reinterpret_cast<const uint4*>(wrow[r] + (size_t)v * EPV));
+        fma_vec<T, BT, RW>(raw, xs, xs_stride, v, acc);
+    }
+}
+
+template <typename T, int BT, int RW, int PRE>
+__device__ __forceinline__ void consume_preloaded(const uint4 (&pre)[RW][PRE], int nvec, const float* __restrict__ xs,
+                                                  int xs_stride, int lane, float (&acc)[RW][BT]) {
 #pragma unroll
-        for (int b = 0; b < BT; ++b) {
-            const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)b * xs_stride + (size_t)v * EPV);
-            float xv[EPV];
+    for (int i = 0; i < PRE; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+            uint4 raw[RW];
 #pragma unroll
-            for (int q = 0; q < EPV / 4; ++q) {
-                float4 t = xp[q];
-                xv[4 * q] = t.x; xv[4 * q + 1] = t.y; xv[4 * q + 2] = t.z; xv[4 * q + 3] = t.w;
-            }
-#pragma unroll
-            for (int r = 0; r < RW; ++r)
-#pragma unroll
-                for (int e = 0; e < EPV; ++e) acc[r][b] = fmaf(w[r][e], xv[e], acc[r][b]);
+            for (int r = 0; r < RW; ++r) raw[r] = pre[r][i];
+            fma_vec<T, BT, RW>(raw, xs, xs_stride, v, acc);
         }
     }
 }
 
 template <typename T, typename T2, typename KVT, int BT, int MODE>
 __global__ void __launch_bounds__(256) gemv_kernel(StepCtl c, GemvParams p) {
-    constexpr int RW = (MODE == GEMV_SWIGLU) ? 2 : 4;
+    constexpr int RWF = GemvShape<BT>::RW;                           // weight rows per warp pass
+    constexpr int RW = (MODE == GEMV_SWIGLU) ? RWF / 2 : RWF;        // output rows per warp pass
+    constexpr int PRE = GemvShape<BT>::PRE;
+    constexpr int EPV = Elem<T>::EPV;
     extern __shared__ __align__(16) float smem[];
     const int K = p.K, Kp = p.Kp, R = p.R;
     float* xs = smem;                                  // [BT][K]
     float* xs2 = xs + (size_t)BT * K;                  // [BT][Kp]
     float* outs = xs2 + (size_t)BT * Kp;               // [BT][R]
     float* rs = outs + (size_t)BT * R;                 // [BT]
+    float* red = rs + BT;                              // [8][BT]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const int b0 = blockIdx.y * BT;
     const int row0 = blockIdx.x * R;
+    const int nvec = K / EPV;
+    const T* W = reinterpret_cast<const T*>(p.W);
+    const T* Wb = reinterpret_cast<const T*>(p.Wb);
+
+    pdl_launch_dependents();
+    // ---- weights of the first pass: fetched before the predecessor's results are needed ---
+    const T* wrow[RW];
+    const T* wrow_b[RW];
+    uint4 pre[RW][PRE], pre_b[RW][PRE];
+    const bool first_pass = warp * RW < R;
+    if (first_pass) {
+        row_pointers<T, RW>(W, p.N, K, row0 + warp * RW, wrow);
+        preload_rows<T, RW, PRE>(wrow, nvec, lane, pre);
+        if (MODE == GEMV_SWIGLU) {
+            row_pointers<T, RW>(Wb, p.N, K, row0 + warp * RW, wrow_b);
+            preload_rows<T, RW, PRE>(wrow_b, nvec, lane, pre_b);
+        }
+    }
+    pdl_wait();
 
     // ---- prologue: stage (and RMS-normalise) the activations of the tile -------------
     // Reference: getRMSColSums + applyRMSNorm, inference.cu:24-50, :83-95 -
     // r = sqrt(mean(x^2) + eps); x / r, then times the gain.
-    for (int b = warp; b < BT; b += nw) {
-        int bg = min(b0 + b, c.B - 1);
-        const float* xr = p.xin + (size_t)bg * K;
-        float ss = 0.f;
-        for (int k = lane; k < K; k += 32) {
-            float v = xr[k];
-            xs[(size_t)b * K + k] = v;
-            ss = fmaf(v, v, ss);
+    {
+        float ss[BT];
+#pragma unroll
+        for (int b = 0; b < BT; ++b) {
+            const int bg = min(b0 + b, c.B - 1);
+            const float4* xr = reinterpret_cast<const float4*>(p.xin + (size_t)bg * K);
+            float4* xd = reinterpret_cast<float4*>(xs + (size_t)b * K);
+            float a = 0.f;
+            for (int k = tid; k < K / 4; k += blockDim.x) {
+                float4 v = xr[k];
+                xd[k] = v;
+                a = fmaf(v.x, v.x, a); a = fmaf(v.y, v.y, a); a = fmaf(v.z, v.z, a); a = fmaf(v.w, v.w, a);
+            }
+            ss[b] = a;
+            if (Kp > 0) {
+                const int t = c.tok[bg];
+                const T2* trow = reinterpret_cast<const T2*>(p.Ptab) + (size_t)t * Kp;
+                for (int k = tid; k < Kp; k += blockDim.x) xs2[(size_t)b * Kp + k] = Elem<T2>::get(trow, k);
+            }
         }
         if (p.do_norm) {
-            ss = warp_sum(ss);
-            float r = sqrtf(ss / (float)K + p.eps);
-            for (int k = lane; k < K; k += 32) xs[(size_t)b * K + k] = (xs[(size_t)b * K + k] / r) * p.gain[k];
-        }
-        if (Kp > 0) {
-            int t = c.tok[bg];
-            const T2* trow = reinterpret_cast<const T2*>(p.Ptab) + (size_t)t * Kp;
-            for (int k = lane; k < Kp; k += 32) xs2[(size_t)b * Kp + k] = Elem<T2>::get(trow, k);
+#pragma unroll
+            for (int b = 0; b < BT; ++b) {
+                float a = warp_sum(ss[b]);
+                if (lane == 0) red[warp * BT + b] = a;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int b = 0; b < BT; ++b) {
+                float tot = 0.f;
+                for (int w = 0; w < nw; ++w) tot += red[w * BT + b];
+                const float r = sqrtf(tot / (float)K + p.eps);
+                float4* xd = reinterpret_cast<float4*>(xs + (size_t)b * K);
+                const float4* gp = reinterpret_cast<const float4*>(p.gain);
+                for (int k = tid; k < K / 4; k += blockDim.x) {
+                    float4 v = xd[k], g = gp[k];
+                    v.x = (v.x / r) * g.x; v.y = (v.y / r) * g.y; v.z = (v.z / r) * g.z; v.w = (v.w / r) * g.w;
+                    xd[k] = v;
+                }
+            }
         }
     }
     __syncthreads();
 
-    // ---- main loop: RW rows per warp pass ---------------------------------------------
-    const T* W = reinterpret_cast<const T*>(p.W);
+    // ---- main loop: RW output rows per warp pass ---------------------------------------
     for (int rb = warp * RW; rb < R; rb += nw * RW) {
+        const bool pre_ok = rb == warp * RW;            // the first pass has its first vectors in registers
         float acc[RW][BT];
 #pragma unroll
         for (int r = 0; r < RW; ++r)
 #pragma unroll
             for (int b = 0; b < BT; ++b) acc[r][b] = 0.f;
-        warp_rows_dot<T, BT, RW>(W, p.N, K, row0 + rb, xs, K, lane, acc);
+        if (!pre_ok) row_pointers<T, RW>(W, p.N, K, row0 + rb, wrow);
+        if (pre_ok) consume_preloaded<T, BT, RW, PRE>(pre, nvec, xs, K, lane, acc);
+        warp_rows_dot<T, BT, RW>(wrow, nvec, pre_ok ? PRE : 0, xs, K, lane, acc);
         if (MODE == GEMV_SWIGLU) {
             float accb[RW][BT];
 #pragma unroll
             for (int r = 0; r < RW; ++r)
 #pragma unroll
                 for (int b = 0; b < BT; ++b) accb[r][b] = 0.f;
-            warp_rows_dot<T, BT, RW>(reinterpret_cast<const T*>(p.Wb), p.N, K, row0 + rb, xs, K, lane, accb);
+            if (!pre_ok) row_pointers<T, RW>(Wb, p.N, K, row0 + rb, wrow_b);
+            if (pre_ok) consume_preloaded<T, BT, RW, PRE>(pre_b, nvec, xs, K, lane, accb);
+            warp_rows_dot<T, BT, RW>(wrow_b, nvec, pre_ok ? PRE : 0, xs, K, lane, accb);
 #pragma unroll
             for (int r = 0; r < RW; ++r) {
                 int row = min(row0 + rb + r, p.N - 1);
@@ -308,7 +428,9 @@ __global__ void __launch_bounds__(256) gemv_kernel(StepCtl c, GemvParams p) {
                 for (int r = 0; r < RW; ++r)
 #pragma unroll
                     for (int b = 0; b < BT; ++b) acc2[r][b] = 0.f;
-                warp_rows_dot<T2, BT, RW>(reinterpret_cast<const T2*>(p.P), p.N, Kp, row0 + rb, xs2, Kp, lane, acc2);
+                const T2* prow[RW];
+                row_pointers<T2, RW>(reinterpret_cast<const T2*>(p.P), p.N, Kp, row0 + rb, prow);
+                warp_rows_dot<T2, BT, RW>(prow, Kp / Elem<T2>::EPV, 0, xs2, Kp, lane, acc2);
 #pragma unroll
                 for (int r = 0; r < RW; ++r) {
                     int row = min(row0 + rb + r, p.N - 1);
@@ -498,6 +620,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     constexpr int NW = 4;
     static_assert(LPR <= 32 && PPI >= 1, "head_dim too large for one warp row");
     const int b = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x, S = gridDim.x;
+    pdl_launch_dependents();
+    pdl_wait();                                    // q and this step's K/V row come from the projection kernel
     if (!seq_active(c, b)) return;                 // uniform for all CTAs of this sequence
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lr = lane % LPR, grp = lane / LPR;
@@ -660,8 +784,25 @@ __global__ void __launch_bounds__(256) delta_net_kernel(StepCtl c, const float* 
     constexpr int EPL = DK / 32;
     constexpr int ROWS_PER_WARP = 4;
     const int b = blockIdx.z, h = blockIdx.y;
-    if (!seq_active(c, b)) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();
+    // The state rows do not depend on this step's projections: fetch them before waiting.
+    const int row0 = blockIdx.x * (8 * ROWS_PER_WARP) + warp * ROWS_PER_WARP;
+    float* Sh = state + ((size_t)b * H + h) * (size_t)dv * DK;
+    float s[ROWS_PER_WARP][EPL];
+#pragma unroll
+    for (int i = 0; i < ROWS_PER_WARP; ++i) {
+        int row = row0 + i;
+        if (row < dv) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) s[i][e] = __ldcg(&Sh[(size_t)row * DK + lane * EPL + e]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) s[i][e] = 0.f;
+        }
+    }
+    pdl_wait();
+    if (!seq_active(c, b)) return;
     __shared__ float sq[DK], sk[DK];
     __shared__ float sgate[2];
     const float* r = raw + (size_t)b * raw_stride;
@@ -687,20 +828,6 @@ __global__ void __launch_bounds__(256) delta_net_kernel(StepCtl c, const float* 
     float qn[EPL], kn[EPL];
 #pragma unroll
     for (int e = 0; e < EPL; ++e) { qn[e] = sq[lane * EPL + e]; kn[e] = sk[lane * EPL + e]; }
-    const int row0 = blockIdx.x * (8 * ROWS_PER_WARP) + warp * ROWS_PER_WARP;
-    float* Sh = state + ((size_t)b * H + h) * (size_t)dv * DK;
-    float s[ROWS_PER_WARP][EPL];
-#pragma unroll
-    for (int i = 0; i < ROWS_PER_WARP; ++i) {
-        int row = row0 + i;
-        if (row < dv) {
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) s[i][e] = Sh[(size_t)row * DK + lane * EPL + e];
-        } else {
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) s[i][e] = 0.f;
-        }
-    }
 #pragma unroll
     for (int i = 0; i < ROWS_PER_WARP; ++i) {
         int row = row0 + i;
@@ -757,6 +884,8 @@ constexpr int kSampleCap = 1024;       // max candidates kept in shared memory
 
 static __global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, SampleParams p) {
     const int b = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     if (!seq_active(c, b)) return;
     const int tid = threadIdx.x;
     const float* lg = p.logits + (size_t)b * p.V;
