@@ -13,6 +13,7 @@
 #include "../../include/mlb.h"
 #include "errors.h"
 #include "kernels.cuh"
+#include "mega.cuh"
 #include "model_file.h"
 
 namespace mlb {
@@ -379,6 +380,14 @@ struct mlb_session {
     float4* flush_buf = nullptr; size_t flush_n = 0;
     int* pinned_tok = nullptr;
     bool use_pdl = true;
+    // cluster-per-sequence single-kernel step (small batch)
+    bool use_cluster = false;
+    int cluster_size = 0;
+    size_t mega_smem = 0;
+    mlb::MegaLayer* mega_layers = nullptr;
+    mlb::MegaParams mega;
+    int* dev_err = nullptr;                 // set by a kernel whose bounded wait ran out
+    int* pinned_err = nullptr;
 };
 
 namespace mlb {
@@ -391,6 +400,22 @@ static int sess_alloc(mlb_session* s, void** p, size_t bytes, bool zero) {
     return MLB_OK;
 }
 
+// Queue the read-back of the device error word; call before the stream synchronisation.
+static int queue_err_readback(mlb_session* s) {
+    CU(cudaMemcpyAsync(s->pinned_err, s->dev_err, 4, cudaMemcpyDeviceToHost, s->stream));
+    return MLB_OK;
+}
+// After the synchronisation: a bounded device-side wait ran out somewhere in the step.
+static int check_err_readback(mlb_session* s) {
+    if (*s->pinned_err == 0) return MLB_OK;
+    const int code = *s->pinned_err;
+    *s->pinned_err = 0;
+    cudaMemsetAsync(s->dev_err, 0, 4, s->stream);
+    cudaStreamSynchronize(s->stream);
+    return fail(MLB_E_TIMEOUT, "a bounded device-side wait ran out (code %d: %s); the results of this call are invalid", code,
+                code == 1 ? "producer waiting for a free ring stage" : "consumer waiting for a weight chunk");
+}
+
 static void free_session(mlb_session* s) {
     if (!s) return;
     cudaSetDevice(s->m->device);
@@ -398,6 +423,7 @@ static void free_session(mlb_session* s) {
     for (auto& g : s->graphs) if (g) cudaGraphExecDestroy(g);
     for (void* p : s->allocs) cudaFree(p);
     if (s->pinned_tok) cudaFreeHost(s->pinned_tok);
+    if (s->pinned_err) cudaFreeHost(s->pinned_err);
     if (s->stream) cudaStreamDestroy(s->stream);
     delete s;
 }
@@ -507,6 +533,74 @@ struct Chain {
         return MLB_OK;
     }
 
+    // One decode (or prefill) step as a single cluster kernel (plus the sampler for top-k).
+    static int run_cluster(mlb_session* s, int kind, const StepCtl& c, Recorder* rec, int* n_launches) {
+        MegaParams mp = s->mega;
+        mp.with_lm_head = kind == CHAIN_PREFILL ? 0 : 1;
+        mp.do_pick = kind == CHAIN_GREEDY ? 1 : 0;
+        int rc, launches = 0;
+        if (rec) {
+            uint64_t w, kv, st, rows;
+            mlb_session_step_bytes(s, &w, &kv, &st, &rows);
+            if ((rc = rec->begin("cluster_decode_step", (uint64_t)s->B * w + kv + st + rows, 0))) return rc;
+        }
+        cudaLaunchConfig_t cfg;
+        std::memset(&cfg, 0, sizeof cfg);
+        cfg.gridDim = dim3(s->cluster_size, s->B);
+        cfg.blockDim = dim3(kMegaThreads);
+        cfg.dynamicSmemBytes = s->mega_smem;
+        cfg.stream = s->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = s->cluster_size;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        CU(cudaLaunchKernelEx(&cfg, mega_decode_kernel<T, T2, KVT>, c, mp));
+        if (rec && (rc = rec->end())) return rc;
+        ++launches;
+        if (kind == CHAIN_TOPK) {
+            SampleParams sp;
+            sp.logits = s->logits; sp.V = s->m->cfg.vocab; sp.top_k = s->cur_topk; sp.temperature = s->cur_temp; sp.seeds = s->seeds;
+            if (rec && (rc = rec->begin("sample_topk_philox", (uint64_t)s->B * s->m->cfg.vocab * 4 * 5, 0))) return rc;
+            CU(launch_chain(false, sample_topk_kernel, dim3(s->B), dim3(256), 0, s->stream, c, sp));
+            if (rec && (rc = rec->end())) return rc;
+            ++launches;
+        }
+        if (n_launches) *n_launches = launches;
+        return MLB_OK;
+    }
+
+    // Shared-memory need and occupancy of the cluster kernel; 0 clusters = not usable here.
+    static int cluster_probe(int cluster_size, size_t smem, int batch, int* max_clusters) {
+        *max_clusters = 0;
+        if (cudaFuncSetAttribute(mega_decode_kernel<T, T2, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(mega_decode_kernel<T, T2, KVT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+            cudaGetLastError();
+            return MLB_OK;
+        }
+        cudaLaunchConfig_t cfg;
+        std::memset(&cfg, 0, sizeof cfg);
+        cfg.gridDim = dim3(cluster_size, batch);
+        cfg.blockDim = dim3(kMegaThreads);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = cluster_size;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, mega_decode_kernel<T, T2, KVT>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        *max_clusters = n;
+        return MLB_OK;
+    }
+
     // One decode (or prefill) step as a chain of launches on the session's stream.
     static int run(mlb_session* s, int kind, Recorder* rec, int* n_launches) {
         const mlb_model* m = s->m;
@@ -514,6 +608,7 @@ struct Chain {
         const StepCtl c = make_ctl(s, kind);
         const int d = cfg.dim, F = cfg.ffn_dim, B = s->B, p = cfg.ple_dim;
         int launches = 0, rc;
+        if (s->use_cluster) return run_cluster(s, kind, c, rec, n_launches);
 
         if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * (d * sizeof(T) + (uint64_t)p * sizeof(T2) + (uint64_t)d * 4) + (uint64_t)d * p * sizeof(T2), 0))) return rc;
         CU(launch_chain(s->use_pdl, embed_kernel<T, T2>, dim3(B), dim3(256), (size_t)p * 4, s->stream, c,
@@ -635,6 +730,101 @@ static int chain_configure(mlb_session* s) {
     if (w == MLB_DT_BF16 && k == MLB_DT_BF16) return Chain<bf16_t, bf16_t, bf16_t>::configure();
     if (w == MLB_DT_FP8_E4M3 && k == MLB_DT_F32) return Chain<fp8_t, bf16_t, float>::configure();
     return Chain<fp8_t, bf16_t, bf16_t>::configure();
+}
+
+static int chain_cluster_probe(mlb_session* s, int cluster_size, size_t smem, int* max_clusters) {
+    const int w = s->m->cfg.weight_dtype, k = s->m->cfg.kv_dtype;
+    if (w == MLB_DT_F32 && k == MLB_DT_F32) return Chain<float, float, float>::cluster_probe(cluster_size, smem, s->B, max_clusters);
+    if (w == MLB_DT_F32 && k == MLB_DT_BF16) return Chain<float, float, bf16_t>::cluster_probe(cluster_size, smem, s->B, max_clusters);
+    if (w == MLB_DT_BF16 && k == MLB_DT_F32) return Chain<bf16_t, bf16_t, float>::cluster_probe(cluster_size, smem, s->B, max_clusters);
+    if (w == MLB_DT_BF16 && k == MLB_DT_BF16) return Chain<bf16_t, bf16_t, bf16_t>::cluster_probe(cluster_size, smem, s->B, max_clusters);
+    if (w == MLB_DT_FP8_E4M3 && k == MLB_DT_F32) return Chain<fp8_t, bf16_t, float>::cluster_probe(cluster_size, smem, s->B, max_clusters);
+    return Chain<fp8_t, bf16_t, bf16_t>::cluster_probe(cluster_size, smem, s->B, max_clusters);
+}
+
+// Decides whether the single-kernel cluster step serves this session and lays out its shared
+// memory. MLB_DECODE_PATH = chain | cluster | auto. The cluster step is opt-in: one cluster
+// lives in one GPC and is held to that GPC's share of the L2 bandwidth, which on B200 makes it
+// slower than the kernel chain (293 vs 180 us per token on the 1-GPU latency configuration).
+static int setup_cluster_path(mlb_session* s) {
+    const mlb_config& c = s->m->cfg;
+    const char* env = std::getenv("MLB_DECODE_PATH");
+    const std::string mode = env ? env : "auto";
+    s->use_cluster = false;
+    if (mode != "cluster") return MLB_OK;
+    auto up4 = [](int v) { return (v + 3) / 4 * 4; };
+    for (int C : {16, 8}) {
+        MegaParams mp;
+        std::memset(&mp, 0, sizeof mp);
+        const int S = std::max(1, C / c.kv_heads);
+        int n_proj = s->raw_stride;
+        for (const DevLayer& L : s->m->layers) n_proj = std::max(n_proj, L.n_qkv);
+        const int a_dim = std::max(c.heads * c.head_dim, c.heads * c.dn_value_dim);
+        const int tmp_n = std::max(std::max(c.head_dim, kMegaAttnWarps * (c.head_dim + 2)),
+                                   std::max(2 * c.heads * c.dn_key_dim + 2 * c.heads, 64));
+        int off = 0;
+        mp.off_x = off; off += up4(c.dim);
+        mp.off_xn = off; off += up4(c.dim);
+        mp.off_proj = off; off += up4(n_proj);
+        mp.off_parts = off; off += up4(c.heads * S * (c.head_dim + 2));
+        mp.off_a = off; off += up4(a_dim);
+        mp.off_h = off; off += up4(c.ffn_dim);
+        mp.off_tmp = off; off += up4(tmp_n);
+        mp.off_ple = off; off += up4(std::max(c.ple_dim, 4));
+        mp.off_pacc = off; off += up4(c.dim / 8 + 8);
+        mp.off_red = off; off += 32;
+        mp.off_lm = off; off += up4(2 * C);
+        off = (off + 31) / 32 * 32;
+        const int max_stages = 8;
+        mp.off_bar = off; off += max_stages * 2 * 2;              // 8-byte barriers: full[] then empty[]
+        off = (off + 31) / 32 * 32;
+        mp.off_ring = off;
+        // ring: 32 KB stages (whole rows), as many as fit below ~208 KB of shared memory
+        mp.stage_bytes = 32 * 1024;
+        const size_t fixed = (size_t)off * 4;
+        if (fixed + 3 * (size_t)mp.stage_bytes > 208 * 1024) continue;
+        mp.n_stages = (int)std::min<size_t>(max_stages, (208 * 1024 - fixed) / mp.stage_bytes);
+        {
+            // every row that is streamed must fit one stage
+            size_t widest = (size_t)std::max(std::max(c.dim, c.ffn_dim), std::max(c.heads * c.head_dim, c.heads * c.dn_value_dim)) *
+                            elt_size(c.weight_dtype);
+            if (widest > (size_t)mp.stage_bytes) continue;
+        }
+        const size_t smem = fixed + (size_t)mp.n_stages * mp.stage_bytes;
+        int max_clusters = 0;
+        int rc = chain_cluster_probe(s, C, smem, &max_clusters);
+        if (rc) return rc;
+        if (max_clusters < 1) continue;
+        // device copy of the per-layer pointer table
+        std::vector<MegaLayer> hl(c.layers);
+        for (int i = 0; i < c.layers; ++i) {
+            const DevLayer& L = s->m->layers[i];
+            MegaLayer& M = hl[i];
+            std::memset(&M, 0, sizeof M);
+            M.type = L.type; M.n_qkv = L.n_qkv; M.nq = L.nq; M.nk = L.nk; M.nv = L.nv; M.ng = L.ng; M.o_in = L.o_in;
+            M.Wqkv = L.Wqkv; M.Sqkv = L.Sqkv; M.g1 = L.g1; M.g2 = L.g2; M.gq = L.gq; M.gk = L.gk;
+            M.Wo = L.Wo; M.So = L.So; M.W1a = L.W1a; M.W1b = L.W1b; M.W2 = L.W2; M.S1a = L.S1a; M.S1b = L.S1b; M.S2 = L.S2;
+            M.pleT = L.pleT; M.pleP = L.pleP; M.kpool = s->kpool[i]; M.vpool = s->vpool[i]; M.state = s->state[i];
+        }
+        int rc2 = sess_alloc(s, (void**)&s->mega_layers, hl.size() * sizeof(MegaLayer), false);
+        if (rc2) return rc2;
+        CU(cudaMemcpy(s->mega_layers, hl.data(), hl.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+        mp.layers = s->mega_layers; mp.n_layers = c.layers;
+        mp.d = c.dim; mp.F = c.ffn_dim; mp.V = c.vocab; mp.heads = c.heads; mp.kv_heads = c.kv_heads; mp.hd = c.head_dim;
+        mp.dk = c.dn_key_dim; mp.dv = c.dn_value_dim; mp.ple = c.ple_dim; mp.qk_norm = c.qk_norm;
+        mp.eps = c.rms_eps; mp.l2_eps = 1e-6f;
+        mp.E = s->m->E; mp.Es = s->m->Es; mp.g_final = s->m->g_final; mp.rope = s->m->rope;
+        mp.page_table = s->page_table; mp.pt_stride = s->max_pages; mp.logits = s->logits;
+        mp.attn_splits = S;
+        mp.err = s->dev_err;
+        s->mega = mp;
+        s->cluster_size = C;
+        s->mega_smem = smem;
+        s->use_cluster = true;
+        return MLB_OK;
+    }
+    if (mode == "cluster") return fail(MLB_E_UNSUPPORTED, "MLB_DECODE_PATH=cluster: no cluster configuration fits this model on this device");
+    return MLB_OK;
 }
 
 // Capture the chain once per kind; sampling parameters are baked into the top-k graph.
@@ -772,6 +962,8 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     s->flush_n = (192ull << 20) / 16;
     SA(sess_alloc(s, (void**)&s->flush_buf, s->flush_n * 16, false));
     SCU(cudaMallocHost((void**)&s->pinned_tok, B * 4));
+    SCU(cudaMallocHost((void**)&s->pinned_err, 4));
+    *s->pinned_err = 0;
     s->alloc.num_pages = s->kv_pages;
     s->alloc.max_pages_per_seq = s->max_pages;
     s->alloc.seq_pages.assign(batch, {});
@@ -784,7 +976,9 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
         const char* e = std::getenv("MLB_NO_PDL");     // measurement switch: plain stream-ordered launches
         s->use_pdl = !(e && e[0] == '1');
     }
+    SA(sess_alloc(s, (void**)&s->dev_err, 4, true));
     SA(chain_configure(s));
+    SA(setup_cluster_path(s));
 #undef SA
 #undef SCU
     *out = s;
@@ -858,9 +1052,10 @@ extern "C" int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t*
         if ((rc = ensure_graph(s, CHAIN_PREFILL))) return rc;
         for (int t = 0; t < max_len - 1; ++t) CU(cudaGraphLaunch(s->graphs[CHAIN_PREFILL], s->stream));
     }
+    if ((rc = queue_err_readback(s))) return rc;
     CU(cudaStreamSynchronize(s->stream));
     for (int b = 0; b < B; ++b) s->h_pos[b] = lens[b] - 1;
-    return MLB_OK;
+    return check_err_readback(s);
 }
 
 namespace mlb {
@@ -905,6 +1100,7 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
         if (step_ms) CU(cudaEventRecord(ev[2 * i + 1], s->stream));
     }
     // result: ring [B][max_ctx] -> out [B][n]
+    if ((rc = queue_err_readback(s))) return rc;
     if (n == 1) {
         // one id per sequence: gather through the pinned buffer
         CU(cudaMemcpy2DAsync(s->pinned_tok, 4, s->out_ring, (size_t)s->max_ctx * 4, 4, B, cudaMemcpyDeviceToHost, s->stream));
@@ -926,7 +1122,7 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
     }
     for (int b = 0; b < B; ++b) s->h_pos[b] = std::min(s->h_pos[b] + n, s->max_ctx);
     s->have_logits = true;
-    return MLB_OK;
+    return check_err_readback(s);
 }
 }  // namespace mlb
 

@@ -57,10 +57,13 @@ def tol_of(spec):
     return TOL_FP32 if spec.weight_dtype == "float32" and spec.kv_dtype == "float32" else TOL_LOWP
 
 
+@pytest.mark.parametrize("path_mode", ["cluster", "chain"])
 @pytest.mark.parametrize("name", list(SPECS))
-def test_greedy_rollout_matches_oracle(api, tmp_path, name):
+def test_greedy_rollout_matches_oracle(api, tmp_path, monkeypatch, name, path_mode):
     """Batch 1: 20-token prompt, 48 greedy tokens: identical ids, logits within tolerance at
-    every step (context crosses three KV pages)."""
+    every step (context crosses three KV pages). Run through both decode paths: the
+    single-kernel cluster step and the kernel chain."""
+    monkeypatch.setenv("MLB_DECODE_PATH", path_mode)
     spec = SPECS[name]
     path = write_model(tmp_path, spec, seed=3)
     oracle = load_oracle(path)
@@ -83,8 +86,12 @@ def test_greedy_rollout_matches_oracle(api, tmp_path, name):
     model.close()
 
 
-@pytest.mark.parametrize("name,batch", [("attn_fp32", 3), ("mixed_ple", 9), ("bf16", 5), ("gqa", 17)])
-def test_ragged_batch_matches_oracle(api, tmp_path, name, batch):
+@pytest.mark.parametrize("name,batch,path_mode", [("attn_fp32", 3, "cluster"), ("attn_fp32", 3, "chain"),
+                                                  ("mixed_ple", 9, "auto"), ("mixed_ple", 7, "cluster"),
+                                                  ("bf16", 5, "cluster"), ("bf16", 5, "chain"), ("gqa", 17, "auto"),
+                                                  ("fp8", 4, "cluster"), ("qknorm_gating", 8, "cluster")])
+def test_ragged_batch_matches_oracle(api, tmp_path, monkeypatch, name, batch, path_mode):
+    monkeypatch.setenv("MLB_DECODE_PATH", path_mode)
     """Ragged prompts (1 .. 37 tokens) in one batch, decode_n in one call: every sequence
     equals its own batch-1 oracle roll-out."""
     spec = SPECS[name]
@@ -296,8 +303,9 @@ def test_cfg1_latency_config_bf16(api, tmp_path):
     ms, _ = sess.decode_timed(4, True)
     assert (ms > 0).all()
     stats = sess.profile(2, False)
-    assert {s["name"] for s in stats} >= {"qkv_gemv_norm_rope_kvappend", "attn_flash_decode_paged",
-                                          "deltanet_state_update", "lmhead_gemv_norm_argmax"}
+    names = {s["name"] for s in stats}
+    assert names == {"cluster_decode_step"} or names >= {"qkv_gemv_norm_rope_kvappend", "attn_flash_decode_paged",
+                                                         "deltanet_state_update", "lmhead_gemv_norm_argmax"}
     sess.close()
     model.close()
 
