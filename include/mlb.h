@@ -165,6 +165,17 @@ int mlb_op_attn_decode(const void* kpool, const void* vpool, int kv_dtype, const
                        float* out, int batch, int heads, int kv_heads, int head_dim, int splits,
                        void* stream);
 
+/* Stand-alone batched projection on the tensor cores (tcgen05 + TMEM, TMA-fed), DEVICE pointers:
+ * the kernel that replaces the reference's cublasGemmEx projections (inference.cu:401-465,
+ * :581-602, :623-695, :720-743) once the batch is >= 16. W [N][K] bf16 row-major, X [batch][K]
+ * bf16; K a multiple of 8. Three forms, chosen by the optional pointers:
+ *   plain      out fp32 [batch][N] = X W^T
+ *   residual   out fp32 [batch][N] = X W^T + resid (resid may alias out)
+ *   gate/up    out bf16 [batch][N] = silu(X W^T) * (X W_up^T)
+ * Returns after the stream has finished. */
+int mlb_op_gemm_bf16(const void* W, const void* W_up_or_null, const void* X, const float* resid_or_null,
+                     void* out, int N, int K, int batch, void* stream);
+
 /* No counterpart in the reference. Same operator and arguments as mlb_op_attn_decode, for
  * callers that cannot allocate device memory: a server that has given all free device memory
  * to its own pool, or a token loop that must never run into the device-wide synchronisation

@@ -93,6 +93,7 @@ def lib() -> C.CDLL:
         "mlb_rope_table": (None, [f32p, C.c_int, C.c_int, C.c_float]),
         "mlb_op_attn_decode": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int,
                                          C.c_int, C.c_int, vp]),
+        "mlb_op_gemm_bf16": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
         "mlb_op_attn_decode_static": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int,
                                                 C.c_int, C.c_int, C.c_int, vp]),
         "mlb_op_attn_decode_static_capacity": (C.c_size_t, []),

@@ -8,11 +8,14 @@
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <type_traits>
 #include <vector>
 
 #include "../../include/mlb.h"
 #include "errors.h"
 #include "kernels.cuh"
+#include "gemm_tc.cuh"
+#include "tc_host.h"
 #include "mega.cuh"
 #include "model_file.h"
 
@@ -387,6 +390,14 @@ struct mlb_session {
     mlb::MegaLayer* mega_layers = nullptr;
     mlb::MegaParams mega;
     int* dev_err = nullptr;                 // set by a kernel whose bounded wait ran out
+    // tensor-core projections (bf16 weights, batch >= 16)
+    bool use_tc = false;
+    int tc_nb = 0, tc_stages = 0, tc_stages_swiglu = 0;
+    mlb::bf16_t *xn16 = nullptr, *a16 = nullptr, *h16 = nullptr;
+    float* rawq = nullptr;
+    struct alignas(64) TcLayerMaps { CUtensorMap qkv, o, w1a, w1b, w2; };
+    std::vector<TcLayerMaps> tc_maps;
+    struct alignas(64) TcGlobalMaps { CUtensorMap E, xn, a_attn, a_dn, h; } tc_g;
     int* pinned_err = nullptr;
 };
 
@@ -601,6 +612,135 @@ struct Chain {
         return MLB_OK;
     }
 
+    template <int MODE>
+    static int gemm_tc(mlb_session* s, const CUtensorMap& A, const CUtensorMap& A2, const CUtensorMap& Bm, int N, int K, float* y,
+                       const float* resid, bf16_t* h16, Recorder* rec, const char* name) {
+        GemmTcParams p;
+        p.N = N; p.K = K; p.B = s->B; p.Nb = s->tc_nb;
+        p.stages = MODE == TC_SWIGLU ? s->tc_stages_swiglu : s->tc_stages;
+        uint32_t cols = 32;
+        while (cols < (uint32_t)(MODE == TC_SWIGLU ? 2 : 1) * (uint32_t)s->tc_nb) cols <<= 1;
+        p.tmem_cols = cols;
+        p.y = y; p.resid = resid; p.h16 = h16; p.err = s->dev_err;
+        const size_t stage_bytes = (size_t)(MODE == TC_SWIGLU ? 2 : 1) * kTcM * 128 + (size_t)s->tc_nb * 128;
+        const size_t smem = (size_t)p.stages * stage_bytes + (2 * (size_t)p.stages + 1) * 8 + 16 + 1024;
+        dim3 grid((N + kTcM - 1) / kTcM, (s->B + s->tc_nb - 1) / s->tc_nb);
+        int rc;
+        if (rec && (rc = rec->begin(name, (uint64_t)N * K * 2 * (MODE == TC_SWIGLU ? 2 : 1) + (uint64_t)s->B * K * 2 + (uint64_t)s->B * N * 4,
+                                    2ull * N * K * s->B * (MODE == TC_SWIGLU ? 2 : 1))))
+            return rc;
+        cudaError_t e = launch_chain(s->use_pdl, gemm_tc_kernel<MODE>, grid, dim3(128), smem, s->stream, A, A2, Bm, p);
+        if (e != cudaSuccess) return fail(MLB_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
+        if (rec) return rec->end();
+        return MLB_OK;
+    }
+
+    // Large-batch step: projections as tcgen05 GEMMs on bf16 operands, small kernels in between.
+    static int run_tc(mlb_session* s, int kind, const StepCtl& c, Recorder* rec, int* n_launches) {
+        if (!std::is_same<T, bf16_t>::value) return fail(MLB_E_UNSUPPORTED, "tensor-core projections need bf16 weights");
+        const mlb_model* m = s->m;
+        const mlb_config& cfg = m->cfg;
+        const int d = cfg.dim, F = cfg.ffn_dim, B = s->B, ple = cfg.ple_dim;
+        int launches = 0, rc;
+        auto prep = [&](const float* gain, const void* pleT, const void* pleP, int p_dim) -> int {
+            int r2;
+            if (rec && (r2 = rec->begin("prep_norm_bf16", (uint64_t)B * d * 6 + (uint64_t)p_dim * d * 2, 0))) return r2;
+            cudaError_t e = launch_chain(s->use_pdl, prep_bf16_kernel<T2>, dim3(B), dim3(256), (size_t)(d + p_dim) * 4, s->stream, c, s->x,
+                                         d, gain, cfg.rms_eps, static_cast<const T2*>(pleT), static_cast<const T2*>(pleP), p_dim, s->xn16);
+            if (e != cudaSuccess) return fail(MLB_E_CUDA, "prep launch failed: %s", cudaGetErrorString(e));
+            if (rec && (r2 = rec->end())) return r2;
+            ++launches;
+            return MLB_OK;
+        };
+        if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * d * 6, 0))) return rc;
+        CU(launch_chain(s->use_pdl, embed_kernel<T, T2>, dim3(B), dim3(256), (size_t)ple * 4, s->stream, c, static_cast<const T*>(m->E),
+                        static_cast<const float*>(m->Es), d, static_cast<const T2*>(m->layers[0].pleT),
+                        static_cast<const T2*>(m->layers[0].pleP), ple, s->x));
+        if (rec && (rc = rec->end())) return rc;
+        ++launches;
+        for (int i = 0; i < cfg.layers; ++i) {
+            const DevLayer& L = m->layers[i];
+            const mlb_session::TcLayerMaps& M = s->tc_maps[i];
+            const bool ple_here = ple > 0 && i > 0;
+            if ((rc = prep(L.g1, ple_here ? L.pleT : nullptr, ple_here ? L.pleP : nullptr, ple_here ? ple : 0))) return rc;
+            if (L.type == MLB_LAYER_ATTENTION) {
+                if ((rc = gemm_tc<TC_RAW>(s, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, s->rawq, nullptr, nullptr, rec, "qkv_gemm_tcgen05"))) return rc;
+                ++launches;
+                QkvPostParams q;
+                q.raw = s->rawq; q.n_qkv = L.n_qkv; q.nq = L.nq; q.nk = L.nk; q.nv = L.nv; q.ng = L.ng; q.hd = cfg.head_dim;
+                q.kv_heads = cfg.kv_heads; q.qk_norm = cfg.qk_norm; q.eps = cfg.rms_eps; q.gq = L.gq; q.gk = L.gk; q.rope = m->rope;
+                q.kpool = s->kpool[i]; q.vpool = s->vpool[i]; q.page_table = s->page_table; q.pt_stride = s->max_pages;
+                q.qbuf = s->qbuf; q.gbuf = s->gbuf;
+                if (rec && (rc = rec->begin("qkv_post_norm_rope_kvappend", (uint64_t)B * L.n_qkv * 8, 0))) return rc;
+                CU(launch_chain(s->use_pdl, qkv_post_kernel<KVT>, dim3(L.n_qkv / cfg.head_dim, B), dim3(cfg.head_dim / 2), 0, s->stream, c, q));
+                if (rec && (rc = rec->end())) return rc;
+                ++launches;
+                AttnParams a;
+                a.kpool = s->kpool[i]; a.vpool = s->vpool[i];
+                a.page_table = s->page_table; a.pt_stride = s->max_pages;
+                a.qbuf = s->qbuf; a.gbuf = L.ng ? s->gbuf : nullptr; a.abuf = s->abuf; a.abuf16 = s->a16;
+                a.part = s->part; a.ticket = s->attn_ticket;
+                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads;
+                if (rec) {
+                    uint64_t kvb = 0, fl = 0;
+                    for (int b = 0; b < B; ++b) {
+                        if (s->h_pos[b] >= s->max_ctx) continue;
+                        kvb += 2ull * cfg.kv_heads * cfg.head_dim * sizeof(KVT) * (s->h_pos[b] + 1);
+                        fl += 4ull * cfg.heads * cfg.head_dim * (s->h_pos[b] + 1);
+                    }
+                    if ((rc = rec->begin("attn_flash_decode_paged", kvb, fl))) return rc;
+                }
+                const int G = cfg.heads / cfg.kv_heads;
+                if (cfg.head_dim == 64) rc = attn_g<64>(s, c, a, G); else rc = attn_g<128>(s, c, a, G);
+                if (rc) return rc;
+                if (rec && (rc = rec->end())) return rc;
+                ++launches;
+            } else {
+                if ((rc = gemm_tc<TC_RAW>(s, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, s->raw, nullptr, nullptr, rec, "deltanet_proj_gemm_tcgen05"))) return rc;
+                ++launches;
+                const int dk = cfg.dn_key_dim, dv = cfg.dn_value_dim, H = cfg.heads;
+                if (rec && (rc = rec->begin("deltanet_state_update", (uint64_t)B * 2ull * H * dk * dv * 4, (uint64_t)B * 6ull * H * dk * dv))) return rc;
+                dim3 grid((dv + 31) / 32, H, B);
+                if (dk == 64) CU(launch_chain(s->use_pdl, delta_net_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
+                else CU(launch_chain(s->use_pdl, delta_net_kernel<128>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
+                if (rec && (rc = rec->end())) return rc;
+                ++launches;
+            }
+            const CUtensorMap& amap = L.type == MLB_LAYER_ATTENTION ? s->tc_g.a_attn : s->tc_g.a_dn;
+            if ((rc = gemm_tc<TC_RESID>(s, M.o, M.o, amap, d, L.o_in, s->x, s->x, nullptr, rec, "oproj_gemm_tcgen05_residual"))) return rc;
+            ++launches;
+            if ((rc = prep(L.g2, nullptr, nullptr, 0))) return rc;
+            if ((rc = gemm_tc<TC_SWIGLU>(s, M.w1a, M.w1b, s->tc_g.xn, F, d, nullptr, nullptr, s->h16, rec, "ffn_gateup_gemm_tcgen05_swiglu"))) return rc;
+            ++launches;
+            if ((rc = gemm_tc<TC_RESID>(s, M.w2, M.w2, s->tc_g.h, d, F, s->x, s->x, nullptr, rec, "ffn_down_gemm_tcgen05_residual"))) return rc;
+            ++launches;
+        }
+        if (kind == CHAIN_PREFILL) {
+            if (rec && (rc = rec->begin("advance_prompt", (uint64_t)B * 12, 0))) return rc;
+            CU(launch_chain(s->use_pdl, advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s->stream, c));
+            if (rec && (rc = rec->end())) return rc;
+            ++launches;
+        } else {
+            if ((rc = prep(m->g_final, nullptr, nullptr, 0))) return rc;
+            if ((rc = gemm_tc<TC_RAW>(s, s->tc_g.E, s->tc_g.E, s->tc_g.xn, cfg.vocab, d, s->logits, nullptr, nullptr, rec, "lmhead_gemm_tcgen05"))) return rc;
+            ++launches;
+            if (kind == CHAIN_GREEDY) {
+                if (rec && (rc = rec->begin("argmax_pick", (uint64_t)B * cfg.vocab * 4, 0))) return rc;
+                CU(launch_chain(s->use_pdl, argmax_advance_kernel, dim3(B), dim3(256), 0, s->stream, c, static_cast<const float*>(s->logits), cfg.vocab));
+                if (rec && (rc = rec->end())) return rc;
+            } else {
+                SampleParams sp;
+                sp.logits = s->logits; sp.V = cfg.vocab; sp.top_k = s->cur_topk; sp.temperature = s->cur_temp; sp.seeds = s->seeds;
+                if (rec && (rc = rec->begin("sample_topk_philox", (uint64_t)B * cfg.vocab * 4 * 5, 0))) return rc;
+                CU(launch_chain(s->use_pdl, sample_topk_kernel, dim3(B), dim3(256), 0, s->stream, c, sp));
+                if (rec && (rc = rec->end())) return rc;
+            }
+            ++launches;
+        }
+        if (n_launches) *n_launches = launches;
+        return MLB_OK;
+    }
+
     // One decode (or prefill) step as a chain of launches on the session's stream.
     static int run(mlb_session* s, int kind, Recorder* rec, int* n_launches) {
         const mlb_model* m = s->m;
@@ -609,6 +749,7 @@ struct Chain {
         const int d = cfg.dim, F = cfg.ffn_dim, B = s->B, p = cfg.ple_dim;
         int launches = 0, rc;
         if (s->use_cluster) return run_cluster(s, kind, c, rec, n_launches);
+        if (s->use_tc) return run_tc(s, kind, c, rec, n_launches);
 
         if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * (d * sizeof(T) + (uint64_t)p * sizeof(T2) + (uint64_t)d * 4) + (uint64_t)d * p * sizeof(T2), 0))) return rc;
         CU(launch_chain(s->use_pdl, embed_kernel<T, T2>, dim3(B), dim3(256), (size_t)p * 4, s->stream, c,
@@ -636,7 +777,7 @@ struct Chain {
                 AttnParams a;
                 a.kpool = s->kpool[i]; a.vpool = s->vpool[i];
                 a.page_table = s->page_table; a.pt_stride = s->max_pages;
-                a.qbuf = s->qbuf; a.gbuf = L.ng ? s->gbuf : nullptr; a.abuf = s->abuf;
+                a.qbuf = s->qbuf; a.gbuf = L.ng ? s->gbuf : nullptr; a.abuf = s->abuf; a.abuf16 = nullptr;
                 a.part = s->part; a.ticket = s->attn_ticket;
                 a.heads = cfg.heads; a.kv_heads = cfg.kv_heads;
                 if (rec) {
@@ -660,8 +801,8 @@ struct Chain {
                 const int dk = cfg.dn_key_dim, dv = cfg.dn_value_dim, H = cfg.heads;
                 if (rec && (rc = rec->begin("deltanet_state_update", (uint64_t)B * 2ull * H * dk * dv * 4, (uint64_t)B * 6ull * H * dk * dv))) return rc;
                 dim3 grid((dv + 31) / 32, H, B);
-                if (dk == 64) CU(launch_chain(s->use_pdl, delta_net_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, 1e-6f));
-                else CU(launch_chain(s->use_pdl, delta_net_kernel<128>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, 1e-6f));
+                if (dk == 64) CU(launch_chain(s->use_pdl, delta_net_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, static_cast<bf16_t*>(nullptr), 1e-6f));
+                else CU(launch_chain(s->use_pdl, delta_net_kernel<128>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, static_cast<bf16_t*>(nullptr), 1e-6f));
                 if (rec && (rc = rec->end())) return rc;
                 ++launches;
             }
@@ -827,6 +968,59 @@ static int setup_cluster_path(mlb_session* s) {
     return MLB_OK;
 }
 
+// Tensor-core projections for large batches: bf16 weights, batch >= 16 (MLB_GEMM=simt turns it off).
+static int setup_tc_path(mlb_session* s) {
+    const mlb_config& c = s->m->cfg;
+    s->use_tc = false;
+    const char* env = std::getenv("MLB_GEMM");
+    const std::string mode = env ? env : "auto";
+    if (mode == "simt" || s->use_cluster) return MLB_OK;
+    if (c.weight_dtype != MLB_DT_BF16) {
+        if (mode == "tc") return fail(MLB_E_UNSUPPORTED, "MLB_GEMM=tc needs bf16 weights");
+        return MLB_OK;
+    }
+    if (mode == "auto" && s->B < 16) return MLB_OK;
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) {
+        if (mode == "tc") return fail(MLB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        return MLB_OK;
+    }
+    const int B = s->B;
+    s->tc_nb = std::min(256, (B + 15) / 16 * 16);
+    const size_t budget = 200 * 1024;
+    s->tc_stages = (int)std::max<size_t>(2, std::min<size_t>(6, budget / ((size_t)kTcM * 128 + (size_t)s->tc_nb * 128)));
+    s->tc_stages_swiglu = (int)std::max<size_t>(2, std::min<size_t>(6, budget / ((size_t)2 * kTcM * 128 + (size_t)s->tc_nb * 128)));
+    const int nq = c.heads * c.head_dim, a_dn = c.heads * c.dn_value_dim;
+    int n_proj = 16;
+    for (const DevLayer& L : s->m->layers) n_proj = std::max(n_proj, L.n_qkv);
+    int rc;
+    if ((rc = sess_alloc(s, (void**)&s->xn16, (size_t)B * c.dim * 2, true))) return rc;
+    if ((rc = sess_alloc(s, (void**)&s->a16, (size_t)B * std::max(nq, a_dn) * 2, true))) return rc;
+    if ((rc = sess_alloc(s, (void**)&s->h16, (size_t)B * c.ffn_dim * 2, true))) return rc;
+    if ((rc = sess_alloc(s, (void**)&s->rawq, (size_t)B * n_proj * 4, true))) return rc;
+    s->tc_maps.resize(c.layers);
+    for (int i = 0; i < c.layers; ++i) {
+        const DevLayer& L = s->m->layers[i];
+        auto& M = s->tc_maps[i];
+        if ((rc = make_bf16_map(enc, &M.qkv, L.Wqkv, L.n_qkv, c.dim, kTcM))) return rc;
+        if ((rc = make_bf16_map(enc, &M.o, L.Wo, c.dim, L.o_in, kTcM))) return rc;
+        if ((rc = make_bf16_map(enc, &M.w1a, L.W1a, c.ffn_dim, c.dim, kTcM))) return rc;
+        if ((rc = make_bf16_map(enc, &M.w1b, L.W1b, c.ffn_dim, c.dim, kTcM))) return rc;
+        if ((rc = make_bf16_map(enc, &M.w2, L.W2, c.dim, c.ffn_dim, kTcM))) return rc;
+    }
+    if ((rc = make_bf16_map(enc, &s->tc_g.E, s->m->E, c.vocab, c.dim, kTcM))) return rc;
+    if ((rc = make_bf16_map(enc, &s->tc_g.xn, s->xn16, B, c.dim, s->tc_nb))) return rc;
+    if ((rc = make_bf16_map(enc, &s->tc_g.a_attn, s->a16, B, nq, s->tc_nb))) return rc;
+    if ((rc = make_bf16_map(enc, &s->tc_g.a_dn, s->a16, B, a_dn, s->tc_nb))) return rc;
+    if ((rc = make_bf16_map(enc, &s->tc_g.h, s->h16, B, c.ffn_dim, s->tc_nb))) return rc;
+    const int big = 227 * 1024;
+    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    s->use_tc = true;
+    return MLB_OK;
+}
+
 // Capture the chain once per kind; sampling parameters are baked into the top-k graph.
 static int ensure_graph(mlb_session* s, int kind) {
     if (kind == CHAIN_TOPK && s->graphs[kind] && (s->g_topk != s->cur_topk || s->g_temp != s->cur_temp)) {
@@ -979,6 +1173,7 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     SA(sess_alloc(s, (void**)&s->dev_err, 4, true));
     SA(chain_configure(s));
     SA(setup_cluster_path(s));
+    SA(setup_tc_path(s));
 #undef SA
 #undef SCU
     *out = s;

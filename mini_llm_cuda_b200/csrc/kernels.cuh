@@ -607,6 +607,7 @@ struct AttnParams {
     const float* qbuf;      // [B][heads*hd]
     const float* gbuf;      // [B][heads*hd] sigmoid gates or null
     float* abuf;            // [B][heads*hd]
+    bf16_t* abuf16;         // same values as the bf16 operand of a tensor-core O projection, or null
     float* part;            // [B][heads][splits][hd+2]
     int* ticket;            // [B*kv_heads]
     int heads, kv_heads;
@@ -732,6 +733,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
             float o = at / lt;
             if (p.gbuf) o *= p.gbuf[((size_t)b * p.heads + h) * HD + e];
             p.abuf[((size_t)b * p.heads + h) * HD + e] = o;
+            if (p.abuf16) p.abuf16[((size_t)b * p.heads + h) * HD + e] = __float2bfloat16_rn(o);
         } else {
             float* pp = p.part + (((size_t)b * p.heads + h) * S + split) * (HD + 2);
             pp[e] = at;
@@ -763,6 +765,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
         float o = at / lt;
         if (p.gbuf) o *= p.gbuf[((size_t)b * p.heads + h) * HD + e];
         p.abuf[((size_t)b * p.heads + h) * HD + e] = o;
+        if (p.abuf16) p.abuf16[((size_t)b * p.heads + h) * HD + e] = __float2bfloat16_rn(o);
     }
     if (tid == 0) p.ticket[b * p.kv_heads + kvh] = 0;
 }
@@ -780,7 +783,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
 template <int DK>
 __global__ void __launch_bounds__(256) delta_net_kernel(StepCtl c, const float* __restrict__ raw, int raw_stride,
                                                         float* __restrict__ state, int H, int dv,
-                                                        float* __restrict__ abuf, float l2_eps) {
+                                                        float* __restrict__ abuf, bf16_t* __restrict__ abuf16, float l2_eps) {
     constexpr int EPL = DK / 32;
     constexpr int ROWS_PER_WARP = 4;
     const int b = blockIdx.z, h = blockIdx.y;
@@ -844,7 +847,10 @@ __global__ void __launch_bounds__(256) delta_net_kernel(StepCtl c, const float* 
         if (row < dv) {
 #pragma unroll
             for (int e = 0; e < EPL; ++e) Sh[(size_t)row * DK + lane * EPL + e] = s[i][e];
-            if (lane == 0) abuf[((size_t)b * H + h) * dv + row] = d2;
+            if (lane == 0) {
+                abuf[((size_t)b * H + h) * dv + row] = d2;
+                if (abuf16) abuf16[((size_t)b * H + h) * dv + row] = __float2bfloat16_rn(d2);
+            }
         }
     }
 }

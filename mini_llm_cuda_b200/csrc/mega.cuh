@@ -717,7 +717,8 @@ template <typename T, typename T2, typename KVT>
 __global__ void __launch_bounds__(kMegaThreads, 1) mega_decode_kernel(StepCtl c, MegaParams p) {
     const int b = blockIdx.y;
     if (!seq_active(c, b)) return;                    // the whole cluster serves sequence b: uniform
-    extern __shared__ __align__(128) float smem[];
+    extern __shared__ __align__(128) float mega_smem[];
+    float* smem = mega_smem;
     MegaCtx k;
     k.C = (int)cluster_nctarank();
     k.rank = (int)cluster_ctarank();

@@ -5,6 +5,7 @@
 #include "../../include/mlb.h"
 #include "errors.h"
 #include "kernels.cuh"
+#include "tc_host.h"
 
 using namespace mlb;
 
@@ -77,7 +78,7 @@ int run_attn(void* scratch, const void* kpool, const void* vpool, int kv_dtype, 
     c.prompt = nullptr; c.prompt_stride = 0; c.out_ring = nullptr; c.out_idx = nullptr; c.out_cap = 0;
     AttnParams p;
     p.kpool = kpool; p.vpool = vpool; p.page_table = page_table; p.pt_stride = pt_stride;
-    p.qbuf = q; p.gbuf = gate; p.abuf = out; p.part = sc.part; p.ticket = sc.ticket;
+    p.qbuf = q; p.gbuf = gate; p.abuf = out; p.abuf16 = nullptr; p.part = sc.part; p.ticket = sc.ticket;
     p.heads = heads; p.kv_heads = kv_heads;
     const int G = heads / kv_heads;
     cudaError_t e;
@@ -106,6 +107,56 @@ extern "C" int mlb_op_attn_decode(const void* kpool, const void* vpool, int kv_d
     cudaFree(scratch);
     if (rc) return rc;
     if (se != cudaSuccess) return fail(MLB_E_CUDA, "attention op failed: %s", cudaGetErrorString(se));
+    return MLB_OK;
+}
+
+extern "C" int mlb_op_gemm_bf16(const void* W, const void* W_up_or_null, const void* X, const float* resid_or_null, void* out, int N,
+                                int K, int batch, void* stream) {
+    if (!W || !X || !out) return fail(MLB_E_INVALID, "gemm op: null pointer");
+    if (N < 1 || K < 8 || K % 8 || batch < 1) return fail(MLB_E_INVALID, "gemm op: N >= 1, K a multiple of 8, batch >= 1");
+    if (W_up_or_null && resid_or_null) return fail(MLB_E_INVALID, "gemm op: gate/up and residual are exclusive");
+    EncodeTiledFn enc = get_encode_tiled();
+    if (!enc) return fail(MLB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const int Nb = batch >= 256 ? 256 : (batch + 15) / 16 * 16;
+    alignas(64) CUtensorMap tA, tA2, tB;
+    int rc;
+    if ((rc = make_bf16_map(enc, &tA, W, N, K, kTcM))) return rc;
+    if ((rc = make_bf16_map(enc, &tA2, W_up_or_null ? W_up_or_null : W, N, K, kTcM))) return rc;
+    if ((rc = make_bf16_map(enc, &tB, X, batch, K, Nb))) return rc;
+    int* err = nullptr;
+    CU(cudaMalloc(&err, 4));
+    CU(cudaMemset(err, 0, 4));
+    const int na = W_up_or_null ? 2 : 1;
+    GemmTcParams p;
+    p.N = N; p.K = K; p.B = batch; p.Nb = Nb;
+    const size_t stage_bytes = (size_t)na * kTcM * 128 + (size_t)Nb * 128;
+    p.stages = (int)((200 * 1024) / stage_bytes);
+    if (p.stages > 6) p.stages = 6;
+    uint32_t cols = 32;
+    while (cols < (uint32_t)na * (uint32_t)Nb) cols <<= 1;
+    p.tmem_cols = cols;
+    p.y = static_cast<float*>(out); p.resid = resid_or_null; p.h16 = static_cast<bf16_t*>(out); p.err = err;
+    const size_t smem = (size_t)p.stages * stage_bytes + (2 * (size_t)p.stages + 1) * 8 + 16 + 1024;
+    dim3 grid((N + kTcM - 1) / kTcM, (batch + Nb - 1) / Nb);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (W_up_or_null) {
+        e = cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e == cudaSuccess) gemm_tc_kernel<TC_SWIGLU><<<grid, 128, smem, st>>>(tA, tA2, tB, p);
+    } else if (resid_or_null) {
+        e = cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e == cudaSuccess) gemm_tc_kernel<TC_RESID><<<grid, 128, smem, st>>>(tA, tA2, tB, p);
+    } else {
+        e = cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e == cudaSuccess) gemm_tc_kernel<TC_RAW><<<grid, 128, smem, st>>>(tA, tA2, tB, p);
+    }
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    int herr = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&herr, err, 4, cudaMemcpyDeviceToHost);
+    cudaFree(err);
+    if (e != cudaSuccess) return fail(MLB_E_CUDA, "gemm op failed: %s", cudaGetErrorString(e));
+    if (herr) return fail(MLB_E_TIMEOUT, "gemm op: a bounded wait ran out (code %d)", herr);
     return MLB_OK;
 }
 

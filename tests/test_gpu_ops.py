@@ -96,3 +96,31 @@ def test_attention_op_rejects_bad_arguments(api):
     bad = list(base); bad[2] = api.DT_FP8
     assert L.mlb_op_attn_decode(*bad) == api.MLB_E_INVALID
     assert L.mlb_op_attn_decode(*base) == 0
+
+
+@pytest.mark.parametrize("N,K,batch", [(128, 64, 16), (256, 512, 32), (1408, 512, 256), (512, 1408, 100), (1552, 512, 20),
+                                       (8192, 512, 300)])
+def test_tcgen05_gemm_matches_fp32_matmul(api, N, K, batch):
+    """Plain / residual / gate-up forms of the tensor-core projection against torch.matmul on the
+    same bf16 values in fp32 (only the accumulation order differs): ragged N and batch tails,
+    several k-blocks, two batch tiles."""
+    import torch
+    g = torch.Generator(device="cpu").manual_seed(N + K + batch)
+    W = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    W2 = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    X = torch.randn(batch, K, generator=g).to(torch.bfloat16).cuda()
+    R = torch.randn(batch, N, generator=g).cuda()
+    want = X.float() @ W.float().T
+    L = api.lib()
+    out = torch.full((batch, N), float("nan"), device="cuda")
+    assert L.mlb_op_gemm_bf16(W.data_ptr(), None, X.data_ptr(), None, out.data_ptr(), N, K, batch, None) == 0, L.mlb_last_error()
+    scale = want.abs().max().item()
+    assert (out - want).abs().max().item() < 2e-5 * max(scale, 1.0) + 1e-5
+    out2 = R.clone()
+    assert L.mlb_op_gemm_bf16(W.data_ptr(), None, X.data_ptr(), out2.data_ptr(), out2.data_ptr(), N, K, batch, None) == 0
+    assert (out2 - (want + R)).abs().max().item() < 2e-5 * max(scale, 1.0) + 1e-5
+    up = X.float() @ W2.float().T
+    h_want = (want / (1.0 + torch.exp(-want))) * up
+    h = torch.zeros(batch, N, dtype=torch.bfloat16, device="cuda")
+    assert L.mlb_op_gemm_bf16(W.data_ptr(), W2.data_ptr(), X.data_ptr(), None, h.data_ptr(), N, K, batch, None) == 0
+    assert (h.float() - h_want).abs().max().item() < 1e-2 * max(h_want.abs().max().item(), 1e-3)

@@ -113,6 +113,41 @@ def test_ragged_batch_matches_oracle(api, tmp_path, monkeypatch, name, batch, pa
     model.close()
 
 
+@pytest.mark.parametrize("name,batch", [("bf16", 16), ("bf16", 40), ("bf16_w_f32_kv", 24)])
+def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name, batch):
+    """Batch >= 16 with bf16 weights runs the projections as tcgen05 GEMMs on bf16 activations.
+    Teacher-forced on the oracle's tokens: logits within 2e-2 at every step; the device pick equals
+    the oracle's wherever the oracle's top-2 margin exceeds that bound."""
+    monkeypatch.setenv("MLB_GEMM", "tc")
+    spec = SPECS[name]
+    path = write_model(tmp_path, spec, seed=6)
+    oracle = load_oracle(path)
+    lens = [1 + (5 * i) % 23 for i in range(batch)]
+    prompts = random_prompts(spec.vocab, lens, seed=9)
+    steps = 12
+    rolls = [oracle_rollout(oracle, prompts[b], steps) for b in range(batch)]
+    model = api.Model(path)
+    sess = api.Session(model, batch)
+    sess.prefill(prompts)
+    worst = 0.0
+    checked = 0
+    for i in range(steps):
+        forced = None if i == 0 else [int(rolls[b][0][i - 1]) for b in range(batch)]
+        picks = sess.decode_step(in_tokens=forced)
+        lg = sess.logits()
+        for b in range(batch):
+            want = rolls[b][1][i]
+            worst = max(worst, logits_error(lg[b], want))
+            top2 = np.sort(want)[-2:]
+            if (top2[1] - top2[0]) > 2 * TOL_LOWP * np.abs(want).max():
+                assert int(picks[b]) == int(rolls[b][0][i]), (i, b)
+                checked += 1
+    assert worst < TOL_LOWP, worst
+    assert checked > batch      # the margin test did not make the check vacuous
+    sess.close()
+    model.close()
+
+
 def test_reference_script_golden_logits(api, tmp_path):
     """Column L-1 of the reference's [V x L] logits (its PyTorch script, run unchanged) against a
     KV-cached decode of the same 256 tokens: logits within 1e-3, identical argmax at all 256
