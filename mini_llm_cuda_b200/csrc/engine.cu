@@ -397,7 +397,8 @@ struct mlb_session {
     float* rawq = nullptr;
     struct alignas(64) TcLayerMaps { CUtensorMap qkv, o, w1a, w1b, w2; };
     std::vector<TcLayerMaps> tc_maps;
-    struct alignas(64) TcGlobalMaps { CUtensorMap E, xn, a_attn, a_dn, h; } tc_g;
+    // activation operand maps per batch tile 16, 32, 64, 128, 256 (index log2(Nb/16))
+    struct alignas(64) TcGlobalMaps { CUtensorMap E, xn[5], a_attn[5], a_dn[5], h[5]; } tc_g;
     int* pinned_err = nullptr;
 };
 
@@ -612,24 +613,39 @@ struct Chain {
         return MLB_OK;
     }
 
+    // Batch tile (UMMA N) of one GEMM: the largest of 256..16 that still yields enough CTAs to
+    // spread the weight stream and the MMAs over the SMs (the projections of a decode step have few
+    // 128-row tiles; the activations are re-read per batch tile from L2, which is cheap).
+    static int tc_pick_nb(const mlb_session* s, int N) {
+        const int tiles_m = (N + kTcM - 1) / kTcM;
+        const int cap = std::min(256, (s->B + 15) / 16 * 16);
+        for (int nb = 256; nb > 16; nb >>= 1) {
+            if (nb > cap) continue;
+            if (tiles_m * ((s->B + nb - 1) / nb) >= 120) return nb;
+        }
+        return std::min(cap, 16);
+    }
+    static int nb_index(int nb) { return nb == 16 ? 0 : nb == 32 ? 1 : nb == 64 ? 2 : nb == 128 ? 3 : 4; }
+
     template <int MODE>
-    static int gemm_tc(mlb_session* s, const CUtensorMap& A, const CUtensorMap& A2, const CUtensorMap& Bm, int N, int K, float* y,
+    static int gemm_tc(mlb_session* s, const CUtensorMap& A, const CUtensorMap& A2, const CUtensorMap* Bmaps, int N, int K, float* y,
                        const float* resid, bf16_t* h16, Recorder* rec, const char* name) {
         GemmTcParams p;
-        p.N = N; p.K = K; p.B = s->B; p.Nb = s->tc_nb;
-        p.stages = MODE == TC_SWIGLU ? s->tc_stages_swiglu : s->tc_stages;
+        const int nb = tc_pick_nb(s, N);
+        p.N = N; p.K = K; p.B = s->B; p.Nb = nb;
+        const size_t stage_bytes = (size_t)(MODE == TC_SWIGLU ? 2 : 1) * kTcM * 128 + (size_t)nb * 128;
+        p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, (200 * 1024) / stage_bytes));
         uint32_t cols = 32;
-        while (cols < (uint32_t)(MODE == TC_SWIGLU ? 2 : 1) * (uint32_t)s->tc_nb) cols <<= 1;
+        while (cols < (uint32_t)(MODE == TC_SWIGLU ? 2 : 1) * (uint32_t)nb) cols <<= 1;
         p.tmem_cols = cols;
         p.y = y; p.resid = resid; p.h16 = h16; p.err = s->dev_err;
-        const size_t stage_bytes = (size_t)(MODE == TC_SWIGLU ? 2 : 1) * kTcM * 128 + (size_t)s->tc_nb * 128;
         const size_t smem = (size_t)p.stages * stage_bytes + (2 * (size_t)p.stages + 1) * 8 + 16 + 1024;
-        dim3 grid((N + kTcM - 1) / kTcM, (s->B + s->tc_nb - 1) / s->tc_nb);
+        dim3 grid((N + kTcM - 1) / kTcM, (s->B + nb - 1) / nb);
         int rc;
         if (rec && (rc = rec->begin(name, (uint64_t)N * K * 2 * (MODE == TC_SWIGLU ? 2 : 1) + (uint64_t)s->B * K * 2 + (uint64_t)s->B * N * 4,
                                     2ull * N * K * s->B * (MODE == TC_SWIGLU ? 2 : 1))))
             return rc;
-        cudaError_t e = launch_chain(s->use_pdl, gemm_tc_kernel<MODE>, grid, dim3(128), smem, s->stream, A, A2, Bm, p);
+        cudaError_t e = launch_chain(s->use_pdl, gemm_tc_kernel<MODE>, grid, dim3(128), smem, s->stream, A, A2, Bmaps[nb_index(nb)], p);
         if (e != cudaSuccess) return fail(MLB_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
         if (rec) return rec->end();
         return MLB_OK;
@@ -706,7 +722,7 @@ struct Chain {
                 if (rec && (rc = rec->end())) return rc;
                 ++launches;
             }
-            const CUtensorMap& amap = L.type == MLB_LAYER_ATTENTION ? s->tc_g.a_attn : s->tc_g.a_dn;
+            const CUtensorMap* amap = L.type == MLB_LAYER_ATTENTION ? s->tc_g.a_attn : s->tc_g.a_dn;
             if ((rc = gemm_tc<TC_RESID>(s, M.o, M.o, amap, d, L.o_in, s->x, s->x, nullptr, rec, "oproj_gemm_tcgen05_residual"))) return rc;
             ++launches;
             if ((rc = prep(L.g2, nullptr, nullptr, 0))) return rc;
@@ -1009,10 +1025,13 @@ static int setup_tc_path(mlb_session* s) {
         if ((rc = make_bf16_map(enc, &M.w2, L.W2, c.dim, c.ffn_dim, kTcM))) return rc;
     }
     if ((rc = make_bf16_map(enc, &s->tc_g.E, s->m->E, c.vocab, c.dim, kTcM))) return rc;
-    if ((rc = make_bf16_map(enc, &s->tc_g.xn, s->xn16, B, c.dim, s->tc_nb))) return rc;
-    if ((rc = make_bf16_map(enc, &s->tc_g.a_attn, s->a16, B, nq, s->tc_nb))) return rc;
-    if ((rc = make_bf16_map(enc, &s->tc_g.a_dn, s->a16, B, a_dn, s->tc_nb))) return rc;
-    if ((rc = make_bf16_map(enc, &s->tc_g.h, s->h16, B, c.ffn_dim, s->tc_nb))) return rc;
+    for (int i = 0; i < 5; ++i) {
+        const uint32_t nb = 16u << i;
+        if ((rc = make_bf16_map(enc, &s->tc_g.xn[i], s->xn16, B, c.dim, nb))) return rc;
+        if ((rc = make_bf16_map(enc, &s->tc_g.a_attn[i], s->a16, B, nq, nb))) return rc;
+        if ((rc = make_bf16_map(enc, &s->tc_g.a_dn[i], s->a16, B, a_dn, nb))) return rc;
+        if ((rc = make_bf16_map(enc, &s->tc_g.h[i], s->h16, B, c.ffn_dim, nb))) return rc;
+    }
     const int big = 227 * 1024;
     CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
     CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
