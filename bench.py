@@ -35,9 +35,26 @@ if ROOT not in sys.path:
 PROMPT_LEN = 128
 HBM_FALLBACK_GBS = 6650.0      # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# capture summarised under profiles/ (None until a capture exists for that kernel).
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch on the cfg1 batch-1 workload, from the
+# ncu --set full capture summarised in profiles/ncu_full_gemv_cfg1_b1.md (None = not captured).
+NCU_TRAFFIC_BYTES = {
+    "ffn_down_gemv_residual_ple": 1543680,
+    "ffn_gateup_gemv_norm_swiglu": 2913792,
+    "qkv_gemv_norm_rope_kvappend": 1614592,
+    "oproj_gemv_residual": 557312,
+    "deltanet_proj_gemv_norm": 1621504,
+    "lmhead_gemv_norm_argmax": 8433408,
+}
+
+# workload name -> (model, batch per GPU at N=1, prompt length, description)
+WORKLOADS = {
+    "cfg1": ("cfg1", 1, 128, "cfg1: d=512, 8 layers (6 attention + 2 gated delta-net), 8 heads x 64, ffn 1408, PLE 64, "
+                             "vocab 8192, bf16 weights+KV, fp32 delta-net state, batch 1 per GPU, 128-token prompt, greedy"),
+    "cfg3": ("cfg3", 64, 64, "cfg3: d=1024, 12 gated delta-net layers, 8 heads, dk=dv=128 (fp32 state 128x128 per head), "
+                             "ffn 2816, vocab 8192, bf16 weights, batch 64 per GPU, 64-token prompt, greedy"),
+    "cfg4": ("cfg4", 1, 512, "cfg4: d=2048, 24 layers (18 GQA attention 16q/4kv x 128 + 6 gated delta-net), ffn 5632, PLE 128, "
+                             "vocab 32000, FP8 e4m3 weights with per-row scales, bf16 KV, batch 1 per GPU, 512-token prompt, greedy"),
+}
 
 
 def measured_peaks():
@@ -214,6 +231,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-batched", action="store_true")
+    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="sequences per GPU (default: the workload's)")
     args = ap.parse_args()
     world, rank, local = dist_setup()
     if args.impl == "reference":
@@ -227,16 +246,19 @@ def main():
     import torch                                # plumbing: device sync, barrier, max over ranks
 
     tmp = tempfile.mkdtemp(prefix="mlb_bench_")
-    spec, path = make_model_file(tmp, "cfg1")
-    K = min(K, spec.max_context - PROMPT_LEN - W)
-    prompt = prompt_for(spec.vocab, PROMPT_LEN, 1 + rank)
+    model_name, wl_batch, prompt_len, wl_text = WORKLOADS[args.workload]
+    batch = args.batch or wl_batch
+    spec, path = make_model_file(tmp, model_name)
+    K = min(K, spec.max_context - prompt_len - W)
+    prompts = [prompt_for(spec.vocab, prompt_len, 1 + rank * batch + i) for i in range(batch)]
     model = api.Model(path, device=local)
-    sess = api.Session(model, 1)
+    os.remove(path)                             # the weights are on the device now
+    sess = api.Session(model, batch)
     hbm_peak, peak_kind = measured_peaks()
 
     clocks = ClockSampler(local)
     # ---- (1) device-timed, L2 flushed between steps --------------------------------------
-    sess.prefill([prompt])
+    sess.prefill(prompts)
     sess.decode(W)
     barrier_sync(world, local)
     clocks.start()
@@ -244,14 +266,14 @@ def main():
     barrier_sync(world, local)
     flushed_ms = max_over_ranks(float(step_ms.sum()), world, local)
     # ---- (2) device-timed, back to back (weights stay in L2) -----------------------------
-    sess.prefill([prompt])
+    sess.prefill(prompts)
     sess.decode(W)
     barrier_sync(world, local)
     warm_step_ms, _ = sess.decode_timed(K, False)
     barrier_sync(world, local)
     warm_ms = max_over_ranks(sess.last_total_ms, world, local)
     # ---- (3) end to end through the C ABI with host buffers every step -------------------
-    sess.prefill([prompt])
+    sess.prefill(prompts)
     tok = sess.decode(W)[:, -1].copy()
     barrier_sync(world, local)
     t0 = time.perf_counter()
@@ -263,7 +285,7 @@ def main():
     launches = sess.launches_per_step()
 
     # ---- (4) per-kernel event timing for the roofline (rank 0) ----------------------------
-    sess.prefill([prompt])
+    sess.prefill(prompts)
     sess.decode(W)
     bytes_now = sess.step_bytes()
     stats = sess.profile(min(K, 64), True)
@@ -286,17 +308,17 @@ def main():
                 "GBps": round(s["bytes"] / max(s["total_ms"], 1e-9) / 1e6, 1)} for s in stats]
 
     out = {
-        "metric": "decode_tokens_per_s", "value": world * K / (flushed_ms * 1e-3), "unit": "tokens/s",
+        "metric": "decode_tokens_per_s", "value": world * batch * K / (flushed_ms * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": flushed_ms / K, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "cfg1: d=512, 8 layers (6 attention + 2 gated delta-net), 8 heads x 64, ffn 1408, PLE 64, "
-                               "vocab 8192, bf16 weights+KV, fp32 delta-net state, batch 1 per GPU, 128-token prompt, greedy",
-                   "batch_per_gpu": 1, "prompt_len": PROMPT_LEN, "max_context": spec.max_context,
-                   "parallelism": f"replicas x{world}, one sequence per GPU, no collective",
+        "scaling": "weak", "vs_baseline": None, "dtype": {"bfloat16": "bf16", "float8_e4m3": "fp8", "float32": "f32"}[spec.weight_dtype], "data": "synthetic",
+        "config": {"workload": wl_text,
+                   "batch_per_gpu": batch, "prompt_len": prompt_len, "max_context": spec.max_context,
+                   "parallelism": f"replicas x{world}, {batch} sequence(s) per GPU, no collective",
                    "l2": "flushed (192 MiB write) before every timed step; value_l2_warm is the unflushed loop"},
-        "value_l2_warm": world * K / (warm_ms * 1e-3), "ms_per_step_l2_warm": warm_ms / K,
+        "value_l2_warm": world * batch * K / (warm_ms * 1e-3), "ms_per_step_l2_warm": warm_ms / K,
         "ms_per_token_p50": float(np.median(step_ms)), "ms_per_token_p50_l2_warm": float(np.median(warm_step_ms)),
-        "e2e": {"value": world * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
+        "e2e": {"value": world * batch * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
+                "d2h_bytes_per_step": 4 * batch,
                 "how": "mlb_decode_step per token: pending id from pinned host memory, picked id back to the host"},
         "gpu_launches": launches * K, "launches_per_step": launches,
         "roofline": roofline, "step_roofline": step_roofline, "kernels": kernels, "clocks": clock_info,
@@ -304,12 +326,14 @@ def main():
     sess.close()
 
     # ---- (5) batched decode (256 sequences sharded over the GPUs, top-k 50 sampling) ------
-    if not args.skip_batched:
-        per = max(1, 256 // world)
+    if not args.skip_batched and args.workload == "cfg1":
+        from mini_llm_cuda_b200.sharding import shard_range
+        lo, hi = shard_range(256, world, rank)
+        per = hi - lo
         bs = api.Session(model, per, max_context=512)
-        prompts = [prompt_for(spec.vocab, 256, rank * per + i) for i in range(per)]
-        samp = {"mode": "top_k", "top_k": 50, "temperature": 1.0, "seeds": [rank * per + i for i in range(per)]}
-        bs.prefill(prompts)
+        bprompts = [prompt_for(spec.vocab, 256, lo + i) for i in range(per)]
+        samp = {"mode": "top_k", "top_k": 50, "temperature": 1.0, "seeds": [lo + i for i in range(per)]}
+        bs.prefill(bprompts)
         bs.decode(W, samp)
         barrier_sync(world, local)
         bms, _ = bs.decode_timed(64, False, samp)
@@ -318,13 +342,14 @@ def main():
         bb = bs.step_bytes()
         out["batched"] = {"workload": f"256 sequences ({per} per GPU), 256-token prompts (seed = sequence index), "
                                       "temperature 1.0 top-k 50 Philox sampling, paged KV block 16, 64 timed steps",
-                          "value": 256 // world * world * 64 / (btot * 1e-3), "unit": "tokens/s", "ms_per_step": btot / 64,
+                          "value": 256 * 64 / (btot * 1e-3), "unit": "tokens/s", "ms_per_step": btot / 64,
                           "algorithmic_bytes_per_step_per_gpu": bb["total"],
                           "hbm_frac": bb["total"] / (btot / 64 * 1e-3) / 1e9 / hbm_peak, "scaling": "strong"}
         bs.close()
 
     if rank == 0 and world == 1 and not args.skip_cpu:
-        out["cpu_baseline"] = cpu_baseline(spec, path, prompt)
+        spec2, path2 = make_model_file(tmp, model_name)
+        out["cpu_baseline"] = cpu_baseline(spec2, path2, prompts[0], 64 if args.workload == "cfg1" else 8)
     elif rank == 0:
         out["cpu_baseline"] = None
     model.close()

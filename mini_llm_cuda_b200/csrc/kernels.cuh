@@ -225,10 +225,11 @@ struct GemvParams {
 };
 
 // Rows a warp streams per pass and 16-byte vectors per row it fetches BEFORE waiting for the
-// predecessor kernel: 2 rows x 4 vectors at batch tile 1 (latency), 4 rows x 2 otherwise.
+// predecessor kernel: 2 rows x 8 vectors at batch tile 1 (latency: a whole row of up to 2048 bf16
+// elements is in flight before the wait), 4 rows x 2 otherwise.
 template <int BT> struct GemvShape {
     static constexpr int RW = (BT == 1) ? 2 : 4;
-    static constexpr int PRE = (BT == 1) ? 4 : 2;
+    static constexpr int PRE = (BT == 1) ? 8 : 2;
 };
 
 template <typename T, int RW>

@@ -345,6 +345,29 @@ def test_cfg1_latency_config_bf16(api, tmp_path):
     model.close()
 
 
+@pytest.mark.parametrize("path_mode", ["chain", "cluster"])
+def test_cfg4_dims_fp8_gqa_reduced_depth(api, tmp_path, monkeypatch, path_mode):
+    """The quantised larger configuration at its real widths (d=2048, 16 query / 4 kv heads of 128,
+    ffn 5632, PLE 128, FP8 e4m3 weights with per-row scales, bf16 KV) with 4 of its 24 layers and
+    a 4096-token vocabulary so that the CPU oracle finishes in seconds."""
+    monkeypatch.setenv("MLB_DECODE_PATH", path_mode)
+    spec = ModelSpec(dim=2048, layers=4, heads=16, kv_heads=4, head_dim=128, ffn_dim=5632, vocab=4096, max_context=256,
+                     rms_eps=1e-5, ple_dim=128, layer_types=periodic_layer_types(4, 4), weight_dtype="float8_e4m3",
+                     kv_dtype="bfloat16")
+    path = write_model(tmp_path, spec, seed=0, random_gains=False)
+    oracle = load_oracle(path)
+    prompt = random_prompts(spec.vocab, [40], seed=1)[0]
+    want_tok, want_logits = oracle_rollout(oracle, prompt, 12)
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    sess.prefill([prompt])
+    got = sess.decode(12)[0]
+    assert got.tolist() == want_tok.tolist()
+    assert logits_error(sess.logits()[0], want_logits[-1]) < TOL_LOWP
+    sess.close()
+    model.close()
+
+
 def test_cfg0_fp32_64_greedy(api, tmp_path):
     """Config 0 (the CPU-runnable case): d=256, 4 layers alternating attention / delta-net,
     PLE 32, V=4096, fp32; 32-token prompt from seed 1, 64 greedy tokens, max context 256."""
