@@ -18,6 +18,7 @@
 #include "tc_host.h"
 #include "mega.cuh"
 #include "model_file.h"
+#include "sgemv.cuh"
 
 namespace mlb {
 
@@ -383,6 +384,8 @@ struct mlb_session {
     float4* flush_buf = nullptr; size_t flush_n = 0;
     int* pinned_tok = nullptr;
     bool use_pdl = true;
+    bool use_sgemv = false;                 // TMA-streamed GEMV for very small batches
+    int sm_count = 148;
     // cluster-per-sequence single-kernel step (small batch)
     bool use_cluster = false;
     int cluster_size = 0;
@@ -482,8 +485,60 @@ static cudaError_t launch_chain(bool pdl, void (*kernel)(KArgs...), dim3 grid, d
 
 template <typename T, typename T2, typename KVT>
 struct Chain {
+    // TMA-streamed variant: one contiguous slab of rows per CTA (one head per CTA for QKV).
+    template <int MODE>
+    static int sgemv(mlb_session* s, const StepCtl& c, GemvParams p, Recorder* rec, const char* name, bool* done) {
+        *done = false;
+        SgemvGeom g;
+        g.stage_bytes = 16 * 1024;
+        if ((size_t)p.K * sizeof(T) > (size_t)g.stage_bytes || (size_t)p.Kp * sizeof(T2) > (size_t)g.stage_bytes) return MLB_OK;
+        int grid_x;
+        if (MODE == GEMV_QKV) {
+            g.rows_per_cta = p.hd;
+            grid_x = p.N / p.hd;
+        } else {
+            const int n_ctas = std::max(1, std::min(s->sm_count, (p.N + 3) / 4));
+            g.rows_per_cta = (p.N + n_ctas - 1) / n_ctas;
+            grid_x = (p.N + g.rows_per_cta - 1) / g.rows_per_cta;
+        }
+        auto up4 = [](int v) { return (v + 3) / 4 * 4; };
+        int off = 0;
+        g.off_xs = off; off += up4(p.K);
+        g.off_xs2 = off; off += up4(std::max(p.Kp, 4));
+        g.off_outs = off; off += up4(std::max(p.hd, 32));
+        g.off_pacc = off; off += up4(g.rows_per_cta + 4);
+        g.off_red = off; off += 32;
+        off = (off + 31) / 32 * 32;
+        g.off_bar = off; off += 8 * 4;
+        off = (off + 31) / 32 * 32;
+        g.off_ring = off;
+        const size_t fixed = (size_t)off * 4;
+        if (fixed + 3 * (size_t)g.stage_bytes > 200 * 1024) return MLB_OK;
+        g.n_stages = (int)std::min<size_t>(8, (200 * 1024 - fixed) / g.stage_bytes);
+        g.err = s->dev_err;
+        const size_t smem = fixed + (size_t)g.n_stages * g.stage_bytes;
+        if (rec) {
+            const uint64_t wbytes = (uint64_t)p.N * p.K * sizeof(T) * (MODE == GEMV_SWIGLU ? 2 : 1) +
+                                    (uint64_t)p.N * p.Kp * sizeof(T2) + (p.wscale ? (uint64_t)p.N * 4 : 0);
+            const uint64_t abytes = (uint64_t)s->B * ((uint64_t)p.K + p.N) * 4;
+            int rc = rec->begin(name, wbytes + abytes, 2ull * p.N * (p.K + p.Kp) * s->B * (MODE == GEMV_SWIGLU ? 2 : 1));
+            if (rc) return rc;
+        }
+        cudaError_t e = launch_chain(s->use_pdl, sgemv_kernel<T, T2, KVT, MODE>, dim3(grid_x, s->B), dim3(kMegaThreads), smem,
+                                     s->stream, c, p, g);
+        if (e != cudaSuccess) return fail(MLB_E_CUDA, "launch of %s (streamed) failed: %s", name, cudaGetErrorString(e));
+        *done = true;
+        if (rec) return rec->end();
+        return MLB_OK;
+    }
+
     template <int MODE>
     static int gemv(mlb_session* s, const StepCtl& c, GemvParams p, int R, Recorder* rec, const char* name) {
+        if (s->use_sgemv) {
+            bool done = false;
+            int rc = sgemv<MODE>(s, c, p, rec, name, &done);
+            if (rc || done) return rc;
+        }
         p.R = R;
         const size_t per_seq = (size_t)p.K + p.Kp + R + 1 + 8;
         const int BT = pick_bt(s->B, per_seq);
@@ -515,6 +570,7 @@ struct Chain {
     template <int MODE>
     static int configure_mode() {
         const int big = 200 * 1024;
+        CU(cudaFuncSetAttribute(sgemv_kernel<T, T2, KVT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big + 2048));
         CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 1, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
         CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 2, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
         CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 4, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
@@ -1188,6 +1244,10 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     {
         const char* e = std::getenv("MLB_NO_PDL");     // measurement switch: plain stream-ordered launches
         s->use_pdl = !(e && e[0] == '1');
+        const char* gv = std::getenv("MLB_GEMV");      // stream | thread | auto (stream for batch <= 4)
+        const std::string gmode = gv ? gv : "auto";
+        s->use_sgemv = gmode == "stream" || (gmode == "auto" && batch <= 4);
+        cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, m->device);
     }
     SA(sess_alloc(s, (void**)&s->dev_err, 4, true));
     SA(chain_configure(s));

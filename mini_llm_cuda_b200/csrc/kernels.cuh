@@ -225,11 +225,11 @@ struct GemvParams {
 };
 
 // Rows a warp streams per pass and 16-byte vectors per row it fetches BEFORE waiting for the
-// predecessor kernel: 2 rows x 8 vectors at batch tile 1 (latency: a whole row of up to 2048 bf16
-// elements is in flight before the wait), 4 rows x 2 otherwise.
+// predecessor kernel: 2 rows x 4 vectors at batch tile 1 (latency; deeper preloads cost occupancy
+// and measured slower), 4 rows x 2 otherwise.
 template <int BT> struct GemvShape {
     static constexpr int RW = (BT == 1) ? 2 : 4;
-    static constexpr int PRE = (BT == 1) ? 8 : 2;
+    static constexpr int PRE = (BT == 1) ? 4 : 2;
 };
 
 template <typename T, int RW>
@@ -621,7 +621,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     constexpr int PPI = 32 / LPR;                  // positions per warp iteration
     constexpr int NW = 4;
     static_assert(LPR <= 32 && PPI >= 1, "head_dim too large for one warp row");
-    const int b = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x, S = gridDim.x;
+    const int b = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();                                    // q and this step's K/V row come from the projection kernel
     if (!seq_active(c, b)) return;                 // uniform for all CTAs of this sequence
@@ -630,6 +630,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     const int pos = c.pos[b];
     const int ctx = pos + 1;
     const int npages = (ctx + kKvBlock - 1) / kKvBlock;
+    // The grid is sized for the longest context; a short one uses fewer splits (at least eight
+    // pages each) so that the combine does not cost more than the attention itself. The CTAs
+    // beyond that leave at once; every CTA of a (sequence, kv head) computes the same S.
+    const int S = min((int)gridDim.x, max(1, (npages + 7) / 8));
+    if (split >= S) return;
     const int pps = (npages + S - 1) / S;
     const int pg_begin = split * pps, pg_end = min(npages, pg_begin + pps);
 

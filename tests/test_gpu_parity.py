@@ -57,13 +57,14 @@ def tol_of(spec):
     return TOL_FP32 if spec.weight_dtype == "float32" and spec.kv_dtype == "float32" else TOL_LOWP
 
 
-@pytest.mark.parametrize("path_mode", ["cluster", "chain"])
+@pytest.mark.parametrize("path_mode", ["cluster", "chain", "chain_thread"])
 @pytest.mark.parametrize("name", list(SPECS))
 def test_greedy_rollout_matches_oracle(api, tmp_path, monkeypatch, name, path_mode):
     """Batch 1: 20-token prompt, 48 greedy tokens: identical ids, logits within tolerance at
-    every step (context crosses three KV pages). Run through both decode paths: the
-    single-kernel cluster step and the kernel chain."""
-    monkeypatch.setenv("MLB_DECODE_PATH", path_mode)
+    every step (context crosses three KV pages). Run through the decode paths: the single-kernel
+    cluster step, the kernel chain with TMA-streamed GEMVs, the chain with per-thread-load GEMVs."""
+    monkeypatch.setenv("MLB_DECODE_PATH", "cluster" if path_mode == "cluster" else "chain")
+    monkeypatch.setenv("MLB_GEMV", "thread" if path_mode == "chain_thread" else "auto")
     spec = SPECS[name]
     path = write_model(tmp_path, spec, seed=3)
     oracle = load_oracle(path)
@@ -89,9 +90,12 @@ def test_greedy_rollout_matches_oracle(api, tmp_path, monkeypatch, name, path_mo
 @pytest.mark.parametrize("name,batch,path_mode", [("attn_fp32", 3, "cluster"), ("attn_fp32", 3, "chain"),
                                                   ("mixed_ple", 9, "auto"), ("mixed_ple", 7, "cluster"),
                                                   ("bf16", 5, "cluster"), ("bf16", 5, "chain"), ("gqa", 17, "auto"),
-                                                  ("fp8", 4, "cluster"), ("qknorm_gating", 8, "cluster")])
+                                                  ("fp8", 4, "cluster"), ("qknorm_gating", 8, "cluster"),
+                                                  ("fp8", 4, "chain"), ("mixed_ple", 2, "chain_thread"),
+                                                  ("gqa", 4, "chain_thread")])
 def test_ragged_batch_matches_oracle(api, tmp_path, monkeypatch, name, batch, path_mode):
-    monkeypatch.setenv("MLB_DECODE_PATH", path_mode)
+    monkeypatch.setenv("MLB_DECODE_PATH", "chain" if path_mode == "chain_thread" else path_mode)
+    monkeypatch.setenv("MLB_GEMV", "thread" if path_mode == "chain_thread" else "auto")
     """Ragged prompts (1 .. 37 tokens) in one batch, decode_n in one call: every sequence
     equals its own batch-1 oracle roll-out."""
     spec = SPECS[name]
