@@ -384,7 +384,8 @@ struct mlb_session {
     float4* flush_buf = nullptr; size_t flush_n = 0;
     int* pinned_tok = nullptr;
     bool use_pdl = true;
-    bool use_sgemv = false;                 // TMA-streamed GEMV for very small batches
+    bool use_sgemv = false;                 // TMA-streamed GEMV for very small batches and large matrices
+    bool force_sgemv = false;               // MLB_GEMV=stream: also for small matrices (tests)
     int sm_count = 148;
     // cluster-per-sequence single-kernel step (small batch)
     bool use_cluster = false;
@@ -489,13 +490,18 @@ struct Chain {
     template <int MODE>
     static int sgemv(mlb_session* s, const StepCtl& c, GemvParams p, Recorder* rec, const char* name, bool* done) {
         *done = false;
+        // Worth it only when the matrix is large: below a few MB the per-thread-load kernel's
+        // shorter latency chain wins (measured on the 1-GPU latency configuration).
+        const size_t mat_bytes = (size_t)p.N * p.K * sizeof(T) * (MODE == GEMV_SWIGLU ? 2 : 1);
+        if (!s->force_sgemv && mat_bytes < (4u << 20)) return MLB_OK;
         SgemvGeom g;
-        g.stage_bytes = 16 * 1024;
+        g.stage_bytes = 48 * 1024;
         if ((size_t)p.K * sizeof(T) > (size_t)g.stage_bytes || (size_t)p.Kp * sizeof(T2) > (size_t)g.stage_bytes) return MLB_OK;
         int grid_x;
         if (MODE == GEMV_QKV) {
-            g.rows_per_cta = p.hd;
-            grid_x = p.N / p.hd;
+            // whole heads when the per-head norm needs them, else 32-row groups (RoPE pairs stay together)
+            g.rows_per_cta = p.qk_norm ? p.hd : 32;
+            grid_x = p.N / g.rows_per_cta;
         } else {
             const int n_ctas = std::max(1, std::min(s->sm_count, (p.N + 3) / 4));
             g.rows_per_cta = (p.N + n_ctas - 1) / n_ctas;
@@ -513,8 +519,8 @@ struct Chain {
         off = (off + 31) / 32 * 32;
         g.off_ring = off;
         const size_t fixed = (size_t)off * 4;
-        if (fixed + 3 * (size_t)g.stage_bytes > 200 * 1024) return MLB_OK;
-        g.n_stages = (int)std::min<size_t>(8, (200 * 1024 - fixed) / g.stage_bytes);
+        if (fixed + 3 * (size_t)g.stage_bytes > 210 * 1024) return MLB_OK;
+        g.n_stages = (int)std::min<size_t>(8, (210 * 1024 - fixed) / g.stage_bytes);
         g.err = s->dev_err;
         const size_t smem = fixed + (size_t)g.n_stages * g.stage_bytes;
         if (rec) {
@@ -570,7 +576,7 @@ struct Chain {
     template <int MODE>
     static int configure_mode() {
         const int big = 200 * 1024;
-        CU(cudaFuncSetAttribute(sgemv_kernel<T, T2, KVT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big + 2048));
+        CU(cudaFuncSetAttribute(sgemv_kernel<T, T2, KVT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 212 * 1024));
         CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 1, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
         CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 2, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
         CU(cudaFuncSetAttribute(gemv_kernel<T, T2, KVT, 4, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
@@ -1211,7 +1217,9 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     SA(sess_alloc(s, (void**)&s->part, B * c.heads * s->splits * (c.head_dim + 2) * 4, true));
     SA(sess_alloc(s, (void**)&s->attn_ticket, B * c.kv_heads * 4, true));
     s->lm_rows = 16;
-    s->lm_parts = (c.vocab + s->lm_rows - 1) / s->lm_rows;
+    // argmax partials per sequence: one per LM-head CTA of either GEMV form (the streamed form
+    // launches up to one CTA per SM, whatever the vocabulary size)
+    s->lm_parts = std::max((c.vocab + s->lm_rows - 1) / s->lm_rows, 2 * sm_count);
     SA(sess_alloc(s, (void**)&s->part_val, B * s->lm_parts * 4, true));
     SA(sess_alloc(s, (void**)&s->part_idx, B * s->lm_parts * 4, true));
     SA(sess_alloc(s, (void**)&s->lm_ticket, (B + 7) / 1 * 4, true));
@@ -1247,6 +1255,7 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
         const char* gv = std::getenv("MLB_GEMV");      // stream | thread | auto (stream for batch <= 4)
         const std::string gmode = gv ? gv : "auto";
         s->use_sgemv = gmode == "stream" || (gmode == "auto" && batch <= 4);
+        s->force_sgemv = gmode == "stream";
         cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, m->device);
     }
     SA(sess_alloc(s, (void**)&s->dev_err, 4, true));

@@ -630,10 +630,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     const int pos = c.pos[b];
     const int ctx = pos + 1;
     const int npages = (ctx + kKvBlock - 1) / kKvBlock;
-    // The grid is sized for the longest context; a short one uses fewer splits (at least eight
-    // pages each) so that the combine does not cost more than the attention itself. The CTAs
-    // beyond that leave at once; every CTA of a (sequence, kv head) computes the same S.
-    const int S = min((int)gridDim.x, max(1, (npages + 7) / 8));
+    // The grid is sized for the longest context; a split needs at least one page, and the CTAs
+    // beyond the page count leave at once (fewer partials for the combine to read). Every CTA of a
+    // (sequence, kv head) computes the same S.
+    const int S = min((int)gridDim.x, npages);
+    const int SG = (int)gridDim.x;                 // stride of the partial buffer: fixed by the grid, not by S
     if (split >= S) return;
     const int pps = (npages + S - 1) / S;
     const int pg_begin = split * pps, pg_end = min(npages, pg_begin + pps);
@@ -741,7 +742,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
             p.abuf[((size_t)b * p.heads + h) * HD + e] = o;
             if (p.abuf16) p.abuf16[((size_t)b * p.heads + h) * HD + e] = __float2bfloat16_rn(o);
         } else {
-            float* pp = p.part + (((size_t)b * p.heads + h) * S + split) * (HD + 2);
+            float* pp = p.part + (((size_t)b * p.heads + h) * SG + split) * (HD + 2);
             pp[e] = at;
             if (e == 0) { pp[HD] = mn; pp[HD + 1] = lt; }
         }
@@ -757,18 +758,29 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // Combine: one warp per head turns the splits' (max, sum) pairs into normalised weights once;
+    // then every thread accumulates its output elements with independent loads.
+    __shared__ float wsm[G][64];
+    for (int g = warp; g < G; g += NW) {
+        const float* pp = p.part + ((size_t)b * p.heads + h0 + g) * SG * (HD + 2);
+        float m0 = kNegBig, l0 = 0.f, m1 = kNegBig, l1 = 0.f;
+        if (lane < S) { m0 = __ldcg(pp + (size_t)lane * (HD + 2) + HD); l0 = __ldcg(pp + (size_t)lane * (HD + 2) + HD + 1); }
+        if (lane + 32 < S) { m1 = __ldcg(pp + (size_t)(lane + 32) * (HD + 2) + HD); l1 = __ldcg(pp + (size_t)(lane + 32) * (HD + 2) + HD + 1); }
+        float mx = fmaxf(m0, m1);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float w0 = expf(m0 - mx), w1 = expf(m1 - mx);
+        const float lt = warp_sum(l0 * w0 + l1 * w1);
+        wsm[g][lane] = w0 / lt;
+        wsm[g][lane + 32] = w1 / lt;
+    }
+    __syncthreads();
     for (int i = tid; i < G * HD; i += blockDim.x) {
         int g = i / HD, e = i % HD, h = h0 + g;
-        const float* pp = p.part + ((size_t)b * p.heads + h) * S * (HD + 2);
-        float mn = kNegBig;
-        for (int s = 0; s < S; ++s) mn = fmaxf(mn, __ldcg(pp + (size_t)s * (HD + 2) + HD));
-        float lt = 0.f, at = 0.f;
-        for (int s = 0; s < S; ++s) {
-            float sc = expf(__ldcg(pp + (size_t)s * (HD + 2) + HD) - mn);
-            lt += __ldcg(pp + (size_t)s * (HD + 2) + HD + 1) * sc;
-            at += __ldcg(pp + (size_t)s * (HD + 2) + e) * sc;
-        }
-        float o = at / lt;
+        const float* pp = p.part + ((size_t)b * p.heads + h) * SG * (HD + 2) + e;
+        float o = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < S; ++s) o = fmaf(wsm[g][s], __ldcg(pp + (size_t)s * (HD + 2)), o);
         if (p.gbuf) o *= p.gbuf[((size_t)b * p.heads + h) * HD + e];
         p.abuf[((size_t)b * p.heads + h) * HD + e] = o;
         if (p.abuf16) p.abuf16[((size_t)b * p.heads + h) * HD + e] = __float2bfloat16_rn(o);

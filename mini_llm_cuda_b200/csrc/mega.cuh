@@ -219,12 +219,21 @@ __device__ __forceinline__ void consume_slab(Ring& r, int rows, int K, const flo
         const int n = min(rpc, rows - r0);
         r.wait(r.full0 + 8u * r.idx, r.phase, 2);
         const T* base = reinterpret_cast<const T*>(r.stages + (size_t)r.idx * r.stage_bytes);
-        for (int i = 2 * warp; i < n; i += 2 * kMegaWarps) {
-            const bool two = i + 1 < n;
-            float a0, a1;
-            smem_rows_dot2<T>(base + (size_t)i * K, base + (size_t)(two ? i + 1 : i) * K, nvec, xs, lane, a0, a1);
-            f(r0 + i, a0);
-            if (two) f(r0 + i + 1, a1);
+        if (n >= 2 * kMegaWarps) {
+            for (int i = 2 * warp; i < n; i += 2 * kMegaWarps) {
+                const bool two = i + 1 < n;
+                float a0, a1;
+                smem_rows_dot2<T>(base + (size_t)i * K, base + (size_t)(two ? i + 1 : i) * K, nvec, xs, lane, a0, a1);
+                f(r0 + i, a0);
+                if (two) f(r0 + i + 1, a1);
+            }
+        } else {
+            // few long rows in the chunk: one row per warp keeps more warps busy
+            for (int i = warp; i < n; i += kMegaWarps) {
+                float a0, a1;
+                smem_rows_dot2<T>(base + (size_t)i * K, base + (size_t)i * K, nvec, xs, lane, a0, a1);
+                f(r0 + i, a0);
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(r.empty0 + 8u * r.idx);

@@ -127,7 +127,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
             }
         });
     } else if (MODE == GEMV_QKV) {
-        // one head (hd rows) per CTA: rows_per_cta == hd
+        // a CTA owns whole heads' worth of rows (rows_per_cta == hd) when the per-head norm is on,
+        // else a 32-row group inside one head
         consume_slab<T>(ring, rows, K, xs, warp, lane, [&](int r, float v) {
             if (lane == 0) outs[r] = p.wscale ? v * p.wscale[r_begin + r] : v;
         });
@@ -139,14 +140,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
         if (p.qk_norm && seg < 2) {
             // getRMSColSumsAcrossHeads + applyRMSNormAcrossHeads, inference.cu:52-81, :97-111
             float ss = 0.f;
-            for (int r = tid; r < hd; r += kMegaConsumers) ss = fmaf(outs[r], outs[r], ss);
+            for (int r = tid; r < rows; r += kMegaConsumers) ss = fmaf(outs[r], outs[r], ss);
             rs = sqrtf(consumer_sum(ss, red, warp, lane) / (float)hd + p.eps);
         }
         if (active) {
             const int pos = c.pos[b];
             KVT* kpool = reinterpret_cast<KVT*>(p.kpool);
             KVT* vpool = reinterpret_cast<KVT*>(p.vpool);
-            for (int pr = tid; pr < hd / 2; pr += kMegaConsumers) {
+            for (int pr = tid; pr < rows / 2; pr += kMegaConsumers) {
                 const int r = 2 * pr, row = r_begin + r;
                 float a = outs[r], cc = outs[r + 1];
                 if (seg < 2) {
@@ -157,7 +158,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
                         cc = (cc / rs) * gg[srow + 1];
                     }
                     // applyRoPE, inference.cu:113-134
-                    const float cs = p.rope[(size_t)pos * hd + r], sn = p.rope[(size_t)pos * hd + r + 1];
+                    const int e = srow % hd;                       // position of the pair inside its head
+                    const float cs = p.rope[(size_t)pos * hd + e], sn = p.rope[(size_t)pos * hd + e + 1];
                     const float ra = cs * a - sn * cc, rc = sn * a + cs * cc;
                     if (seg == 0) {
                         p.qbuf[(size_t)b * p.nq + srow] = ra;
@@ -165,15 +167,15 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
                     } else {
                         const int kvh = srow / hd;
                         const int page = p.page_table[(size_t)b * p.pt_stride + pos / kKvBlock];
-                        const size_t off = (((size_t)page * p.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * hd + r;
+                        const size_t off = (((size_t)page * p.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * hd + e;
                         Elem<KVT>::put(kpool, off, ra);
                         Elem<KVT>::put(kpool, off + 1, rc);
                     }
                 } else if (seg == 2) {
                     const int srow = row - seg_k;
-                    const int kvh = srow / hd;
+                    const int kvh = srow / hd, e = srow % hd;
                     const int page = p.page_table[(size_t)b * p.pt_stride + pos / kKvBlock];
-                    const size_t off = (((size_t)page * p.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * hd + r;
+                    const size_t off = (((size_t)page * p.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * hd + e;
                     Elem<KVT>::put(vpool, off, a);
                     Elem<KVT>::put(vpool, off + 1, cc);
                 } else {
