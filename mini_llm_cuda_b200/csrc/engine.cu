@@ -386,6 +386,7 @@ struct mlb_session {
     bool use_pdl = true;
     bool use_sgemv = false;                 // TMA-streamed GEMV for very small batches and large matrices
     bool force_sgemv = false;               // MLB_GEMV=stream: also for small matrices (tests)
+    int sg_stage_kb = 48, sg_max_stages = 8; // ring geometry of the streamed GEMV (MLB_SG_STAGE_KB, MLB_SG_STAGES)
     int sm_count = 148;
     // cluster-per-sequence single-kernel step (small batch)
     bool use_cluster = false;
@@ -495,7 +496,7 @@ struct Chain {
         const size_t mat_bytes = (size_t)p.N * p.K * sizeof(T) * (MODE == GEMV_SWIGLU ? 2 : 1);
         if (!s->force_sgemv && mat_bytes < (4u << 20)) return MLB_OK;
         SgemvGeom g;
-        g.stage_bytes = 48 * 1024;
+        g.stage_bytes = s->sg_stage_kb * 1024;
         if ((size_t)p.K * sizeof(T) > (size_t)g.stage_bytes || (size_t)p.Kp * sizeof(T2) > (size_t)g.stage_bytes) return MLB_OK;
         int grid_x;
         if (MODE == GEMV_QKV) {
@@ -511,16 +512,16 @@ struct Chain {
         int off = 0;
         g.off_xs = off; off += up4(p.K);
         g.off_xs2 = off; off += up4(std::max(p.Kp, 4));
-        g.off_outs = off; off += up4(std::max(p.hd, 32));
+        g.off_outs = off; off += up4(std::max(p.hd, 64));
         g.off_pacc = off; off += up4(g.rows_per_cta + 4);
-        g.off_red = off; off += 32;
+        g.off_red = off; off += 64;
         off = (off + 31) / 32 * 32;
         g.off_bar = off; off += 8 * 4;
         off = (off + 31) / 32 * 32;
         g.off_ring = off;
         const size_t fixed = (size_t)off * 4;
         if (fixed + 3 * (size_t)g.stage_bytes > 210 * 1024) return MLB_OK;
-        g.n_stages = (int)std::min<size_t>(8, (210 * 1024 - fixed) / g.stage_bytes);
+        g.n_stages = (int)std::min<size_t>(s->sg_max_stages, (210 * 1024 - fixed) / g.stage_bytes);
         g.err = s->dev_err;
         const size_t smem = fixed + (size_t)g.n_stages * g.stage_bytes;
         if (rec) {
@@ -530,7 +531,7 @@ struct Chain {
             int rc = rec->begin(name, wbytes + abytes, 2ull * p.N * (p.K + p.Kp) * s->B * (MODE == GEMV_SWIGLU ? 2 : 1));
             if (rc) return rc;
         }
-        cudaError_t e = launch_chain(s->use_pdl, sgemv_kernel<T, T2, KVT, MODE>, dim3(grid_x, s->B), dim3(kMegaThreads), smem,
+        cudaError_t e = launch_chain(s->use_pdl, sgemv_kernel<T, T2, KVT, MODE>, dim3(grid_x, s->B), dim3(kSgThreads), smem,
                                      s->stream, c, p, g);
         if (e != cudaSuccess) return fail(MLB_E_CUDA, "launch of %s (streamed) failed: %s", name, cudaGetErrorString(e));
         *done = true;
@@ -1256,6 +1257,8 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
         const std::string gmode = gv ? gv : "auto";
         s->use_sgemv = gmode == "stream" || (gmode == "auto" && batch <= 4);
         s->force_sgemv = gmode == "stream";
+        if (const char* v = std::getenv("MLB_SG_STAGE_KB")) s->sg_stage_kb = std::max(8, std::min(96, std::atoi(v)));
+        if (const char* v = std::getenv("MLB_SG_STAGES")) s->sg_max_stages = std::max(2, std::min(8, std::atoi(v)));
         cudaDeviceGetAttribute(&s->sm_count, cudaDevAttrMultiProcessorCount, m->device);
     }
     SA(sess_alloc(s, (void**)&s->dev_err, 4, true));

@@ -86,6 +86,21 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Layout of an activation vector staged in shared memory for a GEMV whose weights come as
+// 16-byte vectors of EPV elements: lane l of a warp multiplies weight vector vi = l + 32 i with
+// x[vi*EPV .. vi*EPV+EPV). Stored linearly, the lanes' float4 reads would be EPV*4 bytes apart
+// (2-way bank conflicts for bf16 weights, 4-way for fp8). Stored as [EPV/4][nvec] float4s, the
+// q-th float4 of 32 consecutive vectors is 512 contiguous bytes: conflict-free.
+template <int EPV>
+__device__ __forceinline__ int xs_f4_index(int j, int nvec) {      // j: float4 index in linear order
+    constexpr int Q = EPV / 4;
+    return (j % Q) * nvec + j / Q;
+}
+template <int EPV>
+__device__ __forceinline__ int xs_index(int k, int nvec) {          // k: element index in linear order
+    return xs_f4_index<EPV>(k >> 2, nvec) * 4 + (k & 3);
+}
+
 // Programmatic dependent launch (PDL): every kernel of the step lets its successor start
 // launching at once and waits for its predecessor's results only where it first needs them, so
 // that launch latency and the weight fetch (which depends on nothing) overlap the predecessor.
@@ -255,7 +270,7 @@ __device__ __forceinline__ void preload_rows(const T* const (&wrow)[RW], int nve
 }
 
 template <typename T, int BT, int RW>
-__device__ __forceinline__ void fma_vec(const uint4 (&raw)[RW], const float* __restrict__ xs, int xs_stride, int v,
+__device__ __forceinline__ void fma_vec(const uint4 (&raw)[RW], const float* __restrict__ xs, int xs_stride, int v, int nvec,
                                         float (&acc)[RW][BT]) {
     constexpr int EPV = Elem<T>::EPV;
     float w[RW][EPV];
@@ -263,11 +278,11 @@ __device__ __forceinline__ void fma_vec(const uint4 (&raw)[RW], const float* __r
     for (int r = 0; r < RW; ++r) Elem<T>::unpack(raw[r], w[r]);
 #pragma unroll
     for (int b = 0; b < BT; ++b) {
-        const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)b * xs_stride + (size_t)v * EPV);
+        const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)b * xs_stride);
         float xv[EPV];
 #pragma unroll
         for (int q = 0; q < EPV / 4; ++q) {
-            float4 t = xp[q];
+            float4 t = xp[q * nvec + v];                // [EPV/4][nvec] layout, see xs_f4_index
             xv[4 * q] = t.x; xv[4 * q + 1] = t.y; xv[4 * q + 2] = t.z; xv[4 * q + 3] = t.w;
         }
 #pragma unroll
@@ -288,7 +303,7 @@ __device__ __forceinline__ void warp_rows_dot(const T* const (&wrow)[RW], int nv
         uint4 raw[RW];
 #pragma unroll
         for (int r = 0; r < RW; ++r) raw[r] = __ldg(reinterpret_cast<const uint4*>(wrow[r] + (size_t)v * EPV));
-        fma_vec<T, BT, RW>(raw, xs, xs_stride, v, acc);
+        fma_vec<T, BT, RW>(raw, xs, xs_stride, v, nvec, acc);
     }
 }
 
@@ -302,7 +317,7 @@ __device__ __forceinline__ void consume_preloaded(const uint4 (&pre)[RW][PRE], i
             uint4 raw[RW];
 #pragma unroll
             for (int r = 0; r < RW; ++r) raw[r] = pre[r][i];
-            fma_vec<T, BT, RW>(raw, xs, xs_stride, v, acc);
+            fma_vec<T, BT, RW>(raw, xs, xs_stride, v, nvec, acc);
         }
     }
 }
@@ -356,14 +371,15 @@ __global__ void __launch_bounds__(256) gemv_kernel(StepCtl c, GemvParams p) {
             float a = 0.f;
             for (int k = tid; k < K / 4; k += blockDim.x) {
                 float4 v = xr[k];
-                xd[k] = v;
+                xd[xs_f4_index<EPV>(k, nvec)] = v;
                 a = fmaf(v.x, v.x, a); a = fmaf(v.y, v.y, a); a = fmaf(v.z, v.z, a); a = fmaf(v.w, v.w, a);
             }
             ss[b] = a;
             if (Kp > 0) {
                 const int t = c.tok[bg];
                 const T2* trow = reinterpret_cast<const T2*>(p.Ptab) + (size_t)t * Kp;
-                for (int k = tid; k < Kp; k += blockDim.x) xs2[(size_t)b * Kp + k] = Elem<T2>::get(trow, k);
+                for (int k = tid; k < Kp; k += blockDim.x)
+                    xs2[(size_t)b * Kp + xs_index<Elem<T2>::EPV>(k, Kp / Elem<T2>::EPV)] = Elem<T2>::get(trow, k);
             }
         }
         if (p.do_norm) {
@@ -381,9 +397,10 @@ __global__ void __launch_bounds__(256) gemv_kernel(StepCtl c, GemvParams p) {
                 float4* xd = reinterpret_cast<float4*>(xs + (size_t)b * K);
                 const float4* gp = reinterpret_cast<const float4*>(p.gain);
                 for (int k = tid; k < K / 4; k += blockDim.x) {
-                    float4 v = xd[k], g = gp[k];
+                    const int d = xs_f4_index<EPV>(k, nvec);
+                    float4 v = xd[d], g = gp[k];
                     v.x = (v.x / r) * g.x; v.y = (v.y / r) * g.y; v.z = (v.z / r) * g.z; v.w = (v.w / r) * g.w;
-                    xd[k] = v;
+                    xd[d] = v;
                 }
             }
         }

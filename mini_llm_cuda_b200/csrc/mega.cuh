@@ -98,7 +98,8 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kMegaConsumers) : "memory"); }
+template <int NW = kMegaConsumers / 32>
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory"); }
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -180,9 +181,10 @@ __device__ __forceinline__ void issue_slab_pair(Ring& r, const unsigned char* a,
 // ---- consumer side ------------------------------------------------------------------------------
 // Two rows at a time against the activation vector in shared memory: one read of x serves both
 // rows, so shared-memory traffic is 2 bytes per weight byte (fp32 x, bf16 weights) instead of 3.
-template <typename T>
+template <typename T, bool PERM = false>
 __device__ __forceinline__ void smem_rows_dot2(const T* row0, const T* row1, int nvec, const float* xs, int lane, float& a0,
                                                float& a1) {
+    // PERM: xs is stored as [EPV/4][nvec] float4s (xs_f4_index), else linearly
     constexpr int EPV = Elem<T>::EPV;
     a0 = 0.f;
     a1 = 0.f;
@@ -191,10 +193,10 @@ __device__ __forceinline__ void smem_rows_dot2(const T* row0, const T* row1, int
         float w0[EPV], w1[EPV];
         Elem<T>::unpack(*reinterpret_cast<const uint4*>(row0 + (size_t)vi * EPV), w0);
         Elem<T>::unpack(*reinterpret_cast<const uint4*>(row1 + (size_t)vi * EPV), w1);
-        const float4* xp = reinterpret_cast<const float4*>(xs + (size_t)vi * EPV);
+        const float4* xp = reinterpret_cast<const float4*>(xs);
 #pragma unroll
         for (int q = 0; q < EPV / 4; ++q) {
-            const float4 t = xp[q];
+            const float4 t = PERM ? xp[q * nvec + vi] : xp[vi * (EPV / 4) + q];
             a0 = fmaf(w0[4 * q], t.x, a0); a0 = fmaf(w0[4 * q + 1], t.y, a0);
             a0 = fmaf(w0[4 * q + 2], t.z, a0); a0 = fmaf(w0[4 * q + 3], t.w, a0);
             a1 = fmaf(w1[4 * q], t.x, a1); a1 = fmaf(w1[4 * q + 1], t.y, a1);
@@ -210,7 +212,7 @@ __device__ __forceinline__ void smem_rows_dot2(const T* row0, const T* row1, int
 
 // Consume a slab of `rows` rows of K elements: f(local_row, dot) runs in every lane of the warp
 // that owns the row, with the full dot product.
-template <typename T, typename F>
+template <typename T, int NW = kMegaWarps, bool PERM = false, typename F>
 __device__ __forceinline__ void consume_slab(Ring& r, int rows, int K, const float* xs, int warp, int lane, F&& f) {
     const int nvec = K / Elem<T>::EPV;
     const int row_bytes = K * (int)sizeof(T);
@@ -219,19 +221,19 @@ __device__ __forceinline__ void consume_slab(Ring& r, int rows, int K, const flo
         const int n = min(rpc, rows - r0);
         r.wait(r.full0 + 8u * r.idx, r.phase, 2);
         const T* base = reinterpret_cast<const T*>(r.stages + (size_t)r.idx * r.stage_bytes);
-        if (n >= 2 * kMegaWarps) {
-            for (int i = 2 * warp; i < n; i += 2 * kMegaWarps) {
+        if (n >= 2 * NW) {
+            for (int i = 2 * warp; i < n; i += 2 * NW) {
                 const bool two = i + 1 < n;
                 float a0, a1;
-                smem_rows_dot2<T>(base + (size_t)i * K, base + (size_t)(two ? i + 1 : i) * K, nvec, xs, lane, a0, a1);
+                smem_rows_dot2<T, PERM>(base + (size_t)i * K, base + (size_t)(two ? i + 1 : i) * K, nvec, xs, lane, a0, a1);
                 f(r0 + i, a0);
                 if (two) f(r0 + i + 1, a1);
             }
         } else {
             // few long rows in the chunk: one row per warp keeps more warps busy
-            for (int i = warp; i < n; i += kMegaWarps) {
+            for (int i = warp; i < n; i += NW) {
                 float a0, a1;
-                smem_rows_dot2<T>(base + (size_t)i * K, base + (size_t)i * K, nvec, xs, lane, a0, a1);
+                smem_rows_dot2<T, PERM>(base + (size_t)i * K, base + (size_t)i * K, nvec, xs, lane, a0, a1);
                 f(r0 + i, a0);
             }
         }
@@ -242,7 +244,7 @@ __device__ __forceinline__ void consume_slab(Ring& r, int rows, int K, const flo
 }
 
 // Chunk-interleaved pair of slabs: f(local_row, dot_a, dot_b).
-template <typename T, typename F>
+template <typename T, int NW = kMegaWarps, bool PERM = false, typename F>
 __device__ __forceinline__ void consume_slab_pair(Ring& r, int rows, int K, const float* xs, int warp, int lane, F&& f) {
     const int nvec = K / Elem<T>::EPV;
     const int row_bytes = K * (int)sizeof(T);
@@ -257,9 +259,9 @@ __device__ __forceinline__ void consume_slab_pair(Ring& r, int rows, int K, cons
         r.advance();
         const T* A = reinterpret_cast<const T*>(r.stages + (size_t)ia * r.stage_bytes);
         const T* Bm = reinterpret_cast<const T*>(r.stages + (size_t)ib * r.stage_bytes);
-        for (int i = warp; i < n; i += kMegaWarps) {
+        for (int i = warp; i < n; i += NW) {
             float a0, a1;
-            smem_rows_dot2<T>(A + (size_t)i * K, Bm + (size_t)i * K, nvec, xs, lane, a0, a1);
+            smem_rows_dot2<T, PERM>(A + (size_t)i * K, Bm + (size_t)i * K, nvec, xs, lane, a0, a1);
             f(r0 + i, a0, a1);
         }
         __syncwarp();
@@ -268,14 +270,15 @@ __device__ __forceinline__ void consume_slab_pair(Ring& r, int rows, int K, cons
 }
 
 // Sum over the consumer threads; every consumer gets the total. `red` holds kMegaWarps floats.
+template <int NW = kMegaWarps>
 __device__ __forceinline__ float consumer_sum(float v, float* red, int warp, int lane) {
     v = warp_sum(v);
-    consumer_sync();                       // red may still be read from a previous use
+    consumer_sync<NW>();                   // red may still be read from a previous use
     if (lane == 0) red[warp] = v;
-    consumer_sync();
+    consumer_sync<NW>();
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < kMegaWarps; ++w) t += red[w];
+    for (int w = 0; w < NW; ++w) t += red[w];
     return t;
 }
 

@@ -24,8 +24,12 @@ struct SgemvGeom {
     int* err;
 };
 
+constexpr int kSgWarps = 31;                       // consumer warps (+ 1 producer warp = 1024 threads, 64 registers each)
+constexpr int kSgConsumers = kSgWarps * 32;
+constexpr int kSgThreads = kSgConsumers + 32;
+
 template <typename T, typename T2, typename KVT, int MODE>
-__global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvParams p, SgemvGeom g) {
+__global__ void __launch_bounds__(kSgThreads, 1) sgemv_kernel(StepCtl c, GemvParams p, SgemvGeom g) {
     extern __shared__ __align__(128) float sg_smem[];
     float* smem = sg_smem;
     float* xs = smem + g.off_xs;
@@ -42,7 +46,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
     const int rows = r_end - r_begin;
 
     Ring ring;
-    int* dead = reinterpret_cast<int*>(red + kMegaWarps);
+    int* dead = reinterpret_cast<int*>(red + kSgWarps);
     ring.full0 = smem_u32(smem + g.off_bar);
     ring.empty0 = ring.full0 + 8u * g.n_stages;
     ring.stages = reinterpret_cast<unsigned char*>(smem + g.off_ring);
@@ -56,14 +60,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
         *dead = 0;
         for (int i = 0; i < g.n_stages; ++i) {
             mbar_init(ring.full0 + 8u * i, 1);
-            mbar_init(ring.empty0 + 8u * i, kMegaWarps);
+            mbar_init(ring.empty0 + 8u * i, kSgWarps);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     pdl_launch_dependents();
 
-    if (warp == kMegaWarps) {
+    if (warp == kSgWarps) {
         // ---- producer: weights only, nothing here depends on the predecessor kernel ------------
         if (Kp > 0)
             issue_slab(ring, reinterpret_cast<const unsigned char*>(p.P) + (size_t)r_begin * Kp * sizeof(T2), rows,
@@ -83,40 +87,45 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
     // stage (and RMS-normalise) the activation vector: inference.cu:24-50, :83-95
     {
         const float* xr = p.xin + (size_t)bg * K;
+        constexpr int EPV = Elem<T>::EPV;
+        const int nvec = K / EPV;
         float ss = 0.f;
-        for (int k = tid; k < K; k += kMegaConsumers) {
+        for (int k = tid; k < K; k += kSgConsumers) {
             const float v = xr[k];
-            xs[k] = v;
+            xs[xs_index<EPV>(k, nvec)] = v;              // bank-conflict-free layout for the dot products
             ss = fmaf(v, v, ss);
         }
         if (Kp > 0) {
             const int t = c.tok[bg];
             const T2* trow = reinterpret_cast<const T2*>(p.Ptab) + (size_t)t * Kp;
-            for (int k = tid; k < Kp; k += kMegaConsumers) xs2[k] = Elem<T2>::get(trow, k);
+            for (int k = tid; k < Kp; k += kSgConsumers) xs2[xs_index<Elem<T2>::EPV>(k, Kp / Elem<T2>::EPV)] = Elem<T2>::get(trow, k);
         }
         if (p.do_norm) {
-            const float tot = consumer_sum(ss, red, warp, lane);
+            const float tot = consumer_sum<kSgWarps>(ss, red, warp, lane);
             const float r = sqrtf(tot / (float)K + p.eps);
-            for (int k = tid; k < K; k += kMegaConsumers) xs[k] = (xs[k] / r) * p.gain[k];
+            for (int k = tid; k < K; k += kSgConsumers) {
+                const int d = xs_index<EPV>(k, nvec);
+                xs[d] = (xs[d] / r) * p.gain[k];
+            }
         }
-        consumer_sync();
+        consumer_sync<kSgWarps>();
     }
     if (Kp > 0) {
-        consume_slab<T2>(ring, rows, Kp, xs2, warp, lane, [&](int r, float v) {
+        consume_slab<T2, kSgWarps, true>(ring, rows, Kp, xs2, warp, lane, [&](int r, float v) {
             if (lane == 0) pacc[r] = v;
         });
-        consumer_sync();
+        consumer_sync<kSgWarps>();
     }
 
     if (MODE == GEMV_SWIGLU) {
-        consume_slab_pair<T>(ring, rows, K, xs, warp, lane, [&](int r, float gt, float up) {
+        consume_slab_pair<T, kSgWarps, true>(ring, rows, K, xs, warp, lane, [&](int r, float gt, float up) {
             const int row = r_begin + r;
             if (p.wscale) { gt *= p.wscale[row]; up *= p.wscale_b[row]; }
             // applySiluToFFN + hadamardMultiplyFFN, inference.cu:262-281
             if (lane == 0 && active) p.y[(size_t)b * N + row] = (gt / (1.0f + expf(-gt))) * up;
         });
     } else if (MODE == GEMV_RAW || MODE == GEMV_RESID) {
-        consume_slab<T>(ring, rows, K, xs, warp, lane, [&](int r, float v) {
+        consume_slab<T, kSgWarps, true>(ring, rows, K, xs, warp, lane, [&](int r, float v) {
             const int row = r_begin + r;
             if (p.wscale) v *= p.wscale[row];
             if (Kp > 0) v += pacc[r];
@@ -129,10 +138,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
     } else if (MODE == GEMV_QKV) {
         // a CTA owns whole heads' worth of rows (rows_per_cta == hd) when the per-head norm is on,
         // else a 32-row group inside one head
-        consume_slab<T>(ring, rows, K, xs, warp, lane, [&](int r, float v) {
+        consume_slab<T, kSgWarps, true>(ring, rows, K, xs, warp, lane, [&](int r, float v) {
             if (lane == 0) outs[r] = p.wscale ? v * p.wscale[r_begin + r] : v;
         });
-        consumer_sync();
+        consumer_sync<kSgWarps>();
         const int hd = p.hd;
         const int seg_q = p.nq, seg_k = p.nq + p.nk, seg_v = seg_k + p.nv;
         const int seg = r_begin < seg_q ? 0 : (r_begin < seg_k ? 1 : (r_begin < seg_v ? 2 : 3));
@@ -140,14 +149,14 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
         if (p.qk_norm && seg < 2) {
             // getRMSColSumsAcrossHeads + applyRMSNormAcrossHeads, inference.cu:52-81, :97-111
             float ss = 0.f;
-            for (int r = tid; r < rows; r += kMegaConsumers) ss = fmaf(outs[r], outs[r], ss);
-            rs = sqrtf(consumer_sum(ss, red, warp, lane) / (float)hd + p.eps);
+            for (int r = tid; r < rows; r += kSgConsumers) ss = fmaf(outs[r], outs[r], ss);
+            rs = sqrtf(consumer_sum<kSgWarps>(ss, red, warp, lane) / (float)hd + p.eps);
         }
         if (active) {
             const int pos = c.pos[b];
             KVT* kpool = reinterpret_cast<KVT*>(p.kpool);
             KVT* vpool = reinterpret_cast<KVT*>(p.vpool);
-            for (int pr = tid; pr < rows / 2; pr += kMegaConsumers) {
+            for (int pr = tid; pr < rows / 2; pr += kSgConsumers) {
                 const int r = 2 * pr, row = r_begin + r;
                 float a = outs[r], cc = outs[r + 1];
                 if (seg < 2) {
@@ -190,19 +199,19 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
         // (inference.cu:720-743; host qsort of inference_orchestrator.cu:77-84 replaced)
         float bv = -INFINITY;
         int bi = 0x7fffffff;
-        consume_slab<T>(ring, rows, K, xs, warp, lane, [&](int r, float v) {
+        consume_slab<T, kSgWarps, true>(ring, rows, K, xs, warp, lane, [&](int r, float v) {
             const int row = r_begin + r;
             if (p.wscale) v *= p.wscale[row];
             if (lane == 0 && active) p.y[(size_t)b * N + row] = v;
             if (v > bv || (v == bv && row < bi)) { bv = v; bi = row; }
         });
-        consumer_sync();
+        consumer_sync<kSgWarps>();
         if (lane == 0) { outs[2 * warp] = bv; outs[2 * warp + 1] = __int_as_float(bi); }
-        consumer_sync();
+        consumer_sync<kSgWarps>();
         __shared__ int is_last;
         const int nparts = gridDim.x;
         if (tid == 0) {
-            for (int w = 1; w < kMegaWarps; ++w) {
+            for (int w = 1; w < kSgWarps; ++w) {
                 const float v = outs[2 * w];
                 const int ix = __float_as_int(outs[2 * w + 1]);
                 if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
@@ -213,7 +222,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) sgemv_kernel(StepCtl c, GemvP
             const int t = atomicAdd(&p.ticket[b], 1);
             is_last = (t == nparts - 1);
         }
-        consumer_sync();
+        consumer_sync<kSgWarps>();
         if (is_last && warp == 0) {
             __threadfence();
             float v2 = -INFINITY;
