@@ -5,7 +5,7 @@
 // are swapped so that the weight rows fill the MMA's M = 128 and the batch is the MMA's N
 // (16..256): a CTA owns 128 output features for a tile of up to 256 sequences.
 //   * one thread feeds a ring of shared-memory stages with TMA tensor loads (128-byte swizzle,
-//     no multicast): a [128 x 64] weight tile (two for gate/up) and the [Nb x 64] activation tile;
+//     one destination CTA): a [128 x 64] weight tile (two for gate/up) and the [Nb x 64] activation tile;
 //   * one thread issues tcgen05.mma (kind::f16, M128 x N=Nb x K16, four per stage) into TMEM and
 //     tcgen05.commit's the stage back to the loader;
 //   * all four warps read the accumulator with tcgen05.ld (warp w owns TMEM lanes 32w..32w+31 =

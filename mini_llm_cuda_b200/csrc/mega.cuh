@@ -6,7 +6,7 @@
 // sequence for the whole step:
 //   * every phase (projection, attention, FFN ...) splits its output rows over the CTAs; a CTA's
 //     rows are one contiguous slab of the row-major weight matrix;
-//   * a producer warp streams those slabs with cp.async.bulk (TMA, no multicast) into a ring of
+//   * a producer warp streams those slabs with cp.async.bulk (TMA; every CTA loads only its own data) into a ring of
 //     shared-memory stages guarded by mbarriers, running ahead of the consumers across phase
 //     boundaries, so that ~100+ KB per SM are in flight without holding registers;
 //   * 16 consumer warps compute dot products out of shared memory with the activation vector
@@ -90,7 +90,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t a, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// TMA bulk copy global -> this CTA's shared memory, completion counted on an mbarrier (no multicast).
+// TMA bulk copy global -> this CTA's shared memory, completion counted on an mbarrier; single destination CTA.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                  "r"(bytes), "r"(mbar)
