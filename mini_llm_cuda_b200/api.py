@@ -84,6 +84,7 @@ def lib() -> C.CDLL:
         "mlb_session_positions": (C.c_int, [vp, i32p]),
         "mlb_session_step_bytes": (C.c_int, [vp, u64p, u64p, u64p, u64p]),
         "mlb_session_launches_per_step": (C.c_int, [vp]),
+        "mlb_session_grid_timers": (C.c_int, [vp, C.POINTER(C.c_longlong), C.c_int]),
         "mlb_kv_alloc_new": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
         "mlb_kv_alloc_ensure": (C.c_int, [vp, C.c_int, C.c_int, C.c_int]),
         "mlb_kv_alloc_table": (C.c_int, [vp, C.c_int, i32p, C.c_int]),
@@ -287,6 +288,12 @@ class Session:
 
     def launches_per_step(self) -> int:
         return check(lib().mlb_session_launches_per_step(self._h))
+
+    def grid_timers(self) -> np.ndarray:
+        """[CTAs][16] cycle counters of the single-kernel step (MLB_GRID_TIMERS=1), else empty."""
+        buf = np.zeros(1024 * 16, dtype=np.int64)
+        n = check(lib().mlb_session_grid_timers(self._h, _ptr(buf, C.c_longlong), buf.size))
+        return buf[:n * 16].reshape(n, 16).copy()
 
     def close(self):
         if self._h:

@@ -17,6 +17,8 @@
 #include "gemm_tc.cuh"
 #include "tc_host.h"
 #include "mega.cuh"
+#include "grid_params.h"
+#include "grid_host.h"
 #include "model_file.h"
 #include "sgemv.cuh"
 
@@ -395,6 +397,11 @@ struct mlb_session {
     mlb::MegaLayer* mega_layers = nullptr;
     mlb::MegaParams mega;
     int* dev_err = nullptr;                 // set by a kernel whose bounded wait ran out
+    // whole-GPU single-kernel step (batch 1)
+    bool use_grid = false;
+    int grid_ctas = 0;
+    size_t grid_smem = 0;
+    mlb::GridParams grid;
     // tensor-core projections (bf16 weights, batch >= 16)
     bool use_tc = false;
     int tc_nb = 0, tc_stages = 0, tc_stages_swiglu = 0;
@@ -430,7 +437,8 @@ static int check_err_readback(mlb_session* s) {
     cudaMemsetAsync(s->dev_err, 0, 4, s->stream);
     cudaStreamSynchronize(s->stream);
     return fail(MLB_E_TIMEOUT, "a bounded device-side wait ran out (code %d: %s); the results of this call are invalid", code,
-                code == 1 ? "producer waiting for a free ring stage" : "consumer waiting for a weight chunk");
+                code == 1 ? "producer waiting for a free ring stage"
+                          : (code == 2 ? "consumer waiting for a weight chunk" : "consumer waiting for another CTA's results"));
 }
 
 static void free_session(mlb_session* s) {
@@ -647,6 +655,33 @@ struct Chain {
         return MLB_OK;
     }
 
+    // One decode (or prefill) step of a batch-1 session as a single cooperative kernel over all
+    // SMs (plus the sampler for top-k).
+    static int run_grid(mlb_session* s, int kind, const StepCtl& c, Recorder* rec, int* n_launches) {
+        GridParams gp = s->grid;
+        gp.with_lm_head = kind == CHAIN_PREFILL ? 0 : 1;
+        gp.do_pick = kind == CHAIN_GREEDY ? 1 : 0;
+        int rc, launches = 0;
+        if (rec) {
+            uint64_t w, kv, st, rows;
+            mlb_session_step_bytes(s, &w, &kv, &st, &rows);
+            if ((rc = rec->begin("grid_decode_step", w + kv + st + rows, 0))) return rc;
+        }
+        CU(grid_kernel_launch(s->m->cfg.weight_dtype, s->m->cfg.kv_dtype, s->grid_ctas, s->grid_smem, s->stream, c, gp));
+        if (rec && (rc = rec->end())) return rc;
+        ++launches;
+        if (kind == CHAIN_TOPK) {
+            SampleParams sp;
+            sp.logits = s->logits; sp.V = s->m->cfg.vocab; sp.top_k = s->cur_topk; sp.temperature = s->cur_temp; sp.seeds = s->seeds;
+            if (rec && (rc = rec->begin("sample_topk_philox", (uint64_t)s->B * s->m->cfg.vocab * 4 * 5, 0))) return rc;
+            CU(launch_chain(false, sample_topk_kernel, dim3(s->B), dim3(256), 0, s->stream, c, sp));
+            if (rec && (rc = rec->end())) return rc;
+            ++launches;
+        }
+        if (n_launches) *n_launches = launches;
+        return MLB_OK;
+    }
+
     // Shared-memory need and occupancy of the cluster kernel; 0 clusters = not usable here.
     static int cluster_probe(int cluster_size, size_t smem, int batch, int* max_clusters) {
         *max_clusters = 0;
@@ -827,6 +862,7 @@ struct Chain {
         const StepCtl c = make_ctl(s, kind);
         const int d = cfg.dim, F = cfg.ffn_dim, B = s->B, p = cfg.ple_dim;
         int launches = 0, rc;
+        if (s->use_grid) return run_grid(s, kind, c, rec, n_launches);
         if (s->use_cluster) return run_cluster(s, kind, c, rec, n_launches);
         if (s->use_tc) return run_tc(s, kind, c, rec, n_launches);
 
@@ -952,6 +988,26 @@ static int chain_configure(mlb_session* s) {
     return Chain<fp8_t, bf16_t, bf16_t>::configure();
 }
 
+// Device copy of the per-layer pointer table of the single-kernel steps.
+static int build_mega_layers(mlb_session* s) {
+    if (s->mega_layers) return MLB_OK;
+    const mlb_config& c = s->m->cfg;
+    std::vector<MegaLayer> hl(c.layers);
+    for (int i = 0; i < c.layers; ++i) {
+        const DevLayer& L = s->m->layers[i];
+        MegaLayer& M = hl[i];
+        std::memset(&M, 0, sizeof M);
+        M.type = L.type; M.n_qkv = L.n_qkv; M.nq = L.nq; M.nk = L.nk; M.nv = L.nv; M.ng = L.ng; M.o_in = L.o_in;
+        M.Wqkv = L.Wqkv; M.Sqkv = L.Sqkv; M.g1 = L.g1; M.g2 = L.g2; M.gq = L.gq; M.gk = L.gk;
+        M.Wo = L.Wo; M.So = L.So; M.W1a = L.W1a; M.W1b = L.W1b; M.W2 = L.W2; M.S1a = L.S1a; M.S1b = L.S1b; M.S2 = L.S2;
+        M.pleT = L.pleT; M.pleP = L.pleP; M.kpool = s->kpool[i]; M.vpool = s->vpool[i]; M.state = s->state[i];
+    }
+    int rc = sess_alloc(s, (void**)&s->mega_layers, hl.size() * sizeof(MegaLayer), false);
+    if (rc) return rc;
+    CU(cudaMemcpy(s->mega_layers, hl.data(), hl.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+    return MLB_OK;
+}
+
 static int chain_cluster_probe(mlb_session* s, int cluster_size, size_t smem, int* max_clusters) {
     const int w = s->m->cfg.weight_dtype, k = s->m->cfg.kv_dtype;
     if (w == MLB_DT_F32 && k == MLB_DT_F32) return Chain<float, float, float>::cluster_probe(cluster_size, smem, s->B, max_clusters);
@@ -1015,20 +1071,8 @@ static int setup_cluster_path(mlb_session* s) {
         int rc = chain_cluster_probe(s, C, smem, &max_clusters);
         if (rc) return rc;
         if (max_clusters < 1) continue;
-        // device copy of the per-layer pointer table
-        std::vector<MegaLayer> hl(c.layers);
-        for (int i = 0; i < c.layers; ++i) {
-            const DevLayer& L = s->m->layers[i];
-            MegaLayer& M = hl[i];
-            std::memset(&M, 0, sizeof M);
-            M.type = L.type; M.n_qkv = L.n_qkv; M.nq = L.nq; M.nk = L.nk; M.nv = L.nv; M.ng = L.ng; M.o_in = L.o_in;
-            M.Wqkv = L.Wqkv; M.Sqkv = L.Sqkv; M.g1 = L.g1; M.g2 = L.g2; M.gq = L.gq; M.gk = L.gk;
-            M.Wo = L.Wo; M.So = L.So; M.W1a = L.W1a; M.W1b = L.W1b; M.W2 = L.W2; M.S1a = L.S1a; M.S1b = L.S1b; M.S2 = L.S2;
-            M.pleT = L.pleT; M.pleP = L.pleP; M.kpool = s->kpool[i]; M.vpool = s->vpool[i]; M.state = s->state[i];
-        }
-        int rc2 = sess_alloc(s, (void**)&s->mega_layers, hl.size() * sizeof(MegaLayer), false);
+        int rc2 = build_mega_layers(s);
         if (rc2) return rc2;
-        CU(cudaMemcpy(s->mega_layers, hl.data(), hl.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
         mp.layers = s->mega_layers; mp.n_layers = c.layers;
         mp.d = c.dim; mp.F = c.ffn_dim; mp.V = c.vocab; mp.heads = c.heads; mp.kv_heads = c.kv_heads; mp.hd = c.head_dim;
         mp.dk = c.dn_key_dim; mp.dv = c.dn_value_dim; mp.ple = c.ple_dim; mp.qk_norm = c.qk_norm;
@@ -1047,13 +1091,220 @@ static int setup_cluster_path(mlb_session* s) {
     return MLB_OK;
 }
 
+// Decides whether the whole-GPU single-kernel step serves this session (batch 1) and lays out
+// its shared memory and exchange buffers. MLB_DECODE_PATH = chain | cluster | grid | auto; auto
+// takes it whenever the model fits its constraints.
+static int setup_grid_path(mlb_session* s) {
+    const mlb_config& c = s->m->cfg;
+    const char* env = std::getenv("MLB_DECODE_PATH");
+    const std::string mode = env ? env : "auto";
+    s->use_grid = false;
+    if (mode != "grid" && mode != "auto") return MLB_OK;
+    auto no = [&](const char* why) {
+        if (mode == "grid") return fail(MLB_E_UNSUPPORTED, "MLB_DECODE_PATH=grid: %s", why);
+        return (int)MLB_OK;
+    };
+    if (s->B != 1) return no("the whole-GPU step serves batch 1 only");
+    // auto: only where it was measured faster than the kernel chain. Its ~4.5 us per phase beat the
+    // chain's launches once the weights of a step take a few hundred microseconds to stream
+    // (1.05 vs 1.37 ms per token on a 1.2 GB FP8 model); on a 60 MB model the chain is ahead
+    // (172 vs 200 us per token).
+    if (mode == "auto" && mlb_model_weight_bytes(s->m) < (256ull << 20)) return MLB_OK;
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, s->m->device);
+    if (!coop) return no("the device has no cooperative launch");
+    const int epv = 16 / (int)elt_size(c.weight_dtype);
+    const int epv2 = c.weight_dtype == MLB_DT_F32 ? 4 : 8;
+    bool has_attn = false, has_dn = false;
+    int n_proj = 0, min_rows = std::min(c.dim, c.ffn_dim), a_dim = 16;
+    for (const DevLayer& L : s->m->layers) {
+        n_proj = std::max(n_proj, L.n_qkv);
+        min_rows = std::min(min_rows, L.n_qkv);
+        a_dim = std::max(a_dim, L.o_in);
+        if (L.type == MLB_LAYER_ATTENTION) has_attn = true; else has_dn = true;
+        if (L.o_in % epv) return no("a projection width is not a multiple of the weight vector");
+    }
+    if (c.dim % epv || c.ffn_dim % epv || (c.ple_dim > 0 && c.ple_dim % epv2)) return no("a projection width is not a multiple of the weight vector");
+    if (has_attn && c.head_dim != 64 && c.head_dim != 128) return no("head_dim must be 64 or 128");
+    if (has_attn && (c.heads % c.kv_heads || c.heads / c.kv_heads > 8)) return no("more than 8 query heads per kv head");
+    if (has_dn && c.dn_key_dim > 128) return no("delta-net key dim above 128");
+    const int C = std::min(s->sm_count, min_rows);
+    if (C < 8) return no("the model is too small to split over the SMs");
+    const int G = has_attn ? c.heads / c.kv_heads : 1;
+    auto up4 = [](int v) { return (v + 3) / 4 * 4; };
+    GridParams gp;
+    std::memset(&gp, 0, sizeof gp);
+    // context splits per kv head: enough items for every CTA; one head's partials fit 32 KB of shared memory
+    gp.s_max = has_attn ? std::max(1, std::min(C / c.kv_heads, 8192 / (c.head_dim + 2))) : 1;
+    const int n_parts = has_attn ? c.heads * gp.s_max * (c.head_dim + 2) : 0;
+    const int tmp_n = std::max(std::max(G * c.head_dim + 2 * c.head_dim + kGridAttnWarps * (c.head_dim + 2), 2 * c.heads * c.dn_key_dim + 2 * c.heads),
+                               64);
+    int off = 0;
+    gp.off_x = off; off += up4(c.dim);
+    gp.off_x2 = off; off += up4(c.dim);
+    gp.off_xn = off; off += up4(c.dim);
+    gp.off_proj = off; off += up4(std::max(n_proj, a_dim));
+    gp.off_parts = off; off += up4(std::max(has_attn ? std::max(gp.s_max * (c.head_dim + 2), kGridDirectWords) : 0, 2 * C));
+    gp.off_a = off; off += up4(a_dim);
+    gp.off_h = off; off += up4(c.ffn_dim);
+    gp.off_tmp = off; off += up4(tmp_n);
+    gp.off_ple = off; off += up4(std::max(c.ple_dim, 4));
+    gp.off_pacc = off; off += up4(c.dim / C + 8);
+    gp.off_red = off; off += 32;
+    gp.off_layers = off; off += up4((int)(c.layers * sizeof(MegaLayer) / 4));
+    gp.off_timers = off; off += 2 * kGridTimers;
+    int n_phases = 1 + (c.ple_dim > 0 ? 1 : 0);      // LM head, embedding rows
+    for (int i = 0; i < c.layers; ++i) n_phases += 4 + (c.ple_dim > 0 && i + 1 < c.layers ? 1 : 0);
+    gp.off_phases = off; off += n_phases * (int)(sizeof(GridPhase) / 4);
+    off = (off + 31) / 32 * 32;
+    const int max_stages = 12;
+    gp.off_bar = off; off += max_stages * 2 * 2;              // 8-byte barriers: full[] then empty[]
+    off = (off + 31) / 32 * 32;
+    gp.off_ring = off;
+    // ring: stages of whole rows, 16 KB unless a row is longer, as many as fit below ~208 KB
+    const size_t widest = (size_t)std::max(std::max(c.dim, c.ffn_dim), a_dim) * elt_size(c.weight_dtype);
+    gp.stage_bytes = (int)std::max<size_t>(16 * 1024, (widest + 1023) / 1024 * 1024);
+    const size_t fixed = (size_t)off * 4;
+    if (fixed + 3 * (size_t)gp.stage_bytes > 208 * 1024) return no("the activations leave too little shared memory for the weight ring");
+    gp.n_stages = (int)std::min<size_t>(max_stages, (208 * 1024 - fixed) / gp.stage_bytes);
+    const size_t smem = fixed + (size_t)gp.n_stages * gp.stage_bytes;
+    int per_sm = 0, rc;
+    if ((rc = grid_kernel_probe(c.weight_dtype, c.kv_dtype, smem, &per_sm))) return rc;
+    if (per_sm < 1) return no("the kernel does not fit an SM");
+    if ((rc = build_mega_layers(s))) return rc;
+    // exchange buffers (zeroed: epoch 0 is never produced) and the epoch word
+    const size_t n_ll = (size_t)2 * c.dim + n_proj + n_parts + a_dim + c.ffn_dim + 2 * (size_t)C + 64;
+    unsigned long long* ll = nullptr;
+    if ((rc = sess_alloc(s, (void**)&ll, n_ll * 8, true))) return rc;
+    gp.ll_xa = ll; ll += c.dim;
+    gp.ll_xb = ll; ll += c.dim;
+    gp.ll_proj = ll; ll += n_proj;
+    gp.ll_parts = ll; ll += n_parts;
+    gp.ll_a = ll; ll += a_dim;
+    gp.ll_h = ll; ll += c.ffn_dim;
+    gp.ll_lm = ll; ll += 2 * (size_t)C;
+    if ((rc = sess_alloc(s, (void**)&gp.epoch, 16, true))) return rc;
+    if (const char* t = std::getenv("MLB_GRID_TIMERS"))
+        if (t[0] == '1' && (rc = sess_alloc(s, (void**)&gp.timers, (size_t)C * kGridTimers * 8, true))) return rc;
+    // the phase list of one step
+    {
+        std::vector<GridPhase> ph;
+        int e = 0;                          // epochs used so far (offsets from the step's base)
+        int e_x = 0;                        // epoch of the residual stream in ll_xa (0: local in shared memory)
+        const size_t esz = elt_size(c.weight_dtype), psz = c.weight_dtype == MLB_DT_F32 ? 4 : 2;
+        auto blank = [&]() {
+            GridPhase d;
+            std::memset(&d, 0, sizeof d);
+            d.resid_off = -1;
+            d.nsrc_off = gp.off_x;
+            d.xs_off = gp.off_xn;
+            return d;
+        };
+        if (c.ple_dim > 0) {
+            GridPhase d = blank();          // embedding row + the first layer's per-layer embedding
+            const DevLayer& L0 = s->m->layers[0];
+            d.W = L0.pleP; d.N = c.dim; d.K = c.ple_dim; d.row_bytes = (int)(c.ple_dim * psz);
+            d.ple_table = L0.pleT; d.flags = GP_T2 | GP_FILL_PLE;
+            d.mode = RJ_RESID; d.dst = gp.ll_xa; d.e_off = ++e; d.resid_off = gp.off_x2; d.xs_off = gp.off_ple;
+            e_x = e;
+            ph.push_back(d);
+        }
+        for (int i = 0; i < c.layers; ++i) {
+            const DevLayer& L = s->m->layers[i];
+            const bool ple_next = c.ple_dim > 0 && i + 1 < c.layers;
+            int e1, e_a, e3, e4;
+            {
+                GridPhase d = blank();      // QKV (or delta-net) projections of the normalised residual stream
+                d.W = L.Wqkv; d.scale = L.Sqkv; d.N = L.n_qkv; d.K = c.dim; d.row_bytes = (int)(c.dim * esz);
+                d.gain = L.g1; d.nsrc_off = gp.off_x; d.xs_off = gp.off_xn;
+                if (e_x) { d.g_src = gp.ll_xa; d.g_n = c.dim; d.g_e_off = e_x; d.g_dst_off = gp.off_x; }
+                d.mode = RJ_STORE; d.dst = gp.ll_proj; d.e_off = e1 = ++e;
+                d.layer = i;
+                if (L.type == MLB_LAYER_ATTENTION) {
+                    d.flags = GP_MIX_ATTN; d.mix_e2_off = ++e; d.mix_ea_off = e_a = ++e;
+                } else {
+                    d.flags = GP_MIX_DELTA; d.mix_ea_off = e_a = ++e;
+                }
+                ph.push_back(d);
+            }
+            {
+                GridPhase d = blank();      // output projection + residual
+                d.W = L.Wo; d.scale = L.So; d.N = c.dim; d.K = L.o_in; d.row_bytes = (int)(L.o_in * esz);
+                d.g_src = gp.ll_a; d.g_n = L.o_in; d.g_perm = L.o_in / epv; d.g_e_off = e_a; d.g_dst_off = gp.off_a;
+                d.flags = GP_SKIP_GATHER_IF_READY;
+                d.xs_off = gp.off_a; d.mode = RJ_RESID; d.resid_off = gp.off_x; d.dst = gp.ll_xb; d.e_off = e3 = ++e;
+                d.layer = i;
+                ph.push_back(d);
+            }
+            {
+                GridPhase d = blank();      // FFN gate/up + SwiGLU
+                d.W = L.W1a; d.W2 = L.W1b; d.scale = L.S1a; d.scale2 = L.S1b; d.N = c.ffn_dim; d.K = c.dim; d.row_bytes = (int)(c.dim * esz);
+                d.g_src = gp.ll_xb; d.g_n = c.dim; d.g_e_off = e3; d.g_dst_off = gp.off_x2;
+                d.gain = L.g2; d.nsrc_off = gp.off_x2; d.xs_off = gp.off_xn;
+                d.flags = GP_PAIR; d.mode = RJ_SWIGLU; d.dst = gp.ll_h; d.e_off = e4 = ++e;
+                d.layer = i;
+                ph.push_back(d);
+            }
+            if (ple_next) {
+                GridPhase d = blank();      // the next layer's per-layer embedding, this CTA's rows
+                const DevLayer& Ln = s->m->layers[i + 1];
+                d.W = Ln.pleP; d.N = c.dim; d.K = c.ple_dim; d.row_bytes = (int)(c.ple_dim * psz);
+                d.ple_table = Ln.pleT; d.flags = GP_T2 | GP_FILL_PLE;
+                d.mode = RJ_PACC; d.xs_off = gp.off_ple;
+                d.layer = i;
+                ph.push_back(d);
+            }
+            {
+                GridPhase d = blank();      // FFN down + residual (+ that per-layer embedding)
+                d.W = L.W2; d.scale = L.S2; d.N = c.dim; d.K = c.ffn_dim; d.row_bytes = (int)(c.ffn_dim * esz);
+                d.g_src = gp.ll_h; d.g_n = c.ffn_dim; d.g_perm = c.ffn_dim / epv; d.g_e_off = e4; d.g_dst_off = gp.off_h;
+                d.xs_off = gp.off_h; d.mode = RJ_RESID; d.resid_off = gp.off_x2; d.dst = gp.ll_xa; d.e_off = ++e;
+                d.flags = ple_next ? GP_PACC_IN : 0;
+                d.layer = i;
+                e_x = e;
+                ph.push_back(d);
+            }
+        }
+        gp.e_total_nolm = e;
+        {
+            GridPhase d = blank();          // final norm + tied LM head
+            d.W = s->m->E; d.scale = s->m->Es; d.N = c.vocab; d.K = c.dim; d.row_bytes = (int)(c.dim * esz);
+            d.gain = s->m->g_final; d.nsrc_off = gp.off_x; d.xs_off = gp.off_xn;
+            if (e_x) { d.g_src = gp.ll_xa; d.g_n = c.dim; d.g_e_off = e_x; d.g_dst_off = gp.off_x; }
+            d.mode = RJ_LM; d.logits = s->logits; d.e_off = ++e; d.flags = GP_LM;
+            ph.push_back(d);
+        }
+        gp.e_total = e;
+        if ((int)ph.size() != n_phases) return fail(MLB_E_INVALID, "phase list of %zu entries, %d expected", ph.size(), n_phases);
+        GridPhase* dev = nullptr;
+        if ((rc = sess_alloc(s, (void**)&dev, ph.size() * sizeof(GridPhase), false))) return rc;
+        CU(cudaMemcpy(dev, ph.data(), ph.size() * sizeof(GridPhase), cudaMemcpyHostToDevice));
+        gp.phases = dev;
+        gp.n_phases = n_phases;
+    }
+    gp.layers = s->mega_layers; gp.n_layers = c.layers;
+    gp.d = c.dim; gp.F = c.ffn_dim; gp.V = c.vocab; gp.heads = c.heads; gp.kv_heads = c.kv_heads; gp.hd = c.head_dim;
+    gp.dk = c.dn_key_dim; gp.dv = c.dn_value_dim; gp.ple = c.ple_dim; gp.qk_norm = c.qk_norm;
+    gp.eps = c.rms_eps; gp.l2_eps = 1e-6f;
+    gp.E = s->m->E; gp.Es = s->m->Es; gp.g_final = s->m->g_final; gp.rope = s->m->rope;
+    gp.page_table = s->page_table; gp.pt_stride = s->max_pages; gp.logits = s->logits;
+    gp.err = s->dev_err;
+    gp.backoff_ns = 100;
+    if (const char* v = std::getenv("MLB_GRID_BACKOFF_NS")) gp.backoff_ns = std::max(0, std::min(10000, std::atoi(v)));
+    s->grid = gp;
+    s->grid_ctas = C;
+    s->grid_smem = smem;
+    s->use_grid = true;
+    return MLB_OK;
+}
+
 // Tensor-core projections for large batches: bf16 weights, batch >= 16 (MLB_GEMM=simt turns it off).
 static int setup_tc_path(mlb_session* s) {
     const mlb_config& c = s->m->cfg;
     s->use_tc = false;
     const char* env = std::getenv("MLB_GEMM");
     const std::string mode = env ? env : "auto";
-    if (mode == "simt" || s->use_cluster) return MLB_OK;
+    if (mode == "simt" || s->use_cluster || s->use_grid) return MLB_OK;
     if (c.weight_dtype != MLB_DT_BF16) {
         if (mode == "tc") return fail(MLB_E_UNSUPPORTED, "MLB_GEMM=tc needs bf16 weights");
         return MLB_OK;
@@ -1110,6 +1361,12 @@ static int ensure_graph(mlb_session* s, int kind) {
         s->graphs[kind] = nullptr;
     }
     if (s->graphs[kind]) return MLB_OK;
+    if (s->use_grid) {
+        // one cooperative launch per step (plus the sampler): launched directly, nothing to capture
+        s->launches_per_step[kind] = kind == CHAIN_TOPK ? 2 : 1;
+        if (kind == CHAIN_TOPK) { s->g_topk = s->cur_topk; s->g_temp = s->cur_temp; }
+        return MLB_OK;
+    }
     cudaGraph_t graph = nullptr;
     CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
     int n = 0;
@@ -1122,6 +1379,13 @@ static int ensure_graph(mlb_session* s, int kind) {
     if (e != cudaSuccess) return fail(MLB_E_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
     s->launches_per_step[kind] = n;
     if (kind == CHAIN_TOPK) { s->g_topk = s->cur_topk; s->g_temp = s->cur_temp; }
+    return MLB_OK;
+}
+
+// One step on the session's stream: the captured chain, or the single cooperative kernel.
+static int launch_step(mlb_session* s, int kind) {
+    if (s->use_grid) return chain_run(s, kind, nullptr, nullptr);
+    CU(cudaGraphLaunch(s->graphs[kind], s->stream));
     return MLB_OK;
 }
 
@@ -1264,6 +1528,7 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     SA(sess_alloc(s, (void**)&s->dev_err, 4, true));
     SA(chain_configure(s));
     SA(setup_cluster_path(s));
+    if (!s->use_cluster) SA(setup_grid_path(s));
     SA(setup_tc_path(s));
 #undef SA
 #undef SCU
@@ -1336,7 +1601,8 @@ extern "C" int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t*
     CU(cudaStreamSynchronize(s->stream));
     if (max_len > 1) {
         if ((rc = ensure_graph(s, CHAIN_PREFILL))) return rc;
-        for (int t = 0; t < max_len - 1; ++t) CU(cudaGraphLaunch(s->graphs[CHAIN_PREFILL], s->stream));
+        for (int t = 0; t < max_len - 1; ++t)
+            if ((rc = launch_step(s, CHAIN_PREFILL))) return rc;
     }
     if ((rc = queue_err_readback(s))) return rc;
     CU(cudaStreamSynchronize(s->stream));
@@ -1382,7 +1648,7 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
             }
             CU(cudaEventRecord(ev[2 * i], s->stream));
         }
-        CU(cudaGraphLaunch(s->graphs[kind], s->stream));
+        if ((rc = launch_step(s, kind))) return rc;
         if (step_ms) CU(cudaEventRecord(ev[2 * i + 1], s->stream));
     }
     // result: ring [B][max_ctx] -> out [B][n]
@@ -1518,6 +1784,18 @@ extern "C" int mlb_session_step_bytes(mlb_session* s, uint64_t* weights, uint64_
     if (state) *state = st;
     if (rows) *rows = rw;
     return MLB_OK;
+}
+
+extern "C" int mlb_session_grid_timers(mlb_session* s, long long* out, int cap) {
+    if (!s || !out) return fail(MLB_E_INVALID, "null argument");
+    if (!s->use_grid || !s->grid.timers) return 0;
+    CU(cudaSetDevice(s->m->device));
+    const int n = s->grid_ctas * kGridTimers;
+    if (cap < n) return fail(MLB_E_INVALID, "room for %d counters needed, %d given", n, cap);
+    CU(cudaStreamSynchronize(s->stream));
+    CU(cudaMemcpy(out, s->grid.timers, (size_t)n * 8, cudaMemcpyDeviceToHost));
+    CU(cudaMemset(s->grid.timers, 0, (size_t)n * 8));
+    return s->grid_ctas;
 }
 
 extern "C" int mlb_session_launches_per_step(mlb_session* s) {

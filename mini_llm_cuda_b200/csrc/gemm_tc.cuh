@@ -137,12 +137,22 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
     const uint32_t tmem_base = *tmem_slot;
 
     pdl_launch_dependents();
-    pdl_wait();                      // the activation operand comes from the predecessor kernel
-
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ---------------------------------------------------------------------
+        // The weight tiles of the first stages depend on nothing: they are on their way before this
+        // kernel waits for its predecessor, whose results only the activation tiles need.
         const uint32_t tx = (uint32_t)stage_bytes;
-        for (int kb = 0; kb < nkb; ++kb) {
+        const int pre = min(p.stages, nkb);
+        for (int kb = 0; kb < pre; ++kb) {
+            mbar_expect_tx(full0 + 8u * kb, tx);
+            const uint32_t base = smem_u32(smem + (size_t)kb * stage_bytes);
+            tma_load_2d(base, &tmA, kb * kTcKB, m0, full0 + 8u * kb);
+            if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes, &tmA2, kb * kTcKB, m0, full0 + 8u * kb);
+        }
+        pdl_wait();                  // the activation operand comes from the predecessor kernel
+        for (int kb = 0; kb < pre; ++kb)
+            tma_load_2d(smem_u32(smem + (size_t)kb * stage_bytes) + NA * a_bytes, &tmB, kb * kTcKB, b0, full0 + 8u * kb);
+        for (int kb = pre; kb < nkb; ++kb) {
             const int s = kb % p.stages;
             const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
             if (!tc_wait(empty0 + 8u * s, ph ^ 1u, p.err, 11)) break;
@@ -152,7 +162,10 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
             if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes, &tmA2, kb * kTcKB, m0, full0 + 8u * s);
             tma_load_2d(base + NA * a_bytes, &tmB, kb * kTcKB, b0, full0 + 8u * s);
         }
-    } else if (warp == 1 && lane == 0) {
+    } else {
+        pdl_wait();
+    }
+    if (warp == 1 && lane == 0) {
         // ---- MMA issuer ------------------------------------------------------------------------
         const uint32_t idesc = umma_idesc_bf16(kTcM, p.Nb);
         for (int kb = 0; kb < nkb; ++kb) {

@@ -40,6 +40,7 @@ struct MegaLayer {
     void *kpool, *vpool;
     float* state;
 };
+static_assert(sizeof(MegaLayer) % 8 == 0, "MegaLayer is copied in 8-byte words");
 
 struct MegaParams {
     const MegaLayer* layers;
@@ -126,13 +127,28 @@ struct Ring {
     uint32_t phase;
     volatile int* dead;            // shared flag: a wait ran out somewhere in this CTA
     int* err;
+    long long wait_cycles;         // diagnostic: cycles spent in wait()
+    unsigned backoff_ns;           // producer: pause between polls for a free stage (0: none)
     __device__ __forceinline__ void advance() {
         if (++idx == nst) { idx = 0; phase ^= 1u; }
     }
     __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, int code) {
         if (*dead) return false;
-        for (uint32_t i = 0; i < kMegaSpinLimit; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
+#ifdef MLB_GRID_TIMERS
+        const long long t0 = clock64();
+#endif
+#pragma unroll 1
+        for (uint32_t i = 0; i < kMegaSpinLimit; ++i) {
+            if (mbar_try_wait(bar, parity)) {
+#ifdef MLB_GRID_TIMERS
+                wait_cycles += clock64() - t0;
+#endif
+                return true;
+            }
+            // the producer runs stages ahead: while the ring is full it polls at leisure and leaves the
+            // issue slots and the shared-memory pipe to the consumers
+            if (code == 1 && backoff_ns) __nanosleep(backoff_ns);
+        }
         *dead = 1;
         atomicExch(err, code);
         return false;
@@ -751,6 +767,8 @@ __global__ void __launch_bounds__(kMegaThreads, 1) mega_decode_kernel(StepCtl c,
     k.ring.phase = 0;
     k.ring.dead = dead;
     k.ring.err = p.err;
+    k.ring.wait_cycles = 0;
+    k.ring.backoff_ns = 0;
     if (threadIdx.x == 0) {
         *dead = 0;
         for (int i = 0; i < p.n_stages; ++i) {

@@ -56,6 +56,8 @@ __global__ void __launch_bounds__(kSgThreads, 1) sgemv_kernel(StepCtl c, GemvPar
     ring.phase = 0;
     ring.dead = dead;
     ring.err = g.err;
+    ring.wait_cycles = 0;
+    ring.backoff_ns = 0;
     if (tid == 0) {
         *dead = 0;
         for (int i = 0; i < g.n_stages; ++i) {

@@ -2,6 +2,7 @@
 against the logits of the reference's own PyTorch script. Integer results (token ids) must be
 identical; logits within 1e-3 (fp32) / 2e-2 (bf16, FP8) of the oracle, in the metric of
 helpers.logits_error."""
+import dataclasses
 import os
 import sys
 
@@ -57,13 +58,14 @@ def tol_of(spec):
     return TOL_FP32 if spec.weight_dtype == "float32" and spec.kv_dtype == "float32" else TOL_LOWP
 
 
-@pytest.mark.parametrize("path_mode", ["cluster", "chain", "chain_thread"])
+@pytest.mark.parametrize("path_mode", ["grid", "cluster", "chain", "chain_thread"])
 @pytest.mark.parametrize("name", list(SPECS))
 def test_greedy_rollout_matches_oracle(api, tmp_path, monkeypatch, name, path_mode):
     """Batch 1: 20-token prompt, 48 greedy tokens: identical ids, logits within tolerance at
-    every step (context crosses three KV pages). Run through the decode paths: the single-kernel
-    cluster step, the kernel chain with TMA-streamed GEMVs, the chain with per-thread-load GEMVs."""
-    monkeypatch.setenv("MLB_DECODE_PATH", "cluster" if path_mode == "cluster" else "chain")
+    every step (context crosses three KV pages). Run through the decode paths: the whole-GPU
+    single-kernel step, the single-kernel cluster step, the kernel chain with TMA-streamed GEMVs,
+    the chain with per-thread-load GEMVs."""
+    monkeypatch.setenv("MLB_DECODE_PATH", path_mode if path_mode in ("grid", "cluster") else "chain")
     monkeypatch.setenv("MLB_GEMV", "thread" if path_mode == "chain_thread" else "auto")
     spec = SPECS[name]
     path = write_model(tmp_path, spec, seed=3)
@@ -83,6 +85,28 @@ def test_greedy_rollout_matches_oracle(api, tmp_path, monkeypatch, name, path_mo
             break
     assert worst < tol_of(spec), f"{name}: logits error {worst}"
     assert got == want_tok[:len(got)].tolist() and len(got) == 48
+    sess.close()
+    model.close()
+
+
+@pytest.mark.parametrize("name", ["gqa", "qknorm_gating", "bf16", "fp8", "hd128"])
+def test_grid_step_long_context_matches_oracle(api, tmp_path, monkeypatch, name):
+    """The whole-GPU single-kernel step with a context long enough for several context splits per
+    kv head (more than 8 KV pages): 150-token prompt, 40 greedy tokens, sampled tokens afterwards."""
+    monkeypatch.setenv("MLB_DECODE_PATH", "grid")
+    spec = SPECS[name]
+    spec = dataclasses.replace(SPECS[name], max_context=512)
+    path = write_model(tmp_path, spec, seed=13)
+    oracle = load_oracle(path)
+    prompt = random_prompts(spec.vocab, [150], seed=17)[0]
+    want_tok, want_logits = oracle_rollout(oracle, prompt, 40)
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    sess.prefill([prompt])
+    assert sess.launches_per_step() == 1
+    got = sess.decode(40)[0]
+    assert got.tolist() == want_tok.tolist()
+    assert logits_error(sess.logits()[0], want_logits[-1]) < tol_of(spec)
     sess.close()
     model.close()
 
@@ -343,7 +367,7 @@ def test_cfg1_latency_config_bf16(api, tmp_path):
     assert (ms > 0).all()
     stats = sess.profile(2, False)
     names = {s["name"] for s in stats}
-    assert names == {"cluster_decode_step"} or names >= {"qkv_gemv_norm_rope_kvappend", "attn_flash_decode_paged",
+    assert names == {"grid_decode_step"} or names == {"cluster_decode_step"} or names >= {"qkv_gemv_norm_rope_kvappend", "attn_flash_decode_paged",
                                                          "deltanet_state_update", "lmhead_gemv_norm_argmax"}
     sess.close()
     model.close()
