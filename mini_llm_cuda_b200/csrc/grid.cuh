@@ -68,7 +68,7 @@ struct GridCtx {
 // Returns the sum of squares of the values this thread fetched (for the RMS norm that follows).
 template <int EPV>
 __device__ __forceinline__ float ll_gather(const unsigned long long* src, int n, uint32_t e, float* dst, int perm_nvec, GridCtx& k) {
-    constexpr int U = 4;
+    constexpr int U = 4;               // words in flight per thread
     float ss = 0.f;
 #pragma unroll 1
     for (int i0 = k.tid; i0 < n; i0 += kMegaConsumers * U) {
@@ -477,6 +477,7 @@ __device__ __forceinline__ void grid_combine(const GridParams& p, const MegaLaye
     float* parts = k.smem + p.off_parts;
     float* gate = k.smem + p.off_proj;
     float* abuf = k.smem + p.off_a;
+    float* scales = k.smem + p.off_tmp;       // [heads in this pass][S]
     const int seg_v = L.nq + L.nk + L.nv;
     const int n_a = p.heads * hd;
     const int h_first = direct ? 0 : k.rank, h_step = direct ? p.heads : k.C, h_count = direct ? p.heads : 1;
@@ -485,19 +486,28 @@ __device__ __forceinline__ void grid_combine(const GridParams& p, const MegaLaye
         ll_gather<4>(p.ll_parts + (size_t)h0 * S * (hd + 2), h_count * S * (hd + 2), e_parts, parts, 0, k);
         if (L.ng) ll_gather<4>(p.ll_proj + seg_v + (size_t)h0 * hd, h_count * hd, e_proj, gate, 0, k);
         consumer_sync();
+        // per (head, split): the factor that brings the split's sums to the head's common maximum
 #pragma unroll 1
-        for (int i = tid; i < h_count * hd; i += kMegaConsumers) {
-            const int hl = i / hd, e = i - hl * hd;
+        for (int i = tid; i < h_count * S; i += kMegaConsumers) {
+            const int hl = i / S;
             const float* pp = parts + (size_t)hl * S * (hd + 2);
             float mn = kNegBig;
 #pragma unroll 1
             for (int s = 0; s < S; ++s) mn = fmaxf(mn, pp[(size_t)s * (hd + 2) + hd]);
-            float lt = 0.f, at = 0.f;
+            scales[i] = expf(parts[(size_t)i * (hd + 2) + hd] - mn);
+        }
+        consumer_sync();
 #pragma unroll 1
+        for (int i = tid; i < h_count * hd; i += kMegaConsumers) {
+            const int hl = i / hd, e = i - hl * hd;
+            const float* pp = parts + (size_t)hl * S * (hd + 2);
+            const float* scl = scales + (size_t)hl * S;
+            float lt = 0.f, at = 0.f;
+#pragma unroll 4
             for (int s = 0; s < S; ++s) {
-                const float sc = expf(pp[(size_t)s * (hd + 2) + hd] - mn);
-                lt += pp[(size_t)s * (hd + 2) + hd + 1] * sc;
-                at += pp[(size_t)s * (hd + 2) + e] * sc;
+                const float sc = scl[s];
+                lt = fmaf(pp[(size_t)s * (hd + 2) + hd + 1], sc, lt);
+                at = fmaf(pp[(size_t)s * (hd + 2) + e], sc, at);
             }
             float o = at / lt;
             if (L.ng) o *= 1.0f / (1.0f + expf(-gate[i]));      // sigmoid of the gate projection (inference.cu:248)
