@@ -655,6 +655,15 @@ struct Chain {
         return MLB_OK;
     }
 
+    // Launch shape of the embedding kernel: with per-layer embeddings and a small batch, the rows
+    // of a sequence are spread over several CTAs of 64 threads (one projection row per thread).
+    static int embed_split(int B, int d, int ple) {
+        if (ple <= 0) return 1;
+        return std::max(1, std::min((d + 63) / 64, 128 / std::max(1, B)));
+    }
+    static dim3 embed_grid(int B, int d, int ple) { return dim3(B, embed_split(B, d, ple)); }
+    static dim3 embed_block(int B, int d, int ple) { return dim3(embed_split(B, d, ple) > 1 ? 64 : 256); }
+
     // One decode (or prefill) step of a batch-1 session as a single cooperative kernel over all
     // SMs (plus the sampler for top-k).
     static int run_grid(mlb_session* s, int kind, const StepCtl& c, Recorder* rec, int* n_launches) {
@@ -767,7 +776,7 @@ struct Chain {
             return MLB_OK;
         };
         if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * d * 6, 0))) return rc;
-        CU(launch_chain(s->use_pdl, embed_kernel<T, T2>, dim3(B), dim3(256), (size_t)ple * 4, s->stream, c, static_cast<const T*>(m->E),
+        CU(launch_chain(s->use_pdl, embed_kernel<T, T2>, embed_grid(B, d, ple), embed_block(B, d, ple), (size_t)ple * 4, s->stream, c, static_cast<const T*>(m->E),
                         static_cast<const float*>(m->Es), d, static_cast<const T2*>(m->layers[0].pleT),
                         static_cast<const T2*>(m->layers[0].pleP), ple, s->x));
         if (rec && (rc = rec->end())) return rc;
@@ -867,7 +876,7 @@ struct Chain {
         if (s->use_tc) return run_tc(s, kind, c, rec, n_launches);
 
         if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * (d * sizeof(T) + (uint64_t)p * sizeof(T2) + (uint64_t)d * 4) + (uint64_t)d * p * sizeof(T2), 0))) return rc;
-        CU(launch_chain(s->use_pdl, embed_kernel<T, T2>, dim3(B), dim3(256), (size_t)p * 4, s->stream, c,
+        CU(launch_chain(s->use_pdl, embed_kernel<T, T2>, embed_grid(B, d, p), embed_block(B, d, p), (size_t)p * 4, s->stream, c,
                         static_cast<const T*>(m->E), static_cast<const float*>(m->Es), d, static_cast<const T2*>(m->layers[0].pleT),
                         static_cast<const T2*>(m->layers[0].pleP), p, s->x));
         if (rec && (rc = rec->end())) return rc;

@@ -174,12 +174,15 @@ __global__ void embed_kernel(StepCtl c, const T* __restrict__ E, const float* __
     }
     float sc = escale ? escale[t] : 1.0f;
     constexpr int EPV2 = Elem<T2>::EPV;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    // grid.y CTAs share the rows of one sequence: a single CTA walking all of them was the
+    // slowest launch of a batch-1 step
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < d; i += gridDim.y * blockDim.x) {
         float v = Elem<T>::get(E, (size_t)t * d + i) * sc;
         if (p > 0) {
             // one row of the projection per thread, 16-byte loads (p is a multiple of 8)
             float a = 0.f;
             const T2* prow = pleP + (size_t)i * p;
+#pragma unroll 4
             for (int j = 0; j < p; j += EPV2) {
                 float w[EPV2];
                 Elem<T2>::load_vec(prow + j, w);
@@ -680,38 +683,79 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     const KVT* kpool = reinterpret_cast<const KVT*>(p.kpool);
     const KVT* vpool = reinterpret_cast<const KVT*>(p.vpool);
 
-    for (int pg = pg_begin + warp; pg < pg_end; pg += NW) {
-        const int page = p.page_table[(size_t)b * p.pt_stride + pg];
+    // This warp's pages: pg_begin + warp + NW * i. Lane i holds the pool index of the i-th one
+    // (refreshed every 32 pages), so that the page loop does not start with a dependent load.
+    constexpr int ITERS = kKvBlock / PPI;
+    constexpr int CH = ITERS < 4 ? ITERS : 4;      // positions per lane group handled together
+    const int* pt = p.page_table + (size_t)b * p.pt_stride;
+    const int span = pg_end - pg_begin - warp;
+    const int npw = span > 0 ? (span + NW - 1) / NW : 0;
+    int pidx = 0;
+    for (int i = 0; i < npw; ++i) {
+        if ((i & 31) == 0) {
+            const int ii = i + lane;
+            pidx = ii < npw ? pt[pg_begin + warp + NW * ii] : 0;
+        }
+        const int pg = pg_begin + warp + NW * i;
+        const int page = __shfl_sync(0xffffffffu, pidx, i & 31);
         const int cnt = min(kKvBlock, ctx - pg * kKvBlock);
         const size_t base = ((size_t)page * p.kv_heads + kvh) * kKvBlock * HD;
 #pragma unroll
-        for (int j0 = 0; j0 < kKvBlock; j0 += PPI) {
-            const int j = j0 + grp;
-            const bool valid = j < cnt;
-            float kv[EPL], vv[EPL];
-            if (valid) {
-                Elem<KVT>::load_vec_cg(kpool + base + (size_t)j * HD + lr * EPL, kv);
-                Elem<KVT>::load_vec_cg(vpool + base + (size_t)j * HD + lr * EPL, vv);
-            } else {
+        for (int c0 = 0; c0 < ITERS; c0 += CH) {
+            // all loads of the chunk first, then the scores of its positions (independent of one
+            // another), one rescale of the running sums and one exponential per position
+            uint4 kk[CH], vv4[CH];
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) { kv[e] = 0.f; vv[e] = 0.f; }
+            for (int u = 0; u < CH; ++u) {
+                const int j = (c0 + u) * PPI + grp;
+                kk[u] = make_uint4(0, 0, 0, 0);
+                vv4[u] = make_uint4(0, 0, 0, 0);
+                if (j < cnt) {
+                    kk[u] = __ldcg(reinterpret_cast<const uint4*>(kpool + base + (size_t)j * HD + lr * EPL));
+                    vv4[u] = __ldcg(reinterpret_cast<const uint4*>(vpool + base + (size_t)j * HD + lr * EPL));
+                }
+            }
+            float sv[G][CH];
+#pragma unroll
+            for (int u = 0; u < CH; ++u) {
+                const bool valid = (c0 + u) * PPI + grp < cnt;
+                float kv[EPL];
+                Elem<KVT>::unpack(kk[u], kv);
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float sdot = 0.f;
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) sdot = fmaf(q[g][e], kv[e], sdot);
+#pragma unroll
+                    for (int o = LPR / 2; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
+                    sv[g][u] = valid ? sdot / inv_div : kNegBig;
+                }
             }
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                float s = 0.f;
+                float mn = m[g];
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) s = fmaf(q[g][e], kv[e], s);
+                for (int u = 0; u < CH; ++u) mn = fmaxf(mn, sv[g][u]);
+                const float sc = expf(m[g] - mn);
+                l[g] *= sc;
 #pragma unroll
-                for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                s = s / inv_div;
-                if (valid) {
-                    float mn = fmaxf(m[g], s);
-                    float sc = expf(m[g] - mn), pe = expf(s - mn);
-                    l[g] = l[g] * sc + pe;
+                for (int e = 0; e < EPL; ++e) acc[g][e] *= sc;
 #pragma unroll
-                    for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * sc + pe * vv[e];
-                    m[g] = mn;
+                for (int u = 0; u < CH; ++u) {
+                    const bool valid = (c0 + u) * PPI + grp < cnt;
+                    sv[g][u] = valid ? expf(sv[g][u] - mn) : 0.f;
+                    l[g] += sv[g][u];
                 }
+                m[g] = mn;
+            }
+#pragma unroll
+            for (int u = 0; u < CH; ++u) {
+                float vv[EPL];
+                Elem<KVT>::unpack(vv4[u], vv);
+#pragma unroll
+                for (int g = 0; g < G; ++g)
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) acc[g][e] = fmaf(sv[g][u], vv[e], acc[g][e]);
             }
         }
     }
