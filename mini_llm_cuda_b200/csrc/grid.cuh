@@ -176,16 +176,17 @@ __device__ __forceinline__ float smem_row_dot(const T* row, int nvec, const floa
     return warp_sum(a0 + a1);
 }
 
-// Lane 0 of the row's warp: finish local row r. (bv, bi): running argmax of RJ_LM.
-__device__ __forceinline__ void row_done(const RowsJob& j, int r, float v, float u, float& bv, int& bi) {
+// Lane 0 of the row's warp: finish local row r (sv, su: the row's weight scales). (bv, bi): running
+// argmax of RJ_LM.
+__device__ __forceinline__ void row_done(const RowsJob& j, int r, float v, float u, float sv, float su, float& bv, int& bi) {
     const int row = j.r0 + r;
+    v *= sv;
     if (j.mode == RJ_SWIGLU) {
-        if (j.scale) { v *= j.scale[row]; u *= j.scale2[row]; }
+        u *= su;
         // applySiluToFFN + hadamardMultiplyFFN, inference.cu:262-281
         ll_store(j.dst + row, (v / (1.0f + expf(-v))) * u, j.epoch);
         return;
     }
-    if (j.scale) v *= j.scale[row];
     if (j.mode == RJ_STORE) {
         ll_store(j.dst + row, v, j.epoch);
     } else if (j.mode == RJ_RESID) {
@@ -223,9 +224,12 @@ __device__ __forceinline__ void consume_rows(Ring& r, const RowsJob& j, bool pai
 #pragma unroll 1
         for (; wrow < c0 + n; wrow += NW) {
             const size_t off = (size_t)(wrow - c0) * K;
+            // the row's scales come from global memory: asked for before the dot products, used after
+            const float sv = j.scale ? j.scale[j.r0 + wrow] : 1.0f;
+            const float su = (pair && j.scale2) ? j.scale2[j.r0 + wrow] : 1.0f;
             const float a = smem_row_dot<T>(A + off, nvec, j.xs, lane);
             const float b = pair ? smem_row_dot<T>(Bm + off, nvec, j.xs, lane) : 0.f;
-            if (lane == 0) row_done(j, wrow, a, b, bv, bi);
+            if (lane == 0) row_done(j, wrow, a, b, sv, su, bv, bi);
         }
         __syncwarp();
         if (lane == 0) {
