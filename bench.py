@@ -44,6 +44,8 @@ NCU_TRAFFIC_BYTES = {
     "oproj_gemv_residual": 557312,
     "deltanet_proj_gemv_norm": 1621504,
     "lmhead_gemv_norm_argmax": 8433408,
+    # whole-GPU single-kernel step on cfg4 (profiles/ncu_full_grid_decode_cfg4_b1.md)
+    "grid_decode_step": 1156106000,
 }
 
 # workload name -> (model, batch per GPU at N=1, prompt length, description)

@@ -173,7 +173,7 @@ int mlb_op_attn_decode(const void* kpool, const void* vpool, int kv_dtype, const
 
 /* Stand-alone batched projection on the tensor cores (tcgen05 + TMEM, TMA-fed), DEVICE pointers:
  * the kernel that replaces the reference's cublasGemmEx projections (inference.cu:401-465,
- * :581-602, :623-695, :720-743) once the batch is >= 16. W [N][K] bf16 row-major, X [batch][K]
+ * :581-602, :623-695, :720-743) once the batch is >= 4. W [N][K] bf16 row-major, X [batch][K]
  * bf16; K a multiple of 8. Three forms, chosen by the optional pointers:
  *   plain      out fp32 [batch][N] = X W^T
  *   residual   out fp32 [batch][N] = X W^T + resid (resid may alias out)
@@ -199,6 +199,13 @@ int mlb_op_attn_decode_static(const void* kpool, const void* vpool, int kv_dtype
                               const float* gate_or_null, float* out, int batch, int heads, int kv_heads,
                               int head_dim, int splits, void* stream);
 size_t mlb_op_attn_decode_static_capacity(void);
+
+/* No counterpart in the reference. Exercises the bounded wait that every streaming kernel of the
+ * library uses: a one-thread kernel waits on `device` for a shared-memory barrier that nothing
+ * completes, gives up after `max_polls` polls (1..2^20, a few milliseconds at most) and records an
+ * error code the way those kernels do. Returns MLB_E_TIMEOUT (the expected outcome) once the
+ * kernel has ended; the CUDA context stays usable. */
+int mlb_op_wait_probe(int device, uint32_t max_polls);
 
 /* RoPE table exactly as getPreComputedRopeTheta builds it (inference.h:4,
  * inference.cu:364-374): [max_len][head_dim] interleaved (cos, sin), host float math. */

@@ -85,6 +85,7 @@ def lib() -> C.CDLL:
         "mlb_session_step_bytes": (C.c_int, [vp, u64p, u64p, u64p, u64p]),
         "mlb_session_launches_per_step": (C.c_int, [vp]),
         "mlb_session_grid_timers": (C.c_int, [vp, C.POINTER(C.c_longlong), C.c_int]),
+        "mlb_op_wait_probe": (C.c_int, [C.c_int, C.c_uint32]),
         "mlb_kv_alloc_new": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
         "mlb_kv_alloc_ensure": (C.c_int, [vp, C.c_int, C.c_int, C.c_int]),
         "mlb_kv_alloc_table": (C.c_int, [vp, C.c_int, i32p, C.c_int]),

@@ -1307,7 +1307,7 @@ static int setup_grid_path(mlb_session* s) {
     return MLB_OK;
 }
 
-// Tensor-core projections for large batches: bf16 weights, batch >= 16 (MLB_GEMM=simt turns it off).
+// Tensor-core projections for batches of 4 sequences or more with bf16 weights (MLB_GEMM=simt turns it off).
 static int setup_tc_path(mlb_session* s) {
     const mlb_config& c = s->m->cfg;
     s->use_tc = false;
@@ -1318,7 +1318,10 @@ static int setup_tc_path(mlb_session* s) {
         if (mode == "tc") return fail(MLB_E_UNSUPPORTED, "MLB_GEMM=tc needs bf16 weights");
         return MLB_OK;
     }
-    if (mode == "auto" && s->B < 16) return MLB_OK;
+    // auto: from 4 sequences on. The GEMV kernels re-read nothing, but their time grows with the batch
+    // (cfg1: 169 us at 1 sequence, 369 at 4, 537 at 8, 635 at 12), while the tensor-core step costs
+    // 360-390 us for any batch up to 16 (its floor is its 60 launches).
+    if (mode == "auto" && s->B < 4) return MLB_OK;
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) {
         if (mode == "tc") return fail(MLB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");

@@ -118,6 +118,17 @@ __device__ __forceinline__ float* map_rank(float* p, uint32_t rank) {
     return (float*)out;
 }
 
+// Wait for a phase of an mbarrier, at most `limit` polls: every wait of the kernels here ends, with
+// the data or with `false`, so that a kernel always terminates and the host can report the failure.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint32_t limit, unsigned backoff_ns) {
+#pragma unroll 1
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (backoff_ns) __nanosleep(backoff_ns);
+    }
+    return false;
+}
+
 // ---- ring of shared-memory stages -------------------------------------------------------------
 struct Ring {
     uint32_t full0, empty0;        // shared addresses of the barrier arrays
@@ -137,18 +148,13 @@ struct Ring {
 #ifdef MLB_GRID_TIMERS
         const long long t0 = clock64();
 #endif
-#pragma unroll 1
-        for (uint32_t i = 0; i < kMegaSpinLimit; ++i) {
-            if (mbar_try_wait(bar, parity)) {
+        // code 1 = the producer waiting for a free stage: it runs stages ahead, so while the ring is full
+        // it polls at leisure and leaves the issue slots and the shared-memory pipe to the consumers
+        const bool ok = mbar_wait_bounded(bar, parity, kMegaSpinLimit, code == 1 ? backoff_ns : 0u);
 #ifdef MLB_GRID_TIMERS
-                wait_cycles += clock64() - t0;
+        wait_cycles += clock64() - t0;
 #endif
-                return true;
-            }
-            // the producer runs stages ahead: while the ring is full it polls at leisure and leaves the
-            // issue slots and the shared-memory pipe to the consumers
-            if (code == 1 && backoff_ns) __nanosleep(backoff_ns);
-        }
+        if (ok) return true;
         *dead = 1;
         atomicExch(err, code);
         return false;

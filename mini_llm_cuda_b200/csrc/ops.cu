@@ -5,6 +5,7 @@
 #include "../../include/mlb.h"
 #include "errors.h"
 #include "kernels.cuh"
+#include "mega.cuh"
 #include "tc_host.h"
 
 using namespace mlb;
@@ -224,4 +225,39 @@ extern "C" int mlb_op_attn_decode_static(const void* kpool, const void* vpool, i
     // rewrites the limits; the partials are fully overwritten before they are read.
     return run_attn(scratch, kpool, vpool, kv_dtype, page_table, pt_stride, positions, q, gate_or_null, out, batch, heads,
                     kv_heads, head_dim, splits, static_cast<cudaStream_t>(stream));
+}
+
+// ---- bounded-wait probe ------------------------------------------------------------------------
+namespace {
+// One thread waits, with the wait routine of the streaming kernels, for an mbarrier phase that
+// nothing completes; when the polls run out it records code 2, as those kernels do.
+__global__ void wait_probe_kernel(uint32_t max_polls, int* err) {
+    __shared__ __align__(8) unsigned long long bar;
+    const uint32_t a = mlb::smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        mlb::mbar_init(a, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mlb::mbar_wait_bounded(a, 0, max_polls, 0)) atomicExch(err, 2);
+    }
+}
+}  // namespace
+
+extern "C" int mlb_op_wait_probe(int device, uint32_t max_polls) {
+    if (max_polls < 1 || max_polls > (1u << 20)) return mlb::fail(MLB_E_INVALID, "max_polls must be in 1..2^20");
+    CU(cudaSetDevice(device));
+    int* err = nullptr;
+    CU(cudaMalloc((void**)&err, 4));
+    cudaError_t e = cudaMemset(err, 0, 4);
+    int code = 0;
+    if (e == cudaSuccess) {
+        wait_probe_kernel<<<1, 32>>>(max_polls, err);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(&code, err, 4, cudaMemcpyDeviceToHost);      // waits for the kernel
+    cudaFree(err);
+    if (e != cudaSuccess) return mlb::fail(MLB_E_CUDA, "wait probe: %s", cudaGetErrorString(e));
+    if (code != 0)
+        return mlb::fail(MLB_E_TIMEOUT, "a bounded device-side wait ran out (code %d) after %u polls; the context stays usable", code,
+                         max_polls);
+    return MLB_OK;
 }

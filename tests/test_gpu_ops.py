@@ -124,3 +124,16 @@ def test_tcgen05_gemm_matches_fp32_matmul(api, N, K, batch):
     h = torch.zeros(batch, N, dtype=torch.bfloat16, device="cuda")
     assert L.mlb_op_gemm_bf16(W.data_ptr(), W2.data_ptr(), X.data_ptr(), None, h.data_ptr(), N, K, batch, None) == 0
     assert (h.float() - h_want).abs().max().item() < 1e-2 * max(h_want.abs().max().item(), 1e-3)
+
+
+def test_bounded_wait_runs_out_and_context_stays_usable(api):
+    """The wait routine of the streaming kernels, on a barrier that nothing completes: the kernel
+    ends by itself, the call reports MLB_E_TIMEOUT, and the next operator call on the same
+    context works (no trap, no fault, no endless loop)."""
+    lib = api.lib()
+    rc = lib.mlb_op_wait_probe(0, 20000)
+    assert rc == api.MLB_E_TIMEOUT
+    assert b"bounded device-side wait ran out" in lib.mlb_last_error()
+    assert lib.mlb_op_wait_probe(0, 0) == api.MLB_E_INVALID
+    # the context is intact: a tcgen05 GEMM right after it still matches torch
+    test_tcgen05_gemm_matches_fp32_matmul(api, 256, 512, 32)
