@@ -412,6 +412,12 @@ struct mlb_session {
     // activation operand maps per batch tile 16, 32, 64, 128, 256 (index log2(Nb/16))
     struct alignas(64) TcGlobalMaps { CUtensorMap E, xn[5], a_attn[5], a_dn[5], h[5]; } tc_g;
     int* pinned_err = nullptr;
+    // prompt columns: a second set of step buffers, `B` columns wide, that shares this session's KV
+    // pool, delta-net state and stream; a column is one prompt token of one sequence
+    mlb_session* cols = nullptr;            // owned by the session it serves
+    mlb_session* parent = nullptr;          // set in the column set
+    bool cols_tried = false;
+    int* seq_of = nullptr;                  // [B] in the column set: column -> sequence of the parent
 };
 
 namespace mlb {
@@ -445,11 +451,12 @@ static void free_session(mlb_session* s) {
     if (!s) return;
     cudaSetDevice(s->m->device);
     if (s->stream) cudaStreamSynchronize(s->stream);
+    if (s->cols) free_session(s->cols);
     for (auto& g : s->graphs) if (g) cudaGraphExecDestroy(g);
     for (void* p : s->allocs) cudaFree(p);
     if (s->pinned_tok) cudaFreeHost(s->pinned_tok);
     if (s->pinned_err) cudaFreeHost(s->pinned_err);
-    if (s->stream) cudaStreamDestroy(s->stream);
+    if (s->stream && !s->parent) cudaStreamDestroy(s->stream);      // a column set runs on its parent's stream
     delete s;
 }
 
@@ -823,9 +830,16 @@ struct Chain {
                 ++launches;
                 const int dk = cfg.dn_key_dim, dv = cfg.dn_value_dim, H = cfg.heads;
                 if (rec && (rc = rec->begin("deltanet_state_update", (uint64_t)B * 2ull * H * dk * dv * 4, (uint64_t)B * 6ull * H * dk * dv))) return rc;
-                dim3 grid((dv + 31) / 32, H, B);
-                if (dk == 64) CU(launch_chain(s->use_pdl, delta_net_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
-                else CU(launch_chain(s->use_pdl, delta_net_kernel<128>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
+                if (s->parent) {
+                    // prompt columns: the recurrence runs over the columns of a sequence in order
+                    dim3 grid((dv + 31) / 32, H, B);
+                    if (dk == 64) CU(launch_chain(s->use_pdl, delta_net_cols_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const int*>(s->seq_of), B, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
+                    else CU(launch_chain(s->use_pdl, delta_net_cols_kernel<128>, grid, dim3(256), 0, s->stream, c, static_cast<const int*>(s->seq_of), B, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
+                } else {
+                    dim3 grid((dv + 31) / 32, H, B);
+                    if (dk == 64) CU(launch_chain(s->use_pdl, delta_net_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
+                    else CU(launch_chain(s->use_pdl, delta_net_kernel<128>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
+                }
                 if (rec && (rc = rec->end())) return rc;
                 ++launches;
             }
@@ -838,7 +852,9 @@ struct Chain {
             if ((rc = gemm_tc<TC_RESID>(s, M.w2, M.w2, s->tc_g.h, d, F, s->x, s->x, nullptr, rec, "ffn_down_gemm_tcgen05_residual"))) return rc;
             ++launches;
         }
-        if (kind == CHAIN_PREFILL) {
+        if (kind == CHAIN_PREFILL && s->parent) {
+            // prompt columns: positions and tokens of the next chunk come from the host
+        } else if (kind == CHAIN_PREFILL) {
             if (rec && (rc = rec->begin("advance_prompt", (uint64_t)B * 12, 0))) return rc;
             CU(launch_chain(s->use_pdl, advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s->stream, c));
             if (rec && (rc = rec->end())) return rc;
@@ -1313,7 +1329,7 @@ static int setup_tc_path(mlb_session* s) {
     s->use_tc = false;
     const char* env = std::getenv("MLB_GEMM");
     const std::string mode = env ? env : "auto";
-    if (mode == "simt" || s->use_cluster || s->use_grid) return MLB_OK;
+    if (!s->parent && (mode == "simt" || s->use_cluster || s->use_grid)) return MLB_OK;
     if (c.weight_dtype != MLB_DT_BF16) {
         if (mode == "tc") return fail(MLB_E_UNSUPPORTED, "MLB_GEMM=tc needs bf16 weights");
         return MLB_OK;
@@ -1321,7 +1337,7 @@ static int setup_tc_path(mlb_session* s) {
     // auto: from 4 sequences on. The GEMV kernels re-read nothing, but their time grows with the batch
     // (cfg1: 169 us at 1 sequence, 369 at 4, 537 at 8, 635 at 12), while the tensor-core step costs
     // 360-390 us for any batch up to 16 (its floor is its 60 launches).
-    if (mode == "auto" && s->B < 4) return MLB_OK;
+    if (!s->parent && mode == "auto" && s->B < 4) return MLB_OK;
     EncodeTiledFn enc = get_encode_tiled();
     if (!enc) {
         if (mode == "tc") return fail(MLB_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -1445,7 +1461,9 @@ static int apply_sampling(mlb_session* s, const mlb_sampling* sp, int* kind) {
 
 }  // namespace mlb
 
-extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_block, int kv_pages, mlb_session** out) {
+// A session, or (parent != null) the column set of one: `batch` columns of step buffers on the
+// parent's KV pool, delta-net state and stream, always on the tensor-core step.
+static int session_create(mlb_model* m, int batch, int max_context, int kv_block, int kv_pages, mlb_session* parent, mlb_session** out) {
     if (!m || !out) return fail(MLB_E_INVALID, "null argument");
     *out = nullptr;
     if (batch < 1) return fail(MLB_E_INVALID, "batch must be >= 1");
@@ -1460,16 +1478,21 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     s->max_ctx = max_context;
     s->max_pages = (max_context + kKvBlock - 1) / kKvBlock;
     s->kv_pages = kv_pages > 0 ? kv_pages : batch * s->max_pages;
+    s->parent = parent;
+    if (parent) s->kv_pages = parent->kv_pages;
 #define SA(expr) do { int r__ = (expr); if (r__) { free_session(s); return r__; } } while (0)
 #define SCU(expr) do { cudaError_t e__ = (expr); if (e__ != cudaSuccess) { free_session(s); return fail(MLB_E_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)); } } while (0)
-    SCU(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+    if (parent) s->stream = parent->stream;
+    else SCU(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
     const size_t B = batch;
+    const size_t ctx_rows = parent ? 1 : (size_t)max_context;      // a column set has no prompt / output ring of its own
     SA(sess_alloc(s, (void**)&s->pos, B * 4, true));
     SA(sess_alloc(s, (void**)&s->tok, B * 4, true));
     SA(sess_alloc(s, (void**)&s->limit_prefill, B * 4, true));
     SA(sess_alloc(s, (void**)&s->limit_decode, B * 4, true));
-    SA(sess_alloc(s, (void**)&s->prompt, B * max_context * 4, true));
-    SA(sess_alloc(s, (void**)&s->out_ring, B * max_context * 4, true));
+    SA(sess_alloc(s, (void**)&s->prompt, B * ctx_rows * 4, true));
+    SA(sess_alloc(s, (void**)&s->out_ring, B * ctx_rows * 4, true));
+    if (parent) SA(sess_alloc(s, (void**)&s->seq_of, B * 4, true));
     SA(sess_alloc(s, (void**)&s->out_idx, B * 4, true));
     SA(sess_alloc(s, (void**)&s->page_table, B * s->max_pages * 4, true));
     SA(sess_alloc(s, (void**)&s->seeds, B * 8, true));
@@ -1505,7 +1528,11 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     s->state.assign(c.layers, nullptr);
     const size_t kv_elt = elt_size(c.kv_dtype);
     for (int i = 0; i < c.layers; ++i) {
-        if (c.layer_types[i] == MLB_LAYER_ATTENTION) {
+        if (parent) {
+            s->kpool[i] = parent->kpool[i];
+            s->vpool[i] = parent->vpool[i];
+            s->state[i] = parent->state[i];
+        } else if (c.layer_types[i] == MLB_LAYER_ATTENTION) {
             size_t bytes = (size_t)s->kv_pages * c.kv_heads * kKvBlock * c.head_dim * kv_elt;
             SA(sess_alloc(s, &s->kpool[i], bytes, true));
             SA(sess_alloc(s, &s->vpool[i], bytes, true));
@@ -1513,8 +1540,10 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
             SA(sess_alloc(s, (void**)&s->state[i], B * c.heads * c.dn_value_dim * c.dn_key_dim * 4, true));
         }
     }
-    s->flush_n = (192ull << 20) / 16;
-    SA(sess_alloc(s, (void**)&s->flush_buf, s->flush_n * 16, false));
+    if (!parent) {
+        s->flush_n = (192ull << 20) / 16;
+        SA(sess_alloc(s, (void**)&s->flush_buf, s->flush_n * 16, false));
+    }
     SCU(cudaMallocHost((void**)&s->pinned_tok, B * 4));
     SCU(cudaMallocHost((void**)&s->pinned_err, 4));
     *s->pinned_err = 0;
@@ -1539,13 +1568,23 @@ extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_
     }
     SA(sess_alloc(s, (void**)&s->dev_err, 4, true));
     SA(chain_configure(s));
-    SA(setup_cluster_path(s));
-    if (!s->use_cluster) SA(setup_grid_path(s));
+    if (!parent) {
+        SA(setup_cluster_path(s));
+        if (!s->use_cluster) SA(setup_grid_path(s));
+    }
     SA(setup_tc_path(s));
+    if (parent && !s->use_tc) {
+        free_session(s);
+        return fail(MLB_E_UNSUPPORTED, "prompt columns need the tensor-core step (bf16 weights)");
+    }
 #undef SA
 #undef SCU
     *out = s;
     return MLB_OK;
+}
+
+extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_block, int kv_pages, mlb_session** out) {
+    return session_create(m, batch, max_context, kv_block, kv_pages, nullptr, out);
 }
 
 extern "C" int mlb_session_reset(mlb_session* s) {
@@ -1572,6 +1611,86 @@ extern "C" int mlb_session_reset(mlb_session* s) {
 }
 
 extern "C" void mlb_session_free(mlb_session* s) { free_session(s); }
+
+// Prompt by columns. The token loop consumes a prompt one token per step and sequence: a
+// 512-token prompt costs 511 steps. Here the prompt tokens of all sequences become the columns of
+// tensor-core steps (bf16 weights): the projections of up to kPromptCols tokens are one GEMM each,
+// every column appends its K/V row and attends to the rows before it (same kernels as a decode
+// step, the column's page-table row is its sequence's), and the delta-net recurrence walks the
+// columns of a sequence in order (delta_net_cols_kernel). All tokens but the last of each prompt
+// are consumed; the last one stays pending, as after the token loop. MLB_PREFILL = auto | step |
+// chunk: auto takes this path from 64 prompt tokens on (its activations are bf16, so the cache
+// differs from the token loop's within the low-precision tolerance); `*done` tells whether it ran.
+static const int kPromptCols = 128;
+static int prefill_columns(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride, bool* done) {
+    *done = false;
+    const char* env = std::getenv("MLB_PREFILL");
+    const std::string mode = env ? env : "auto";
+    if (mode == "step") return MLB_OK;
+    const int B = s->B;
+    long total = 0;
+    for (int b = 0; b < B; ++b) total += lens[b] - 1;
+    if (total < 1 || (mode == "auto" && total < 64)) return MLB_OK;
+    if (s->m->cfg.weight_dtype != MLB_DT_BF16) {
+        if (mode == "chunk") return fail(MLB_E_UNSUPPORTED, "MLB_PREFILL=chunk needs bf16 weights");
+        return MLB_OK;
+    }
+    if (!s->cols && !s->cols_tried) {
+        s->cols_tried = true;
+        int rc = session_create(s->m, kPromptCols, s->max_ctx, 0, 0, s, &s->cols);
+        if (rc) {
+            s->cols = nullptr;
+            if (mode == "chunk") return rc;
+        }
+    }
+    mlb_session* cs = s->cols;
+    if (!cs) return MLB_OK;
+    const int T = cs->B, MP = s->max_pages;
+    int rc;
+    if ((rc = ensure_graph(cs, CHAIN_PREFILL))) return rc;
+    std::vector<int> h_tok(T), h_pos(T), h_lim(T), h_seq(T), h_tab((size_t)T * MP);
+    // A chunk takes the next tokens of as many sequences as it can, an equal share each: the
+    // delta-net recurrence is serial along a sequence and parallel across sequences, so 64 sequences
+    // with 2 columns each beat 1 sequence with 128. Columns stay grouped by sequence, positions ascending.
+    std::vector<int> cursor(B, 0);
+    long left = total;
+    while (left > 0) {
+        int n_active = 0;
+        for (int b = 0; b < B; ++b) n_active += cursor[b] < lens[b] - 1 ? 1 : 0;
+        const int share = std::max(1, T / n_active);
+        int n = 0;
+        for (int b = 0; b < B && n < T; ++b) {
+            const int take = std::min(std::min(share, lens[b] - 1 - cursor[b]), T - n);
+            for (int i = 0; i < take; ++i, ++n) {
+                const int t = cursor[b] + i;
+                h_tok[n] = tokens[(size_t)b * stride + t];
+                h_pos[n] = t;
+                h_lim[n] = t + 1;        // active: pos < limit
+                h_seq[n] = b;
+                std::memcpy(&h_tab[(size_t)n * MP], &s->h_table[(size_t)b * MP], (size_t)MP * 4);
+            }
+            if (take > 0) cursor[b] += take;
+        }
+        left -= n;
+        for (int i = n; i < T; ++i) { h_tok[i] = 0; h_pos[i] = 0; h_lim[i] = 0; h_seq[i] = 0; }      // idle columns
+        CU(cudaMemcpyAsync(cs->tok, h_tok.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
+        CU(cudaMemcpyAsync(cs->pos, h_pos.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
+        CU(cudaMemcpyAsync(cs->limit_prefill, h_lim.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
+        CU(cudaMemcpyAsync(cs->seq_of, h_seq.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
+        CU(cudaMemcpyAsync(cs->page_table, h_tab.data(), h_tab.size() * 4, cudaMemcpyHostToDevice, s->stream));
+        CU(cudaGraphLaunch(cs->graphs[CHAIN_PREFILL], s->stream));
+        CU(cudaStreamSynchronize(s->stream));          // the host arrays are rewritten for the next chunk
+    }
+    // what the token loop would have left: position len-1 with the last prompt token pending
+    std::vector<int> pos(B), last(B);
+    for (int i = 0; i < B; ++i) { pos[i] = lens[i] - 1; last[i] = tokens[(size_t)i * stride + lens[i] - 1]; }
+    CU(cudaMemcpyAsync(s->pos, pos.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
+    CU(cudaMemcpyAsync(s->tok, last.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
+    if ((rc = queue_err_readback(cs))) return rc;
+    CU(cudaStreamSynchronize(s->stream));
+    *done = true;
+    return check_err_readback(cs);
+}
 
 extern "C" int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride) {
     if (!s || !tokens || !lens) return fail(MLB_E_INVALID, "null argument");
@@ -1611,7 +1730,9 @@ extern "C" int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t*
     CU(cudaMemcpyAsync(s->tok, first.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
     CU(cudaMemcpyAsync(s->limit_prefill, lim.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
     CU(cudaStreamSynchronize(s->stream));
-    if (max_len > 1) {
+    bool by_columns = false;
+    if ((rc = prefill_columns(s, tokens, lens, stride, &by_columns))) return rc;
+    if (!by_columns && max_len > 1) {
         if ((rc = ensure_graph(s, CHAIN_PREFILL))) return rc;
         for (int t = 0; t < max_len - 1; ++t)
             if ((rc = launch_step(s, CHAIN_PREFILL))) return rc;

@@ -94,7 +94,7 @@ def test_grid_step_long_context_matches_oracle(api, tmp_path, monkeypatch, name)
     """The whole-GPU single-kernel step with a context long enough for several context splits per
     kv head (more than 8 KV pages): 150-token prompt, 40 greedy tokens, sampled tokens afterwards."""
     monkeypatch.setenv("MLB_DECODE_PATH", "grid")
-    spec = SPECS[name]
+    monkeypatch.setenv("MLB_PREFILL", "step")    # fp32 activations in the prompt too: identical ids are expected
     spec = dataclasses.replace(SPECS[name], max_context=512)
     path = write_model(tmp_path, spec, seed=13)
     oracle = load_oracle(path)
@@ -121,6 +121,7 @@ def test_ragged_batch_matches_oracle(api, tmp_path, monkeypatch, name, batch, pa
     monkeypatch.setenv("MLB_DECODE_PATH", "chain" if path_mode == "chain_thread" else path_mode)
     monkeypatch.setenv("MLB_GEMV", "thread" if path_mode == "chain_thread" else "auto")
     monkeypatch.setenv("MLB_GEMM", "simt")      # fp32 activations: identical ids are expected (the tensor-core path has its own test)
+    monkeypatch.setenv("MLB_PREFILL", "step")   # likewise for the prompt (prompt columns have their own test)
     """Ragged prompts (1 .. 37 tokens) in one batch, decode_n in one call: every sequence
     equals its own batch-1 oracle roll-out."""
     spec = SPECS[name]
@@ -174,6 +175,62 @@ def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name,
                 checked += 1
     assert worst < TOL_LOWP, worst
     assert checked > batch      # the margin test did not make the check vacuous
+    sess.close()
+    model.close()
+
+
+@pytest.mark.parametrize("name,lens,decode_path", [("bf16", [131], "chain"), ("bf16", [1, 2, 130, 60, 201, 17], "auto"),
+                                                   ("bf16_w_f32_kv", [300, 5, 129], "chain"), ("bf16", [257], "grid")])
+def test_prompt_by_columns_matches_oracle(api, tmp_path, monkeypatch, name, lens, decode_path):
+    """The prompt consumed as columns of tensor-core steps (128 per chunk; prompts that end inside a
+    chunk, span several, or have a single token), attention and delta-net layers mixed, PLE: the
+    decode steps that follow, teacher-forced on the oracle's tokens, give its logits within 2e-2,
+    and the positions are those the token loop leaves."""
+    monkeypatch.setenv("MLB_PREFILL", "chunk")
+    monkeypatch.setenv("MLB_DECODE_PATH", decode_path)
+    spec = dataclasses.replace(SPECS[name], max_context=512)
+    path = write_model(tmp_path, spec, seed=21)
+    oracle = load_oracle(path)
+    batch = len(lens)
+    prompts = random_prompts(spec.vocab, lens, seed=23)
+    steps = 6
+    rolls = [oracle_rollout(oracle, prompts[b], steps) for b in range(batch)]
+    model = api.Model(path)
+    sess = api.Session(model, batch)
+    sess.prefill(prompts)
+    assert sess.positions().tolist() == [l - 1 for l in lens]
+    worst = 0.0
+    checked = 0
+    for i in range(steps):
+        forced = None if i == 0 else [int(rolls[b][0][i - 1]) for b in range(batch)]
+        picks = sess.decode_step(in_tokens=forced)
+        lg = sess.logits()
+        for b in range(batch):
+            want = rolls[b][1][i]
+            worst = max(worst, logits_error(lg[b], want))
+            top2 = np.sort(want)[-2:]
+            if (top2[1] - top2[0]) > 2 * TOL_LOWP * np.abs(want).max():
+                assert int(picks[b]) == int(rolls[b][0][i]), (i, b)
+                checked += 1
+    assert worst < TOL_LOWP, worst
+    assert checked > 0
+    # a second prompt on the same session starts from a clean cache and state
+    sess.prefill(prompts)
+    sess.decode_step()
+    assert max(logits_error(sess.logits()[b], rolls[b][1][0]) for b in range(batch)) < TOL_LOWP
+    sess.close()
+    model.close()
+
+
+def test_prompt_by_columns_needs_bf16_weights(api, tmp_path, monkeypatch):
+    monkeypatch.setenv("MLB_PREFILL", "chunk")
+    spec = SPECS["attn_fp32"]
+    path = write_model(tmp_path, spec, seed=2)
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    with pytest.raises(api.MlbError) as e:
+        sess.prefill([random_prompts(spec.vocab, [40], seed=1)[0]])
+    assert e.value.status == api.MLB_E_UNSUPPORTED
     sess.close()
     model.close()
 
