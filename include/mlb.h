@@ -107,7 +107,7 @@ void mlb_session_free(mlb_session* s);
  * recompute-everything loop: ingests tokens[b*stride .. +lens[b]) for every sequence. After
  * it, position lens[b]-1 holds the last prompt token as the pending input of the next step.
  * With bf16 weights and 64 prompt tokens or more the prompt is consumed as columns of
- * tensor-core steps, 128 tokens at a time (bf16 activations: the cache equals the token loop's
+ * tensor-core steps, 256 tokens at a time (bf16 activations: the cache equals the token loop's
  * within the low-precision tolerance); otherwise, or with MLB_PREFILL=step in the environment,
  * one token per step and sequence. MLB_PREFILL=chunk asks for the columns and fails with
  * MLB_E_UNSUPPORTED where they cannot run. */

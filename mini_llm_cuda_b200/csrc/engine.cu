@@ -832,9 +832,15 @@ struct Chain {
                 if (rec && (rc = rec->begin("deltanet_state_update", (uint64_t)B * 2ull * H * dk * dv * 4, (uint64_t)B * 6ull * H * dk * dv))) return rc;
                 if (s->parent) {
                     // prompt columns: the recurrence runs over the columns of a sequence in order
-                    dim3 grid((dv + 31) / 32, H, B);
-                    if (dk == 64) CU(launch_chain(s->use_pdl, delta_net_cols_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const int*>(s->seq_of), B, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
-                    else CU(launch_chain(s->use_pdl, delta_net_cols_kernel<128>, grid, dim3(256), 0, s->stream, c, static_cast<const int*>(s->seq_of), B, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
+                    dim3 ngrid(H, B), grid((dv + 31) / 32, H, B);
+                    if (dk == 64) {
+                        CU(launch_chain(s->use_pdl, delta_cols_norm_kernel<64>, ngrid, dim3(64), 0, s->stream, c, s->raw, s->raw_stride, H, dv, 1e-6f));
+                        CU(launch_chain(s->use_pdl, delta_net_cols_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const int*>(s->seq_of), B, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16));
+                    } else {
+                        CU(launch_chain(s->use_pdl, delta_cols_norm_kernel<128>, ngrid, dim3(64), 0, s->stream, c, s->raw, s->raw_stride, H, dv, 1e-6f));
+                        CU(launch_chain(s->use_pdl, delta_net_cols_kernel<128>, grid, dim3(256), 0, s->stream, c, static_cast<const int*>(s->seq_of), B, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16));
+                    }
+                    ++launches;
                 } else {
                     dim3 grid((dv + 31) / 32, H, B);
                     if (dk == 64) CU(launch_chain(s->use_pdl, delta_net_kernel<64>, grid, dim3(256), 0, s->stream, c, static_cast<const float*>(s->raw), s->raw_stride, s->state[i], H, dv, s->abuf, s->a16, 1e-6f));
@@ -1614,14 +1620,14 @@ extern "C" void mlb_session_free(mlb_session* s) { free_session(s); }
 
 // Prompt by columns. The token loop consumes a prompt one token per step and sequence: a
 // 512-token prompt costs 511 steps. Here the prompt tokens of all sequences become the columns of
-// tensor-core steps (bf16 weights): the projections of up to kPromptCols tokens are one GEMM each,
+// tensor-core steps (bf16 weights): the projections of up to kPromptCols (256) tokens are one GEMM each,
 // every column appends its K/V row and attends to the rows before it (same kernels as a decode
 // step, the column's page-table row is its sequence's), and the delta-net recurrence walks the
 // columns of a sequence in order (delta_net_cols_kernel). All tokens but the last of each prompt
 // are consumed; the last one stays pending, as after the token loop. MLB_PREFILL = auto | step |
 // chunk: auto takes this path from 64 prompt tokens on (its activations are bf16, so the cache
 // differs from the token loop's within the low-precision tolerance); `*done` tells whether it ran.
-static const int kPromptCols = 128;
+static const int kPromptCols = 256;
 static int prefill_columns(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride, bool* done) {
     *done = false;
     const char* env = std::getenv("MLB_PREFILL");

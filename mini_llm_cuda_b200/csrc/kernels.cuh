@@ -935,18 +935,46 @@ __global__ void __launch_bounds__(256) delta_net_kernel(StepCtl c, const float* 
 }
 
 // The same update for prompt columns: the columns of a chunk are consecutive tokens of one or
-// several sequences (seq_of[col], ascending, positions ascending inside a sequence), and the
-// recurrence S_t = f(S_{t-1}) runs over them in order. A CTA owns 32 rows of one head's state,
-// keeps them in registers across the columns of a sequence, and reads / writes the state in
-// global memory once per sequence and chunk. The sequences of a chunk are independent: CTA z
-// serves the run of columns that starts at column z, if a sequence starts there, and leaves
-// otherwise.
+// several sequences (seq_of[col], grouped by sequence, positions ascending inside a sequence), and
+// the recurrence S_t = f(S_{t-1}) runs over a sequence's columns in order.
+//
+// delta_cols_norm_kernel first turns the raw projections of every (column, head) into what the
+// recurrence consumes - L2-normalised q and k, sigmoid gates - in place, in parallel over columns.
+// grid = (H, columns), block = 64.
+template <int DK>
+__global__ void __launch_bounds__(64) delta_cols_norm_kernel(StepCtl c, float* __restrict__ raw, int raw_stride, int H, int dv,
+                                                             float l2_eps) {
+    constexpr int EPL = DK / 32;
+    const int h = blockIdx.x, col = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (!seq_active(c, col)) return;
+    float* r = raw + (size_t)col * raw_stride;
+    float* vec = r + (size_t)(warp == 0 ? 0 : H) * DK + (size_t)h * DK;       // q heads, then k heads
+    float v[EPL], ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) { v[e] = vec[lane * EPL + e]; ss = fmaf(v[e], v[e], ss); }
+    ss = warp_sum(ss);
+    const float n = sqrtf(ss + l2_eps);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) vec[lane * EPL + e] = v[e] / n;
+    if (warp == 0 && lane < 2) {
+        float* g = r + (size_t)2 * H * DK + (size_t)H * dv + (size_t)lane * H + h;       // beta[H] then alpha[H]
+        *g = 1.0f / (1.0f + expf(-*g));
+    }
+}
+
+// The recurrence itself. A warp owns 4 rows of one head's state and keeps them in registers
+// across the columns of a sequence; the state is read and written once per sequence and chunk, and
+// the next column's q, k, v and gates are requested while the current one is applied (no block
+// barrier in the loop). The sequences of a chunk are independent: CTA z serves the run of columns
+// that starts at column z, if a sequence starts there, and leaves otherwise.
 // grid = (ceil(dv / 32), H, columns), block = 256.
 template <int DK>
 __global__ void __launch_bounds__(256) delta_net_cols_kernel(StepCtl c, const int* __restrict__ seq_of, int n_cols,
                                                              const float* __restrict__ raw, int raw_stride, float* __restrict__ state,
-                                                             int H, int dv, float* __restrict__ abuf, bf16_t* __restrict__ abuf16,
-                                                             float l2_eps) {
+                                                             int H, int dv, float* __restrict__ abuf, bf16_t* __restrict__ abuf16) {
     constexpr int EPL = DK / 32;
     constexpr int ROWS_PER_WARP = 4;
     const int h = blockIdx.y;
@@ -954,60 +982,75 @@ __global__ void __launch_bounds__(256) delta_net_cols_kernel(StepCtl c, const in
     pdl_launch_dependents();
     pdl_wait();
     const int row0 = blockIdx.x * (8 * ROWS_PER_WARP) + warp * ROWS_PER_WARP;
-    __shared__ float sq[DK], sk[DK];
-    __shared__ float sgate[2];
-    float s[ROWS_PER_WARP][EPL];
     const int first = blockIdx.z;
-    if (first >= n_cols || !seq_active(c, first)) return;  // uniform over the CTA
+    if (first >= n_cols || !seq_active(c, first)) return;
     const int cur = seq_of[first];
     if (first > 0 && seq_active(c, first - 1) && seq_of[first - 1] == cur) return;     // not the start of a run
+    if (row0 >= dv) return;
     float* Sh = state + ((size_t)cur * H + h) * (size_t)dv * DK;
+    float s[ROWS_PER_WARP][EPL];
 #pragma unroll
     for (int i = 0; i < ROWS_PER_WARP; ++i)
 #pragma unroll
         for (int e = 0; e < EPL; ++e) s[i][e] = row0 + i < dv ? __ldcg(&Sh[(size_t)(row0 + i) * DK + lane * EPL + e]) : 0.f;
-    for (int col = first; col < n_cols; ++col) {
-        if (!seq_active(c, col) || seq_of[col] != cur) break;      // the run ends (uniform over the CTA)
+    // one column's inputs: normalised q and k of the head (EPL values per lane), the warp's 4 values
+    // of v, the two gates
+    float qn[EPL], kn[EPL], vr[ROWS_PER_WARP], beta, alpha;
+    auto fetch = [&](int col, float* q_, float* k_, float* v_, float& b_, float& a_) {
         const float* r = raw + (size_t)col * raw_stride;
-        const float* rv = r + (size_t)2 * H * DK + (size_t)h * dv;
-        __syncthreads();                                   // the previous column's q, k, gates are no longer read
-        if (warp < 2) {
-            const float* src = r + (size_t)(warp == 0 ? 0 : H) * DK + (size_t)h * DK;
-            float v[EPL], ss = 0.f;
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) { v[e] = src[lane * EPL + e]; ss = fmaf(v[e], v[e], ss); }
-            ss = warp_sum(ss);
-            const float n = sqrtf(ss + l2_eps);
-            float* dst = warp == 0 ? sq : sk;
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) dst[lane * EPL + e] = v[e] / n;
-        } else if (warp == 2 && lane < 2) {
-            const float g = r[(size_t)2 * H * DK + (size_t)H * dv + (size_t)lane * H + h];
-            sgate[lane] = 1.0f / (1.0f + expf(-g));
+        for (int e = 0; e < EPL; ++e) {
+            q_[e] = __ldcg(r + (size_t)h * DK + lane * EPL + e);
+            k_[e] = __ldcg(r + (size_t)H * DK + (size_t)h * DK + lane * EPL + e);
         }
-        __syncthreads();
-        const float beta = sgate[0], alpha = sgate[1];
-        float qn[EPL], kn[EPL];
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) { qn[e] = sq[lane * EPL + e]; kn[e] = sk[lane * EPL + e]; }
+        for (int i = 0; i < ROWS_PER_WARP; ++i) v_[i] = row0 + i < dv ? __ldcg(r + (size_t)2 * H * DK + (size_t)h * dv + row0 + i) : 0.f;
+        b_ = __ldcg(r + (size_t)2 * H * DK + (size_t)H * dv + h);
+        a_ = __ldcg(r + (size_t)2 * H * DK + (size_t)H * dv + H + h);
+    };
+    fetch(first, qn, kn, vr, beta, alpha);
+    for (int col = first; col < n_cols; ++col) {
+        const bool more = col + 1 < n_cols && seq_active(c, col + 1) && seq_of[col + 1] == cur;
+        float qx[EPL], kx[EPL], vx[ROWS_PER_WARP], bx = 0.f, ax = 0.f;
+        if (more) fetch(col + 1, qx, kx, vx, bx, ax);
+        float d1[ROWS_PER_WARP], d2[ROWS_PER_WARP];
 #pragma unroll
         for (int i = 0; i < ROWS_PER_WARP; ++i) {
-            const int row = row0 + i;
-            float d1 = 0.f;
+            d1[i] = 0.f;
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) { s[i][e] *= alpha; d1 = fmaf(s[i][e], kn[e], d1); }
-            d1 = warp_sum(d1);
-            const float vi = row < dv ? rv[row] : 0.f;
-            const float cf = beta * (vi - d1);
-            float d2 = 0.f;
+            for (int e = 0; e < EPL; ++e) { s[i][e] *= alpha; d1[i] = fmaf(s[i][e], kn[e], d1[i]); }
+        }
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) { s[i][e] = fmaf(cf, kn[e], s[i][e]); d2 = fmaf(s[i][e], qn[e], d2); }
-            d2 = warp_sum(d2);
-            if (row < dv && lane == 0) {
-                abuf[((size_t)col * H + h) * dv + row] = d2;
-                if (abuf16) abuf16[((size_t)col * H + h) * dv + row] = __float2bfloat16_rn(d2);
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < ROWS_PER_WARP; ++i) d1[i] += __shfl_xor_sync(0xffffffffu, d1[i], o);
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; ++i) {
+            const float cf = beta * (vr[i] - d1[i]);
+            d2[i] = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) { s[i][e] = fmaf(cf, kn[e], s[i][e]); d2[i] = fmaf(s[i][e], qn[e], d2[i]); }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int i = 0; i < ROWS_PER_WARP; ++i) d2[i] += __shfl_xor_sync(0xffffffffu, d2[i], o);
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < ROWS_PER_WARP; ++i) {
+                if (row0 + i < dv) {
+                    abuf[((size_t)col * H + h) * dv + row0 + i] = d2[i];
+                    if (abuf16) abuf16[((size_t)col * H + h) * dv + row0 + i] = __float2bfloat16_rn(d2[i]);
+                }
             }
         }
+        if (!more) break;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) { qn[e] = qx[e]; kn[e] = kx[e]; }
+#pragma unroll
+        for (int i = 0; i < ROWS_PER_WARP; ++i) vr[i] = vx[i];
+        beta = bx;
+        alpha = ax;
     }
 #pragma unroll
     for (int i = 0; i < ROWS_PER_WARP; ++i)

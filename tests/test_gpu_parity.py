@@ -182,7 +182,7 @@ def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name,
 @pytest.mark.parametrize("name,lens,decode_path", [("bf16", [131], "chain"), ("bf16", [1, 2, 130, 60, 201, 17], "auto"),
                                                    ("bf16_w_f32_kv", [300, 5, 129], "chain"), ("bf16", [257], "grid")])
 def test_prompt_by_columns_matches_oracle(api, tmp_path, monkeypatch, name, lens, decode_path):
-    """The prompt consumed as columns of tensor-core steps (128 per chunk; prompts that end inside a
+    """The prompt consumed as columns of tensor-core steps (256 per chunk; prompts that end inside a
     chunk, span several, or have a single token), attention and delta-net layers mixed, PLE: the
     decode steps that follow, teacher-forced on the oracle's tokens, give its logits within 2e-2,
     and the positions are those the token loop leaves."""
