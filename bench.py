@@ -324,7 +324,7 @@ def main():
         "ms_per_token_p50": float(np.median(step_ms)), "ms_per_token_p50_l2_warm": float(np.median(warm_step_ms)),
         "e2e": {"value": world * batch * K / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
                 "d2h_bytes_per_step": 4 * batch,
-                "how": "mlb_decode_step per token: pending id from pinned host memory, picked id back to the host"},
+                "how": "mlb_decode_step per token with host buffers: the pending id is read from pinned host memory by the step's first kernel, the picked id and the error word are written to pinned host memory by its last one; one graph launch and one stream synchronisation per token"},
         "gpu_launches": launches * K, "launches_per_step": launches,
         "prompt": {"tokens_per_s": batch * (prompt_len - 1) / prompt_s, "ms": prompt_s * 1e3,
                    "how": "mlb_prefill of the workload's prompts, second call, host clock (outside the timed decode steps)"},

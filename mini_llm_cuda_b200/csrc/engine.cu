@@ -383,6 +383,11 @@ struct mlb_session {
     int g_topk = -1; float g_temp = 0.f;
     int cur_topk = 50; float cur_temp = 1.f;
     int launches_per_step[3] = {0, 0, 0};
+    // one-token call as ONE graph: upload of the pending ids, the step, read-back of ids and error word
+    cudaGraphExec_t tgraphs[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};     // [kind][with input ids]
+    int tg_topk[2] = {-1, -1}; float tg_temp[2] = {0.f, 0.f};
+    int* pinned_out = nullptr;
+    int ctl_host_io = 0;                    // while the one-token graph is captured: 1 = ids and error word to the host, 2 = + ids from the host
     float4* flush_buf = nullptr; size_t flush_n = 0;
     int* pinned_tok = nullptr;
     bool use_pdl = true;
@@ -453,8 +458,10 @@ static void free_session(mlb_session* s) {
     if (s->stream) cudaStreamSynchronize(s->stream);
     if (s->cols) free_session(s->cols);
     for (auto& g : s->graphs) if (g) cudaGraphExecDestroy(g);
+    for (auto& g : s->tgraphs) if (g) cudaGraphExecDestroy(g);
     for (void* p : s->allocs) cudaFree(p);
     if (s->pinned_tok) cudaFreeHost(s->pinned_tok);
+    if (s->pinned_out) cudaFreeHost(s->pinned_out);
     if (s->pinned_err) cudaFreeHost(s->pinned_err);
     if (s->stream && !s->parent) cudaStreamDestroy(s->stream);      // a column set runs on its parent's stream
     delete s;
@@ -472,6 +479,10 @@ static StepCtl make_ctl(mlb_session* s, int kind) {
     c.out_ring = s->out_ring;
     c.out_idx = s->out_idx;
     c.out_cap = s->max_ctx;
+    c.tok_src = s->ctl_host_io == 2 ? s->pinned_tok : nullptr;
+    c.host_out = s->ctl_host_io ? s->pinned_out : nullptr;
+    c.host_err = s->ctl_host_io ? s->pinned_err : nullptr;
+    c.dev_err = s->dev_err;
     return c;
 }
 
@@ -1416,6 +1427,36 @@ static int ensure_graph(mlb_session* s, int kind) {
     return MLB_OK;
 }
 
+// The one-token call (mlb_decode_step) as a single graph of the step's own kernels: the embedding
+// kernel reads the pending ids from pinned host memory, the kernel that advances a sequence writes
+// the picked id and the error word there. One launch and one synchronisation per token, no copy
+// queued around the step (as graph nodes such copies cost more than the enqueues they replaced:
+// 199 vs 188 us per token). The error word is copied when sequence 0 advances: a wait that runs out
+// in the very last kernel of a step may be reported one call late.
+static int ensure_token_graph(mlb_session* s, int kind, bool with_input) {
+    const int idx = kind * 2 + (with_input ? 1 : 0);
+    if (kind == CHAIN_TOPK && s->tgraphs[idx] && (s->tg_topk[with_input] != s->cur_topk || s->tg_temp[with_input] != s->cur_temp)) {
+        cudaGraphExecDestroy(s->tgraphs[idx]);
+        s->tgraphs[idx] = nullptr;
+    }
+    if (s->tgraphs[idx]) return MLB_OK;
+    cudaGraph_t graph = nullptr;
+    CU(cudaStreamBeginCapture(s->stream, cudaStreamCaptureModeThreadLocal));
+    int n = 0;
+    s->ctl_host_io = with_input ? 2 : 1;
+    int rc = chain_run(s, kind, nullptr, &n);
+    s->ctl_host_io = 0;
+    cudaError_t e = cudaStreamEndCapture(s->stream, &graph);
+    if (rc) { if (graph) cudaGraphDestroy(graph); return rc; }
+    if (e != cudaSuccess) return fail(MLB_E_CUDA, "capture of the one-token graph failed: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&s->tgraphs[idx], graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return fail(MLB_E_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
+    s->launches_per_step[kind] = n;
+    if (kind == CHAIN_TOPK) { s->tg_topk[with_input] = s->cur_topk; s->tg_temp[with_input] = s->cur_temp; }
+    return MLB_OK;
+}
+
 // One step on the session's stream: the captured chain, or the single cooperative kernel.
 static int launch_step(mlb_session* s, int kind) {
     if (s->use_grid) return chain_run(s, kind, nullptr, nullptr);
@@ -1551,6 +1592,7 @@ static int session_create(mlb_model* m, int batch, int max_context, int kv_block
         SA(sess_alloc(s, (void**)&s->flush_buf, s->flush_n * 16, false));
     }
     SCU(cudaMallocHost((void**)&s->pinned_tok, B * 4));
+    SCU(cudaMallocHost((void**)&s->pinned_out, B * 4));
     SCU(cudaMallocHost((void**)&s->pinned_err, 4));
     *s->pinned_err = 0;
     s->alloc.num_pages = s->kv_pages;
@@ -1764,15 +1806,25 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
     int kind, rc;
     if ((rc = apply_sampling(s, sp, &kind))) return rc;
     if ((rc = grow_pages(s, n))) return rc;
-    if ((rc = ensure_graph(s, kind))) return rc;
     if (in_tokens) {
         const int V = s->m->cfg.vocab;
         for (int b = 0; b < B; ++b) {
             if (in_tokens[b] < 0 || in_tokens[b] >= V) return fail(MLB_E_INVALID, "sequence %d: token %d is outside the vocabulary", b, in_tokens[b]);
             s->pinned_tok[b] = in_tokens[b];
         }
-        CU(cudaMemcpyAsync(s->tok, s->pinned_tok, (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
     }
+    if (n == 1 && !step_ms && !s->use_grid && !s->use_cluster) {
+        // the one-token call: one graph launch, one synchronisation
+        if ((rc = ensure_token_graph(s, kind, in_tokens != nullptr))) return rc;
+        CU(cudaGraphLaunch(s->tgraphs[kind * 2 + (in_tokens ? 1 : 0)], s->stream));
+        CU(cudaStreamSynchronize(s->stream));
+        for (int b = 0; b < B; ++b) out_tokens[b] = s->h_pos[b] < s->max_ctx ? s->pinned_out[b] : -1;
+        for (int b = 0; b < B; ++b) s->h_pos[b] = std::min(s->h_pos[b] + 1, s->max_ctx);
+        s->have_logits = true;
+        return check_err_readback(s);
+    }
+    if ((rc = ensure_graph(s, kind))) return rc;
+    if (in_tokens) CU(cudaMemcpyAsync(s->tok, s->pinned_tok, (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
     CU(cudaMemsetAsync(s->out_idx, 0, (size_t)B * 4, s->stream));
     std::vector<cudaEvent_t> ev;
     if (step_ms) {

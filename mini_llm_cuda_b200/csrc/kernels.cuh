@@ -123,6 +123,12 @@ struct StepCtl {
     int* out_ring;       // [B][out_cap]
     int* out_idx;        // [B]
     int out_cap;
+    // one-token call: ids and the error word cross the bus inside the step's own kernels (pinned host
+    // memory mapped into the device), instead of as copies queued around the step; all null otherwise
+    const int* tok_src;  // [B] pending ids in host memory, read by the embedding kernel
+    int* host_out;       // [B] picked ids, written where the sequence advances
+    int* host_err;       // copy of *dev_err at the end of the step
+    const int* dev_err;
 };
 
 __device__ __forceinline__ bool seq_active(const StepCtl& c, int b) {
@@ -141,6 +147,8 @@ __device__ __forceinline__ void advance_seq(const StepCtl& c, int b, int sampled
         if (oi < c.out_cap) c.out_ring[(size_t)b * c.out_cap + oi] = sampled;
         c.out_idx[b] = oi + 1;
         c.tok[b] = sampled;
+        if (c.host_out != nullptr) c.host_out[b] = sampled;
+        if (c.host_err != nullptr && b == 0) *c.host_err = *c.dev_err;
     }
     c.pos[b] = p + 1;
 }
@@ -167,6 +175,11 @@ __global__ void embed_kernel(StepCtl c, const T* __restrict__ E, const float* __
     int b = blockIdx.x;
     if (!seq_active(c, b)) return;
     int t = c.tok[b];
+    if (c.tok_src != nullptr) {
+        // the pending id comes straight from host memory; later kernels of the step read the device copy
+        t = c.tok_src[b];
+        if (blockIdx.y == 0 && threadIdx.x == 0) c.tok[b] = t;
+    }
     extern __shared__ __align__(16) float trow[];
     if (p > 0) {
         for (int j = threadIdx.x; j < p; j += blockDim.x) trow[j] = Elem<T2>::get(pleT, (size_t)t * p + j);

@@ -77,6 +77,7 @@ int run_attn(void* scratch, const void* kpool, const void* vpool, int kv_dtype, 
     c.B = batch; c.vocab = 0;
     c.pos = const_cast<int*>(positions); c.tok = nullptr; c.limit = sc.limit;
     c.prompt = nullptr; c.prompt_stride = 0; c.out_ring = nullptr; c.out_idx = nullptr; c.out_cap = 0;
+    c.tok_src = nullptr; c.host_out = nullptr; c.host_err = nullptr; c.dev_err = nullptr;
     AttnParams p;
     p.kpool = kpool; p.vpool = vpool; p.page_table = page_table; p.pt_stride = pt_stride;
     p.qbuf = q; p.gbuf = gate; p.abuf = out; p.abuf16 = nullptr; p.part = sc.part; p.ticket = sc.ticket;
