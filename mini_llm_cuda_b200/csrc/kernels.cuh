@@ -704,72 +704,96 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     const int span = pg_end - pg_begin - warp;
     const int npw = span > 0 ? (span + NW - 1) / NW : 0;
     int pidx = 0;
-    for (int i = 0; i < npw; ++i) {
-        if ((i & 31) == 0) {
+    constexpr int CPP = ITERS / CH;                // chunks per page
+    const int nq = npw * CPP;                      // this warp's chunks, in order
+    // All loads of a chunk first, then the scores of its positions (independent of one another), one
+    // rescale of the running sums and one exponential per position.
+    auto load_chunk = [&](int qi, uint4* kk, uint4* vv4, int& cnt, int& c0) {
+        const int i = qi / CPP;
+        c0 = (qi - i * CPP) * CH;
+        if (c0 == 0 && (i & 31) == 0) {
             const int ii = i + lane;
             pidx = ii < npw ? pt[pg_begin + warp + NW * ii] : 0;
         }
         const int pg = pg_begin + warp + NW * i;
         const int page = __shfl_sync(0xffffffffu, pidx, i & 31);
-        const int cnt = min(kKvBlock, ctx - pg * kKvBlock);
+        cnt = min(kKvBlock, ctx - pg * kKvBlock);
         const size_t base = ((size_t)page * p.kv_heads + kvh) * kKvBlock * HD;
 #pragma unroll
-        for (int c0 = 0; c0 < ITERS; c0 += CH) {
-            // all loads of the chunk first, then the scores of its positions (independent of one
-            // another), one rescale of the running sums and one exponential per position
-            uint4 kk[CH], vv4[CH];
-#pragma unroll
-            for (int u = 0; u < CH; ++u) {
-                const int j = (c0 + u) * PPI + grp;
-                kk[u] = make_uint4(0, 0, 0, 0);
-                vv4[u] = make_uint4(0, 0, 0, 0);
-                if (j < cnt) {
-                    kk[u] = __ldcg(reinterpret_cast<const uint4*>(kpool + base + (size_t)j * HD + lr * EPL));
-                    vv4[u] = __ldcg(reinterpret_cast<const uint4*>(vpool + base + (size_t)j * HD + lr * EPL));
-                }
+        for (int u = 0; u < CH; ++u) {
+            const int j = (c0 + u) * PPI + grp;
+            kk[u] = make_uint4(0, 0, 0, 0);
+            vv4[u] = make_uint4(0, 0, 0, 0);
+            if (j < cnt) {
+                kk[u] = __ldcg(reinterpret_cast<const uint4*>(kpool + base + (size_t)j * HD + lr * EPL));
+                vv4[u] = __ldcg(reinterpret_cast<const uint4*>(vpool + base + (size_t)j * HD + lr * EPL));
             }
-            float sv[G][CH];
+        }
+    };
+    auto use_chunk = [&](const uint4* kk, const uint4* vv4, int cnt, int c0) {
+        float sv[G][CH];
+#pragma unroll
+        for (int u = 0; u < CH; ++u) {
+            const bool valid = (c0 + u) * PPI + grp < cnt;
+            float kv[EPL];
+            Elem<KVT>::unpack(kk[u], kv);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float sdot = 0.f;
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) sdot = fmaf(q[g][e], kv[e], sdot);
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
+                sv[g][u] = valid ? sdot / inv_div : kNegBig;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float mn = m[g];
+#pragma unroll
+            for (int u = 0; u < CH; ++u) mn = fmaxf(mn, sv[g][u]);
+            const float sc = expf(m[g] - mn);
+            l[g] *= sc;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) acc[g][e] *= sc;
 #pragma unroll
             for (int u = 0; u < CH; ++u) {
                 const bool valid = (c0 + u) * PPI + grp < cnt;
-                float kv[EPL];
-                Elem<KVT>::unpack(kk[u], kv);
-#pragma unroll
-                for (int g = 0; g < G; ++g) {
-                    float sdot = 0.f;
-#pragma unroll
-                    for (int e = 0; e < EPL; ++e) sdot = fmaf(q[g][e], kv[e], sdot);
-#pragma unroll
-                    for (int o = LPR / 2; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
-                    sv[g][u] = valid ? sdot / inv_div : kNegBig;
-                }
+                sv[g][u] = valid ? expf(sv[g][u] - mn) : 0.f;
+                l[g] += sv[g][u];
             }
+            m[g] = mn;
+        }
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float mn = m[g];
+        for (int u = 0; u < CH; ++u) {
+            float vv[EPL];
+            Elem<KVT>::unpack(vv4[u], vv);
 #pragma unroll
-                for (int u = 0; u < CH; ++u) mn = fmaxf(mn, sv[g][u]);
-                const float sc = expf(m[g] - mn);
-                l[g] *= sc;
+            for (int g = 0; g < G; ++g)
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) acc[g][e] *= sc;
-#pragma unroll
-                for (int u = 0; u < CH; ++u) {
-                    const bool valid = (c0 + u) * PPI + grp < cnt;
-                    sv[g][u] = valid ? expf(sv[g][u] - mn) : 0.f;
-                    l[g] += sv[g][u];
-                }
-                m[g] = mn;
+                for (int e = 0; e < EPL; ++e) acc[g][e] = fmaf(sv[g][u], vv[e], acc[g][e]);
+        }
+    };
+    if (G <= 2) {
+        // few heads per CTA leave registers for a second chunk: the next chunk's loads are in flight
+        // while the current one is used (twice the bytes in flight per warp)
+        uint4 ka[CH], va[CH], kb[CH], vb[CH];
+        int cnt_a = 0, c0_a = 0, cnt_b = 0, c0_b = 0;
+        if (nq > 0) load_chunk(0, ka, va, cnt_a, c0_a);
+        for (int qi = 0; qi < nq; qi += 2) {
+            if (qi + 1 < nq) load_chunk(qi + 1, kb, vb, cnt_b, c0_b);
+            use_chunk(ka, va, cnt_a, c0_a);
+            if (qi + 1 < nq) {
+                if (qi + 2 < nq) load_chunk(qi + 2, ka, va, cnt_a, c0_a);
+                use_chunk(kb, vb, cnt_b, c0_b);
             }
-#pragma unroll
-            for (int u = 0; u < CH; ++u) {
-                float vv[EPL];
-                Elem<KVT>::unpack(vv4[u], vv);
-#pragma unroll
-                for (int g = 0; g < G; ++g)
-#pragma unroll
-                    for (int e = 0; e < EPL; ++e) acc[g][e] = fmaf(sv[g][u], vv[e], acc[g][e]);
-            }
+        }
+    } else {
+        uint4 ka[CH], va[CH];
+        int cnt_a = 0, c0_a = 0;
+        for (int qi = 0; qi < nq; ++qi) {
+            load_chunk(qi, ka, va, cnt_a, c0_a);
+            use_chunk(ka, va, cnt_a, c0_a);
         }
     }
     // merge the PPI lane groups of the warp
