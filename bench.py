@@ -330,6 +330,16 @@ def main():
                    "how": "mlb_prefill of the workload's prompts, second call, host clock (outside the timed decode steps)"},
         "roofline": roofline, "step_roofline": step_roofline, "kernels": kernels, "clocks": clock_info,
     }
+    # ---- scoring forward (teacher-forced full-sequence logits), where the model allows it ----
+    if spec.weight_dtype == "bfloat16":
+        n_score = min(512, spec.max_context)
+        stoks = prompt_for(spec.vocab, n_score, 7 + rank)
+        sess.score(stoks)
+        t0 = time.perf_counter()
+        sess.score(stoks)
+        score_s = time.perf_counter() - t0
+        out["score"] = {"tokens_per_s": n_score / score_s, "ms": score_s * 1e3,
+                        "how": f"mlb_score_tokens on {n_score} tokens, second call, host clock, [len][V] fp32 logits copied to the host"}
     sess.close()
 
     # ---- (5) batched decode (256 sequences sharded over the GPUs, top-k 50 sampling) ------

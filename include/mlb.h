@@ -113,6 +113,16 @@ void mlb_session_free(mlb_session* s);
  * MLB_E_UNSUPPORTED where they cannot run. */
 int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride);
 
+/* Teacher-forced scoring forward: the full-sequence forward of runInference(L)
+ * (inference.cu:376-752), whose [V x L] scores the reference's trainer consumes
+ * (training_orchestrator.cu:308). logits_out [len][V] fp32 host, row t = prediction after
+ * tokens[0..t] (the reference's column t of vocabScores_DEVICE, before the softmax). The tokens
+ * run as columns of tensor-core steps like a long prompt, with the LM head on every column:
+ * needs bf16 weights (MLB_E_UNSUPPORTED otherwise); activations are bf16, i.e. the logits agree
+ * with the fp32 forward within the low-precision tolerance. Uses sequence 0 of the session; the
+ * session is reset before and after. */
+int mlb_score_tokens(mlb_session* s, const int32_t* tokens, int len, float* logits_out);
+
 /* Replaces one iteration of the while loop of runInferenceLoop
  * (inference_orchestrator.cu:64-160): forward for the pending token of every sequence, pick
  * the next token on the device, append it. in_tokens (nullable) overrides the pending tokens

@@ -86,6 +86,7 @@ def lib() -> C.CDLL:
         "mlb_session_launches_per_step": (C.c_int, [vp]),
         "mlb_session_grid_timers": (C.c_int, [vp, C.POINTER(C.c_longlong), C.c_int]),
         "mlb_op_wait_probe": (C.c_int, [C.c_int, C.c_uint32]),
+        "mlb_score_tokens": (C.c_int, [vp, C.POINTER(C.c_int32), C.c_int, C.POINTER(C.c_float)]),
         "mlb_kv_alloc_new": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
         "mlb_kv_alloc_ensure": (C.c_int, [vp, C.c_int, C.c_int, C.c_int]),
         "mlb_kv_alloc_table": (C.c_int, [vp, C.c_int, i32p, C.c_int]),
@@ -232,6 +233,13 @@ class Session:
         for b, p in enumerate(prompts):
             toks[b, :len(p)] = p
         check(lib().mlb_prefill(self._h, _ptr(toks, C.c_int32), _ptr(lens, C.c_int32), stride))
+
+    def score(self, tokens: Sequence[int]) -> np.ndarray:
+        """Logits [len][V] of every position of one token sequence (teacher-forced forward)."""
+        t = _i32(tokens)
+        out = np.empty((len(t), self.model.config.vocab), dtype=np.float32)
+        check(lib().mlb_score_tokens(self._h, _ptr(t, C.c_int32), len(t), _ptr(out, C.c_float)))
+        return out
 
     def decode_step(self, sampling: Optional[dict] = None, in_tokens=None) -> np.ndarray:
         out = np.empty(self.batch, dtype=np.int32)

@@ -478,7 +478,7 @@ static StepCtl make_ctl(mlb_session* s, int kind) {
     c.prompt_stride = s->max_ctx;
     c.out_ring = s->out_ring;
     c.out_idx = s->out_idx;
-    c.out_cap = s->max_ctx;
+    c.out_cap = s->parent ? 0 : s->max_ctx;     // a column set has no output ring
     c.tok_src = s->ctl_host_io == 2 ? s->pinned_tok : nullptr;
     c.host_out = s->ctl_host_io ? s->pinned_out : nullptr;
     c.host_err = s->ctl_host_io ? s->pinned_err : nullptr;
@@ -1670,14 +1670,18 @@ extern "C" void mlb_session_free(mlb_session* s) { free_session(s); }
 // chunk: auto takes this path from 64 prompt tokens on (its activations are bf16, so the cache
 // differs from the token loop's within the low-precision tolerance); `*done` tells whether it ran.
 static const int kPromptCols = 256;
-static int prefill_columns(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride, bool* done) {
+// score_out != null: the scoring forward instead (mlb_score_tokens): every token of sequence 0 is a
+// column, the LM head runs on the columns too, and the logits of each chunk go to score_out.
+static int prefill_columns(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride, bool* done, float* score_out = nullptr) {
     *done = false;
     const char* env = std::getenv("MLB_PREFILL");
-    const std::string mode = env ? env : "auto";
+    const std::string mode = score_out ? "chunk" : (env ? env : "auto");
     if (mode == "step") return MLB_OK;
-    const int B = s->B;
+    const int B = score_out ? 1 : s->B;
+    const int keep = score_out ? 0 : 1;            // tokens per prompt that stay pending
+    const int kind = score_out ? CHAIN_GREEDY : CHAIN_PREFILL;
     long total = 0;
-    for (int b = 0; b < B; ++b) total += lens[b] - 1;
+    for (int b = 0; b < B; ++b) total += lens[b] - keep;
     if (total < 1 || (mode == "auto" && total < 64)) return MLB_OK;
     if (s->m->cfg.weight_dtype != MLB_DT_BF16) {
         if (mode == "chunk") return fail(MLB_E_UNSUPPORTED, "MLB_PREFILL=chunk needs bf16 weights");
@@ -1695,7 +1699,9 @@ static int prefill_columns(mlb_session* s, const int32_t* tokens, const int32_t*
     if (!cs) return MLB_OK;
     const int T = cs->B, MP = s->max_pages;
     int rc;
-    if ((rc = ensure_graph(cs, CHAIN_PREFILL))) return rc;
+    if ((rc = ensure_graph(cs, kind))) return rc;
+    const size_t V = (size_t)s->m->cfg.vocab;
+    size_t scored = 0;
     std::vector<int> h_tok(T), h_pos(T), h_lim(T), h_seq(T), h_tab((size_t)T * MP);
     // A chunk takes the next tokens of as many sequences as it can, an equal share each: the
     // delta-net recurrence is serial along a sequence and parallel across sequences, so 64 sequences
@@ -1704,11 +1710,11 @@ static int prefill_columns(mlb_session* s, const int32_t* tokens, const int32_t*
     long left = total;
     while (left > 0) {
         int n_active = 0;
-        for (int b = 0; b < B; ++b) n_active += cursor[b] < lens[b] - 1 ? 1 : 0;
+        for (int b = 0; b < B; ++b) n_active += cursor[b] < lens[b] - keep ? 1 : 0;
         const int share = std::max(1, T / n_active);
         int n = 0;
         for (int b = 0; b < B && n < T; ++b) {
-            const int take = std::min(std::min(share, lens[b] - 1 - cursor[b]), T - n);
+            const int take = std::min(std::min(share, lens[b] - keep - cursor[b]), T - n);
             for (int i = 0; i < take; ++i, ++n) {
                 const int t = cursor[b] + i;
                 h_tok[n] = tokens[(size_t)b * stride + t];
@@ -1723,17 +1729,24 @@ static int prefill_columns(mlb_session* s, const int32_t* tokens, const int32_t*
         for (int i = n; i < T; ++i) { h_tok[i] = 0; h_pos[i] = 0; h_lim[i] = 0; h_seq[i] = 0; }      // idle columns
         CU(cudaMemcpyAsync(cs->tok, h_tok.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
         CU(cudaMemcpyAsync(cs->pos, h_pos.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
-        CU(cudaMemcpyAsync(cs->limit_prefill, h_lim.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
+        CU(cudaMemcpyAsync(kind == CHAIN_PREFILL ? cs->limit_prefill : cs->limit_decode, h_lim.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
         CU(cudaMemcpyAsync(cs->seq_of, h_seq.data(), (size_t)T * 4, cudaMemcpyHostToDevice, s->stream));
         CU(cudaMemcpyAsync(cs->page_table, h_tab.data(), h_tab.size() * 4, cudaMemcpyHostToDevice, s->stream));
-        CU(cudaGraphLaunch(cs->graphs[CHAIN_PREFILL], s->stream));
+        CU(cudaGraphLaunch(cs->graphs[kind], s->stream));
+        if (score_out) {
+            // one sequence: the columns of a chunk are its next n positions, in order
+            CU(cudaMemcpyAsync(score_out + scored * V, cs->logits, (size_t)n * V * 4, cudaMemcpyDeviceToHost, s->stream));
+            scored += (size_t)n;
+        }
         CU(cudaStreamSynchronize(s->stream));          // the host arrays are rewritten for the next chunk
     }
-    // what the token loop would have left: position len-1 with the last prompt token pending
-    std::vector<int> pos(B), last(B);
-    for (int i = 0; i < B; ++i) { pos[i] = lens[i] - 1; last[i] = tokens[(size_t)i * stride + lens[i] - 1]; }
-    CU(cudaMemcpyAsync(s->pos, pos.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
-    CU(cudaMemcpyAsync(s->tok, last.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
+    if (!score_out) {
+        // what the token loop would have left: position len-1 with the last prompt token pending
+        std::vector<int> pos(B), last(B);
+        for (int i = 0; i < B; ++i) { pos[i] = lens[i] - 1; last[i] = tokens[(size_t)i * stride + lens[i] - 1]; }
+        CU(cudaMemcpyAsync(s->pos, pos.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
+        CU(cudaMemcpyAsync(s->tok, last.data(), (size_t)B * 4, cudaMemcpyHostToDevice, s->stream));
+    }
     if ((rc = queue_err_readback(cs))) return rc;
     CU(cudaStreamSynchronize(s->stream));
     *done = true;
@@ -1789,6 +1802,33 @@ extern "C" int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t*
     CU(cudaStreamSynchronize(s->stream));
     for (int b = 0; b < B; ++b) s->h_pos[b] = lens[b] - 1;
     return check_err_readback(s);
+}
+
+extern "C" int mlb_score_tokens(mlb_session* s, const int32_t* tokens, int len, float* logits_out) {
+    if (!s || !tokens || !logits_out) return fail(MLB_E_INVALID, "null argument");
+    if (len < 1) return fail(MLB_E_INVALID, "len must be >= 1");
+    if (len > s->max_ctx) return fail(MLB_E_CONTEXT_FULL, "%d tokens exceed max_context %d", len, s->max_ctx);
+    CU(cudaSetDevice(s->m->device));
+    const int V = s->m->cfg.vocab;
+    for (int i = 0; i < len; ++i)
+        if (tokens[i] < 0 || tokens[i] >= V) return fail(MLB_E_INVALID, "token %d at position %d is outside the vocabulary (%d)", tokens[i], i, V);
+    if (s->m->cfg.weight_dtype != MLB_DT_BF16) return fail(MLB_E_UNSUPPORTED, "the scoring forward needs bf16 weights (tensor-core columns)");
+    int rc = mlb_session_reset(s);
+    if (rc) return rc;
+    bool has_attn = false;
+    for (auto* p : s->kpool) if (p) has_attn = true;
+    if (has_attn) {
+        if ((rc = kv_ensure(&s->alloc, 0, len, kKvBlock))) return rc;
+        s->table_dirty = true;
+        if ((rc = sync_page_table(s))) return rc;
+    }
+    bool done = false;
+    const int32_t lens[1] = {len};
+    rc = prefill_columns(s, tokens, lens, len, &done, logits_out);
+    const int rc2 = mlb_session_reset(s);          // the cache holds the scored sequence: not a state to decode from
+    if (rc) return rc;
+    if (!done) return fail(MLB_E_UNSUPPORTED, "the scoring forward could not set up its tensor-core columns");
+    return rc2;
 }
 
 namespace mlb {

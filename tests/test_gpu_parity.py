@@ -222,6 +222,39 @@ def test_prompt_by_columns_matches_oracle(api, tmp_path, monkeypatch, name, lens
     model.close()
 
 
+@pytest.mark.parametrize("name,length", [("bf16", 40), ("bf16", 300), ("bf16_w_f32_kv", 257)])
+def test_scoring_forward_matches_oracle(api, tmp_path, name, length):
+    """mlb_score_tokens: logits of every position of one sequence (the reference's full forward
+    runInference(L)) against the KV-cached oracle fed the same tokens: within 2e-2 at every
+    position, identical argmax wherever the oracle's top-2 margin exceeds that bound. One chunk, and
+    several chunks with the run of columns continuing across them."""
+    spec = dataclasses.replace(SPECS[name], max_context=512)
+    path = write_model(tmp_path, spec, seed=31)
+    oracle = load_oracle(path)
+    tokens = random_prompts(spec.vocab, [length], seed=37)[0]
+    st = oracle.new_state()
+    want = np.stack([np.asarray(oracle.step(st, int(t))) for t in tokens])
+    model = api.Model(path)
+    sess = api.Session(model, 2)
+    got = sess.score(tokens)
+    assert got.shape == want.shape
+    worst = max(logits_error(got[i], want[i]) for i in range(length))
+    assert worst < TOL_LOWP, worst
+    checked = 0
+    for i in range(length):
+        top2 = np.sort(want[i])[-2:]
+        if (top2[1] - top2[0]) > 2 * TOL_LOWP * np.abs(want[i]).max():
+            assert int(np.argmax(got[i])) == int(np.argmax(want[i])), i
+            checked += 1
+    assert checked > length // 4
+    # the session is reset: a prompt and a decode step work as on a fresh one
+    sess.prefill([tokens[:20], tokens[:7]])
+    assert sess.positions().tolist() == [19, 6]
+    sess.decode_step()
+    sess.close()
+    model.close()
+
+
 def test_prompt_by_columns_needs_bf16_weights(api, tmp_path, monkeypatch):
     monkeypatch.setenv("MLB_PREFILL", "chunk")
     spec = SPECS["attn_fp32"]
