@@ -9,8 +9,8 @@
 //   * a producer warp streams those slabs with cp.async.bulk (TMA; every CTA loads only its own data) into a ring of
 //     shared-memory stages guarded by mbarriers, running ahead of the consumers across phase
 //     boundaries, so that ~100+ KB per SM are in flight without holding registers;
-//   * 16 consumer warps compute dot products out of shared memory with the activation vector
-//     held in registers, and push each result into the shared memory of ALL CTAs of the cluster
+//   * 15 consumer warps compute dot products out of shared memory, two rows per read of the
+//     activation vector, and push each result into the shared memory of ALL CTAs of the cluster
 //     (distributed shared memory); a hardware cluster barrier separates the phases.
 // Activations never leave the SMs between phases and a phase boundary costs a cluster barrier
 // instead of a kernel launch. One cluster per GPC can run at a time, so a few sequences decode

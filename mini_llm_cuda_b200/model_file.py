@@ -25,6 +25,13 @@ Two top-level keys that the reference does not know are appended after
             decay gate weights); their data follows the last block, in list order.
 
 Tensor dtypes in the file: ``float32``, ``float64`` (reference) and ``bfloat16``.
+
+``read_model_bin`` is the inverse of the writer, and ``convert_model_bin`` turns a file
+written for the reference (fp32 / fp64, dims in its ``network_meta.h``) into one that carries
+its own ``config`` and, optionally, bf16 tensors:
+
+    python -m mini_llm_cuda_b200.model_file convert model/in.bin model/out.bin \
+        --heads 8 --head-dim 64 --file-dtype bfloat16 --weight-dtype bfloat16 --kv-dtype bfloat16
 """
 from __future__ import annotations
 
@@ -245,6 +252,121 @@ def write_model_bin(path: str, spec: ModelSpec, weights: dict, file_dtype: str =
             f.write(c)
 
 
+def _decode(buf: bytes, shape, dtype: str) -> np.ndarray:
+    n = int(np.prod(shape)) if len(shape) else 1
+    if dtype == "float32":
+        a = np.frombuffer(buf, dtype="<f4", count=n).astype(np.float32)
+    elif dtype == "float64":
+        a = np.frombuffer(buf, dtype="<f8", count=n).astype(np.float32)     # narrowed as load_model.cu:81-85 does
+    elif dtype == "bfloat16":
+        a = (np.frombuffer(buf, dtype="<u2", count=n).astype(np.uint32) << 16).view(np.float32)
+    else:
+        raise ValueError(f"Unsupported dtype: {dtype}")                      # load_model.cu:55-57
+    return a.reshape(shape)
+
+
+_DT_SIZE = {"float32": 4, "float64": 8, "bfloat16": 2}
+
+
+def read_model_bin(path: str):
+    """Inverse of :func:`write_model_bin`: returns ``(header, weights)`` with ``weights`` in the
+    dict layout of :func:`synth_weights` (fp32 arrays; ``ext`` present when the file has it).
+    Tensors are consumed positionally in header order, as load_model.cu:411-450 does."""
+    with open(path, "rb") as f:
+        raw = f.read()
+    if len(raw) < 8:
+        raise ValueError("file shorter than its header length field")
+    (hlen,) = struct.unpack_from("<Q", raw, 0)
+    if 8 + hlen > len(raw):
+        raise ValueError("header length exceeds the file")
+    header = json.loads(raw[8:8 + hlen].decode("utf-8"))
+    off = 8 + hlen
+    off += (8 - off % 8) % 8
+
+    def take(meta):
+        nonlocal off
+        shape = [int(x) for x in meta["shape"]]
+        nbytes = int(np.prod(shape)) * _DT_SIZE.get(meta["dtype"], 0)
+        if meta["dtype"] not in _DT_SIZE:
+            raise ValueError(f"Unsupported dtype: {meta['dtype']}")
+        if off + nbytes > len(raw):
+            raise ValueError("tensor data exceeds the file")
+        a = _decode(raw[off:off + nbytes], shape, meta["dtype"])
+        off += nbytes
+        return a
+
+    weights = {"tokenEmbeddings": take(header["tokenEmbeddings"]),
+               "finalRMSNormGamma": take(header["finalRMSNormGamma"]), "blocks": []}
+    for blk in header["transformerBlocks"]:
+        weights["blocks"].append({k: take(m) for k, m in blk.items()})
+    if "ext" in header:
+        weights["ext"] = [dict() for _ in header["transformerBlocks"]]
+        for e in header["ext"]:
+            weights["ext"][int(e["block"])][e["name"]] = take(e)
+    return header, weights
+
+
+def convert_model_bin(src: str, dst: str, heads: int = 0, head_dim: int = 0, kv_heads: int = 0,
+                      file_dtype: str = "float32", weight_dtype: str = "", kv_dtype: str = "",
+                      rope_theta: float = 10000.0, rms_eps: float = 1e-8, max_context: int = 1024) -> ModelSpec:
+    """Rewrite ``src`` as a file that carries its own ``config`` (and bf16 tensors if asked).
+
+    A file that already has ``config`` keeps it (``weight_dtype`` / ``kv_dtype`` can still be
+    changed). A file written for the reference has none: ``heads`` and ``head_dim`` must be given
+    (the reference keeps them in network_meta.h), ``rope_theta``, ``rms_eps`` and ``max_context``
+    default to its values (ropeDenomBase 10000, eps 1e-8 of inference.cu:48); QK-norm and query
+    gating are recognised by their tensors. Returns the spec written."""
+    header, weights = read_model_bin(src)
+    E = weights["tokenEmbeddings"]
+    blocks = weights["blocks"]
+    if "config" in header:
+        c = dict(header["config"])
+        spec = ModelSpec(dim=int(E.shape[1]), layers=len(blocks), heads=int(c["heads"]), head_dim=int(c["head_dim"]),
+                         ffn_dim=int(blocks[0]["feedForwardWeights1A"].shape[0]), vocab=int(E.shape[0]),
+                         kv_heads=int(c.get("kv_heads", c["heads"])), max_context=int(c.get("max_context", max_context)),
+                         rope_theta=float(c.get("rope_theta", rope_theta)), rms_eps=float(c.get("rms_eps", rms_eps)),
+                         qk_norm=bool(c.get("qk_norm", False)), query_gating=bool(c.get("query_gating", False)),
+                         ple_dim=int(c.get("ple_dim", 0)), layer_types=list(c.get("layer_types", [])),
+                         dn_key_dim=c.get("dn_key_dim"), dn_value_dim=c.get("dn_value_dim"),
+                         weight_dtype=c.get("weight_dtype", "float32"), kv_dtype=c.get("kv_dtype", "float32"))
+    else:
+        if heads <= 0 or head_dim <= 0:
+            raise ValueError("a file without 'config' needs heads and head_dim (network_meta.h of the build that wrote it)")
+        spec = ModelSpec(dim=int(E.shape[1]), layers=len(blocks), heads=heads, head_dim=head_dim,
+                         ffn_dim=int(blocks[0]["feedForwardWeights1A"].shape[0]), vocab=int(E.shape[0]),
+                         kv_heads=kv_heads or heads, max_context=max_context, rope_theta=rope_theta, rms_eps=rms_eps,
+                         qk_norm="queryRMSGamma" in blocks[0], query_gating="gatedQueryWeights" in blocks[0])
+    if weight_dtype:
+        spec.weight_dtype = weight_dtype
+    if kv_dtype:
+        spec.kv_dtype = kv_dtype
+    write_model_bin(dst, spec, weights, file_dtype=file_dtype, with_config=True)
+    return spec
+
+
+def _main(argv) -> int:
+    import argparse
+    ap = argparse.ArgumentParser(prog="python -m mini_llm_cuda_b200.model_file")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    cv = sub.add_parser("convert", help="rewrite a model.bin with an embedded config, optionally as bf16")
+    cv.add_argument("src")
+    cv.add_argument("dst")
+    cv.add_argument("--heads", type=int, default=0)
+    cv.add_argument("--head-dim", type=int, default=0)
+    cv.add_argument("--kv-heads", type=int, default=0)
+    cv.add_argument("--file-dtype", default="float32", choices=["float32", "float64", "bfloat16"])
+    cv.add_argument("--weight-dtype", default="", choices=["", "float32", "bfloat16", "float8_e4m3"])
+    cv.add_argument("--kv-dtype", default="", choices=["", "float32", "bfloat16"])
+    cv.add_argument("--rope-theta", type=float, default=10000.0)
+    cv.add_argument("--rms-eps", type=float, default=1e-8)
+    cv.add_argument("--max-context", type=int, default=1024)
+    a = ap.parse_args(argv)
+    spec = convert_model_bin(a.src, a.dst, a.heads, a.head_dim, a.kv_heads, a.file_dtype, a.weight_dtype, a.kv_dtype,
+                             a.rope_theta, a.rms_eps, a.max_context)
+    print(json.dumps(spec.config_dict()))
+    return 0
+
+
 # The configurations the decode path is measured and checked on.
 def named_spec(name: str) -> ModelSpec:
     if name == "cfg0":      # CPU-runnable tiny model, fp32
@@ -269,3 +391,8 @@ def named_spec(name: str) -> ModelSpec:
                          layer_types=periodic_layer_types(24, 4),
                          weight_dtype="float8_e4m3", kv_dtype="bfloat16")
     raise KeyError(name)
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(_main(sys.argv[1:]))

@@ -3,6 +3,7 @@ import json
 import os
 import re
 import struct
+import sys
 
 import numpy as np
 import pytest
@@ -86,6 +87,41 @@ def test_writer_reader_round_trip_and_layout(tmp_path):
     # execution order N-1 .. 0: block 0 is the last layer, a delta-net one for cfg0
     assert spec.block_type(0) == "delta_net" and "betaWeights" in m["ext"][0]
     assert m["config"]["layer_types"] == ["attention", "delta_net", "attention", "delta_net"]
+
+
+def test_converter_gives_a_reference_file_its_config(api, tmp_path):
+    """A file as the reference's tools write it (fp32, no config key, QK-norm and gating tensors)
+    converted to a bf16 file with an embedded config: the product's own Python reader and the C++
+    parser agree with the oracle's reader on it, tensors are the nearest-even bf16 of the source, and
+    the command-line form writes the same bytes."""
+    import subprocess
+    import torch
+    from mini_llm_cuda_b200 import model_file as mf
+    spec = ModelSpec(dim=128, layers=2, heads=2, head_dim=64, ffn_dim=256, vocab=96, qk_norm=True, query_gating=True)
+    w = synth_weights(spec, seed=5, random_gains=True)
+    src = os.path.join(str(tmp_path), "ref.bin")
+    dst = os.path.join(str(tmp_path), "conv.bin")
+    write_model_bin(src, spec, w, with_config=False)
+    with pytest.raises(ValueError):
+        mf.convert_model_bin(src, dst)                      # heads / head_dim are not in a reference file
+    out = mf.convert_model_bin(src, dst, heads=2, head_dim=64, file_dtype="bfloat16", weight_dtype="bfloat16",
+                               kv_dtype="bfloat16", rms_eps=1e-8, max_context=256)
+    assert out.qk_norm and out.query_gating and out.kv_heads == 2 and out.dim == 128 and out.ffn_dim == 256
+    header, got = mf.read_model_bin(dst)
+    assert header["config"]["weight_dtype"] == "bfloat16" and header["config"]["max_context"] == 256
+    m = read_model_bin(dst)                                  # the oracle's reader
+    for k in ("queryWeights", "feedForwardWeights2", "gatedQueryWeights"):
+        want = torch.from_numpy(w["blocks"][1][k]).to(torch.bfloat16).float().numpy()
+        assert np.array_equal(got["blocks"][1][k], want) and np.array_equal(m["blocks"][1][k], want)
+    assert np.array_equal(got["blocks"][0]["queryRMSGamma"], w["blocks"][0]["queryRMSGamma"])     # gains stay fp32
+    cfg, nbytes = api.inspect_file(dst)
+    assert (cfg.heads, cfg.head_dim, cfg.qk_norm, cfg.query_gating, cfg.max_context) == (2, 64, 1, 1, 256)
+    dst2 = os.path.join(str(tmp_path), "conv2.bin")
+    r = subprocess.run([sys.executable, "-m", "mini_llm_cuda_b200.model_file", "convert", src, dst2, "--heads", "2",
+                        "--head-dim", "64", "--file-dtype", "bfloat16", "--weight-dtype", "bfloat16", "--kv-dtype",
+                        "bfloat16", "--max-context", "256"], capture_output=True, text=True, cwd=ROOT)
+    assert r.returncode == 0, r.stderr
+    assert open(dst, "rb").read() == open(dst2, "rb").read()
 
 
 def test_bf16_file_rounding_is_nearest_even(tmp_path):
