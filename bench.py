@@ -331,7 +331,7 @@ def main():
         "roofline": roofline, "step_roofline": step_roofline, "kernels": kernels, "clocks": clock_info,
     }
     # ---- scoring forward (teacher-forced full-sequence logits), where the model allows it ----
-    if spec.weight_dtype == "bfloat16":
+    if spec.weight_dtype in ("bfloat16", "float8_e4m3"):
         n_score = min(512, spec.max_context)
         stoks = prompt_for(spec.vocab, n_score, 7 + rank)
         sess.score(stoks)

@@ -106,9 +106,10 @@ void mlb_session_free(mlb_session* s);
 /* Replaces loadStoryContext's upload (main.cu:166) and the prompt part of the reference's
  * recompute-everything loop: ingests tokens[b*stride .. +lens[b]) for every sequence. After
  * it, position lens[b]-1 holds the last prompt token as the pending input of the next step.
- * With bf16 weights and 64 prompt tokens or more the prompt is consumed as columns of
+ * With bf16 or FP8 weights and 64 prompt tokens or more the prompt is consumed as columns of
  * tensor-core steps, 256 tokens at a time (bf16 activations: the cache equals the token loop's
- * within the low-precision tolerance); otherwise, or with MLB_PREFILL=step in the environment,
+ * within the low-precision tolerance; an FP8 model gets a bf16 copy of its weights on the device
+ * the first time, 2 bytes per weight); otherwise, or with MLB_PREFILL=step in the environment,
  * one token per step and sequence. MLB_PREFILL=chunk asks for the columns and fails with
  * MLB_E_UNSUPPORTED where they cannot run. */
 int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride);
@@ -118,7 +119,7 @@ int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t* lens, int 
  * (training_orchestrator.cu:308). logits_out [len][V] fp32 host, row t = prediction after
  * tokens[0..t] (the reference's column t of vocabScores_DEVICE, before the softmax). The tokens
  * run as columns of tensor-core steps like a long prompt, with the LM head on every column:
- * needs bf16 weights (MLB_E_UNSUPPORTED otherwise); activations are bf16, i.e. the logits agree
+ * needs bf16 or FP8 weights (MLB_E_UNSUPPORTED otherwise); activations are bf16, i.e. the logits agree
  * with the fp32 forward within the low-precision tolerance. Uses sequence 0 of the session; the
  * session is reset before and after. */
 int mlb_score_tokens(mlb_session* s, const int32_t* tokens, int len, float* logits_out);

@@ -9,6 +9,7 @@
 #include <cstring>
 #include <string>
 #include <type_traits>
+#include <mutex>
 #include <vector>
 
 #include "../../include/mlb.h"
@@ -102,6 +103,11 @@ struct mlb_model {
     std::vector<mlb::DevLayer> layers;      // execution order
     uint64_t weight_bytes = 0;
     std::vector<void*> allocs;
+    // FP8 models: the same weights as bf16 (code * row scale, rounded), made on first use for the
+    // tensor-core steps that consume a prompt as columns; shares gains, RoPE table and PLE tensors
+    mlb_model* bf16_view = nullptr;
+    bool bf16_view_failed = false;
+    std::mutex view_mu;
 };
 
 namespace mlb {
@@ -203,8 +209,55 @@ static int validate_for_kernels(const mlb_config& c) {
 static void free_model(mlb_model* m) {
     if (!m) return;
     cudaSetDevice(m->device);
+    if (m->bf16_view) free_model(m->bf16_view);
     for (void* p : m->allocs) cudaFree(p);
     delete m;
+}
+
+// The model whose projections the tensor-core steps can read: the model itself (bf16), or its bf16
+// view (FP8, built here on first use: 2 bytes per weight of extra device memory); null for fp32.
+static mlb_model* model_for_tc(mlb_model* m) {
+    if (m->cfg.weight_dtype == MLB_DT_BF16) return m;
+    if (m->cfg.weight_dtype != MLB_DT_FP8_E4M3) return nullptr;
+    std::lock_guard<std::mutex> lock(m->view_mu);
+    if (m->bf16_view || m->bf16_view_failed) return m->bf16_view;
+    cudaSetDevice(m->device);
+    mlb_model* v = new mlb_model();
+    v->cfg = m->cfg;
+    v->cfg.weight_dtype = MLB_DT_BF16;
+    v->device = m->device;
+    v->g_final = m->g_final;
+    v->rope = m->rope;
+    v->layers = m->layers;
+    bool ok = true;
+    auto widen = [&](const void* src, const float* scale, int rows, int cols) -> void* {
+        if (!ok || !src) return nullptr;
+        void* dst = nullptr;
+        if (cudaMalloc(&dst, (size_t)rows * cols * 2) != cudaSuccess) { cudaGetLastError(); ok = false; return nullptr; }
+        v->allocs.push_back(dst);
+        v->weight_bytes += (uint64_t)rows * cols * 2;
+        dequant_fp8_rows_kernel<<<(rows + 7) / 8, 256>>>(static_cast<const fp8_t*>(src), scale, static_cast<bf16_t*>(dst), rows, cols);
+        return dst;
+    };
+    const mlb_config& c = m->cfg;
+    v->E = widen(m->E, m->Es, c.vocab, c.dim);
+    v->Es = nullptr;
+    for (size_t i = 0; i < v->layers.size(); ++i) {
+        DevLayer& L = v->layers[i];
+        L.Wqkv = widen(L.Wqkv, L.Sqkv, L.n_qkv, c.dim); L.Sqkv = nullptr;
+        L.Wo = widen(L.Wo, L.So, c.dim, L.o_in); L.So = nullptr;
+        L.W1a = widen(L.W1a, L.S1a, c.ffn_dim, c.dim); L.S1a = nullptr;
+        L.W1b = widen(L.W1b, L.S1b, c.ffn_dim, c.dim); L.S1b = nullptr;
+        L.W2 = widen(L.W2, L.S2, c.dim, c.ffn_dim); L.S2 = nullptr;
+    }
+    if (ok && cudaDeviceSynchronize() != cudaSuccess) { cudaGetLastError(); ok = false; }
+    if (!ok) {
+        free_model(v);
+        m->bf16_view_failed = true;       // not enough device memory: the token loop keeps serving prompts
+        return nullptr;
+    }
+    m->bf16_view = v;
+    return v;
 }
 
 }  // namespace mlb
@@ -1683,13 +1736,15 @@ static int prefill_columns(mlb_session* s, const int32_t* tokens, const int32_t*
     long total = 0;
     for (int b = 0; b < B; ++b) total += lens[b] - keep;
     if (total < 1 || (mode == "auto" && total < 64)) return MLB_OK;
-    if (s->m->cfg.weight_dtype != MLB_DT_BF16) {
-        if (mode == "chunk") return fail(MLB_E_UNSUPPORTED, "MLB_PREFILL=chunk needs bf16 weights");
+    if (s->m->cfg.weight_dtype != MLB_DT_BF16 && s->m->cfg.weight_dtype != MLB_DT_FP8_E4M3) {
+        if (mode == "chunk") return fail(MLB_E_UNSUPPORTED, "MLB_PREFILL=chunk needs bf16 or FP8 weights");
         return MLB_OK;
     }
     if (!s->cols && !s->cols_tried) {
         s->cols_tried = true;
-        int rc = session_create(s->m, kPromptCols, s->max_ctx, 0, 0, s, &s->cols);
+        mlb_model* tm = model_for_tc(s->m);            // FP8: the bf16 view of the weights
+        int rc = tm ? session_create(tm, kPromptCols, s->max_ctx, 0, 0, s, &s->cols)
+                    : fail(MLB_E_NOMEM, "no device memory for the bf16 view of the FP8 weights");
         if (rc) {
             s->cols = nullptr;
             if (mode == "chunk") return rc;
@@ -1812,7 +1867,8 @@ extern "C" int mlb_score_tokens(mlb_session* s, const int32_t* tokens, int len, 
     const int V = s->m->cfg.vocab;
     for (int i = 0; i < len; ++i)
         if (tokens[i] < 0 || tokens[i] >= V) return fail(MLB_E_INVALID, "token %d at position %d is outside the vocabulary (%d)", tokens[i], i, V);
-    if (s->m->cfg.weight_dtype != MLB_DT_BF16) return fail(MLB_E_UNSUPPORTED, "the scoring forward needs bf16 weights (tensor-core columns)");
+    if (s->m->cfg.weight_dtype != MLB_DT_BF16 && s->m->cfg.weight_dtype != MLB_DT_FP8_E4M3)
+        return fail(MLB_E_UNSUPPORTED, "the scoring forward needs bf16 or FP8 weights (tensor-core columns)");
     int rc = mlb_session_reset(s);
     if (rc) return rc;
     bool has_attn = false;

@@ -180,10 +180,12 @@ def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name,
 
 
 @pytest.mark.parametrize("name,lens,decode_path", [("bf16", [131], "chain"), ("bf16", [1, 2, 130, 60, 201, 17], "auto"),
-                                                   ("bf16_w_f32_kv", [300, 5, 129], "chain"), ("bf16", [257], "grid")])
+                                                   ("bf16_w_f32_kv", [300, 5, 129], "chain"), ("bf16", [257], "grid"),
+                                                   ("fp8", [280, 3, 70], "auto")])
 def test_prompt_by_columns_matches_oracle(api, tmp_path, monkeypatch, name, lens, decode_path):
     """The prompt consumed as columns of tensor-core steps (256 per chunk; prompts that end inside a
-    chunk, span several, or have a single token), attention and delta-net layers mixed, PLE: the
+    chunk, span several, or have a single token), attention and delta-net layers mixed, PLE; FP8
+    weights run the columns on their bf16 view: the
     decode steps that follow, teacher-forced on the oracle's tokens, give its logits within 2e-2,
     and the positions are those the token loop leaves."""
     monkeypatch.setenv("MLB_PREFILL", "chunk")
@@ -222,7 +224,7 @@ def test_prompt_by_columns_matches_oracle(api, tmp_path, monkeypatch, name, lens
     model.close()
 
 
-@pytest.mark.parametrize("name,length", [("bf16", 40), ("bf16", 300), ("bf16_w_f32_kv", 257)])
+@pytest.mark.parametrize("name,length", [("bf16", 40), ("bf16", 300), ("bf16_w_f32_kv", 257), ("fp8", 270)])
 def test_scoring_forward_matches_oracle(api, tmp_path, name, length):
     """mlb_score_tokens: logits of every position of one sequence (the reference's full forward
     runInference(L)) against the KV-cached oracle fed the same tokens: within 2e-2 at every
