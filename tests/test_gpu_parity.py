@@ -144,9 +144,10 @@ def test_ragged_batch_matches_oracle(api, tmp_path, monkeypatch, name, batch, pa
 
 
 @pytest.mark.parametrize("name,batch,gemm", [("bf16", 16, "tc"), ("bf16", 40, "tc"), ("bf16_w_f32_kv", 24, "tc"), ("bf16", 5, "auto"),
-                                             ("bf16_w_f32_kv", 9, "auto")])
+                                             ("bf16_w_f32_kv", 9, "auto"), ("fp8", 12, "auto")])
 def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name, batch, gemm):
-    """Batch >= 4 with bf16 weights runs the projections as tcgen05 GEMMs on bf16 activations.
+    """Batch >= 4 with bf16 weights (or FP8 weights, through their bf16 view) runs the projections as
+    tcgen05 GEMMs on bf16 activations.
     Teacher-forced on the oracle's tokens: logits within 2e-2 at every step; the device pick equals
     the oracle's wherever the oracle's top-2 margin exceeds that bound."""
     monkeypatch.setenv("MLB_GEMM", gemm)
