@@ -97,7 +97,10 @@ int mlb_file_inspect(const char* path, const mlb_config* override_or_null, mlb_c
 /* Replaces the activation half of allocateMemory (memory_allocation.cu:500-552): instead of
  * maxL-sized scratch per op it owns a paged KV cache (pages of kv_block positions),
  * fp32 delta-net state and one decode step's scratch. kv_pages = 0 sizes the pool for
- * batch * max_context. */
+ * batch * max_context. A session of 4 sequences or more on an FP8 model runs its steps as
+ * tensor-core GEMMs on a bf16 copy of the weights that the model builds on the device the first
+ * time (2 bytes per weight, shared by all its sessions); MLB_GEMM=simt in the environment keeps
+ * the FP8 GEMV kernels. */
 int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_block, int kv_pages,
                     mlb_session** out);
 int mlb_session_reset(mlb_session* s);

@@ -1616,7 +1616,7 @@ static int session_create(mlb_model* m, int batch, int max_context, int kv_block
     // four pages of work per split at full context
     int sm_count = 148;
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, m->device);
-    int want = (2 * sm_count + c.kv_heads * batch - 1) / (c.kv_heads * batch);
+    int want = (4 * sm_count + c.kv_heads * batch - 1) / (c.kv_heads * batch);
     s->splits = std::max(1, std::min(std::min(want, 32), std::max(1, s->max_pages / 4)));
     SA(sess_alloc(s, (void**)&s->part, B * c.heads * s->splits * (c.head_dim + 2) * 4, true));
     SA(sess_alloc(s, (void**)&s->attn_ticket, B * c.kv_heads * 4, true));
