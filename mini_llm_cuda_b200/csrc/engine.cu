@@ -734,7 +734,7 @@ struct Chain {
     // of a sequence are spread over several CTAs of 64 threads (one projection row per thread).
     static int embed_split(int B, int d, int ple) {
         if (ple <= 0) return 1;
-        return std::max(1, std::min((d + 63) / 64, 128 / std::max(1, B)));
+        return std::max(1, std::min((d + 63) / 64, 1024 / std::max(1, B)));
     }
     static dim3 embed_grid(int B, int d, int ple) { return dim3(B, embed_split(B, d, ple)); }
     static dim3 embed_block(int B, int d, int ple) { return dim3(embed_split(B, d, ple) > 1 ? 64 : 256); }
@@ -842,6 +842,16 @@ struct Chain {
         int launches = 0, rc;
         auto prep = [&](const float* gain, const void* pleT, const void* pleP, int p_dim) -> int {
             int r2;
+            if (p_dim > 0 && (size_t)d * p_dim >= 131072) {
+                // large per-layer embedding: its own launch over many CTAs, then the plain norm
+                if (rec && (r2 = rec->begin("ple_add", (uint64_t)B * d * 8 + (uint64_t)p_dim * d * 2, 0))) return r2;
+                cudaError_t e0 = launch_chain(s->use_pdl, ple_add_kernel<T2>, dim3(B, (d + 63) / 64), dim3(64), (size_t)p_dim * 4, s->stream, c,
+                                              s->x, d, static_cast<const T2*>(pleT), static_cast<const T2*>(pleP), p_dim);
+                if (e0 != cudaSuccess) return fail(MLB_E_CUDA, "per-layer embedding launch failed: %s", cudaGetErrorString(e0));
+                if (rec && (r2 = rec->end())) return r2;
+                ++launches;
+                pleT = nullptr; pleP = nullptr; p_dim = 0;
+            }
             if (rec && (r2 = rec->begin("prep_norm_bf16", (uint64_t)B * d * 6 + (uint64_t)p_dim * d * 2, 0))) return r2;
             cudaError_t e = launch_chain(s->use_pdl, prep_bf16_kernel<T2>, dim3(B), dim3(256), (size_t)(d + p_dim) * 4, s->stream, c, s->x,
                                          d, gain, cfg.rms_eps, static_cast<const T2*>(pleT), static_cast<const T2*>(pleP), p_dim, s->xn16);

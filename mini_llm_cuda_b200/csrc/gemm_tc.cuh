@@ -252,6 +252,36 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
 // ---- small kernels around the GEMMs ---------------------------------------------------------------
 // RMS norm (+ the layer's per-layer embedding added to the residual stream first) and conversion to
 // the bf16 activation operand. One CTA per sequence. (inference.cu:24-50, :83-95)
+// x[b] += P . T[tok_b]: the per-layer embedding of a large model as a launch of its own, one
+// projection row per thread and the rows of a sequence spread over grid.y CTAs. Inside
+// prep_bf16_kernel one CTA per sequence walks all d rows (25 us at d = 2048, ple = 128).
+// grid = (B, ceil(d / 64)), block = 64, dynamic shared memory = ple floats.
+template <typename T2>
+__global__ void __launch_bounds__(64) ple_add_kernel(StepCtl c, float* __restrict__ x, int K, const T2* __restrict__ pleT,
+                                                     const T2* __restrict__ pleP, int ple) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    if (!seq_active(c, b)) return;
+    extern __shared__ __align__(16) float trow[];
+    const int t = c.tok[b];
+    for (int j = threadIdx.x; j < ple; j += blockDim.x) trow[j] = Elem<T2>::get(pleT, (size_t)t * ple + j);
+    __syncthreads();
+    constexpr int EPV2 = Elem<T2>::EPV;
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= K) return;
+    float a = 0.f;
+    const T2* prow = pleP + (size_t)i * ple;
+#pragma unroll 4
+    for (int j = 0; j < ple; j += EPV2) {
+        float w[EPV2];
+        Elem<T2>::load_vec(prow + j, w);
+#pragma unroll
+        for (int e = 0; e < EPV2; ++e) a = fmaf(w[e], trow[j + e], a);
+    }
+    x[(size_t)b * K + i] += a;
+}
+
 template <typename T2>
 __global__ void __launch_bounds__(256) prep_bf16_kernel(StepCtl c, float* __restrict__ x, int K, const float* __restrict__ gain,
                                                         float eps, const T2* __restrict__ pleT, const T2* __restrict__ pleP, int ple,

@@ -49,6 +49,8 @@ SPECS = {
     "bf16": small(ple_dim=32, layers=4, layer_types=periodic_layer_types(4, 2), weight_dtype="bfloat16",
                   kv_dtype="bfloat16"),
     "bf16_w_f32_kv": small(weight_dtype="bfloat16", kv_dtype="float32", query_gating=True),
+    "bf16_wide_ple": small(dim=1024, heads=16, head_dim=64, ffn_dim=512, layers=2, ple_dim=128,
+                           layer_types=periodic_layer_types(2, 2), weight_dtype="bfloat16", kv_dtype="bfloat16"),
     "fp8": small(dim=256, heads=4, kv_heads=2, ple_dim=32, layers=4, layer_types=periodic_layer_types(4, 4),
                  weight_dtype="float8_e4m3", kv_dtype="bfloat16"),
 }
@@ -144,7 +146,7 @@ def test_ragged_batch_matches_oracle(api, tmp_path, monkeypatch, name, batch, pa
 
 
 @pytest.mark.parametrize("name,batch,gemm", [("bf16", 16, "tc"), ("bf16", 40, "tc"), ("bf16_w_f32_kv", 24, "tc"), ("bf16", 5, "auto"),
-                                             ("bf16_w_f32_kv", 9, "auto"), ("fp8", 12, "auto")])
+                                             ("bf16_w_f32_kv", 9, "auto"), ("fp8", 12, "auto"), ("bf16_wide_ple", 6, "auto")])
 def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name, batch, gemm):
     """Batch >= 4 with bf16 weights (or FP8 weights, through their bf16 view) runs the projections as
     tcgen05 GEMMs on bf16 activations.
