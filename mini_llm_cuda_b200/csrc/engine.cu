@@ -798,14 +798,22 @@ struct Chain {
     // Batch tile (UMMA N) of one GEMM: the largest of 256..16 that still yields enough CTAs to
     // spread the weight stream and the MMAs over the SMs (the projections of a decode step have few
     // 128-row tiles; the activations are re-read per batch tile from L2, which is cheap).
-    static int tc_pick_nb(const mlb_session* s, int N) {
+    // One CTA per SM fits (the ring takes ~200 KB), so a grid runs in ceil(CTAs / SMs) waves and a CTA's
+    // time follows the bytes it streams: `na` weight tiles of 128 rows plus the batch tile, per k-block.
+    // Pick the tile with the least waves x bytes: 176 CTAs of 16 columns are two waves, 88 CTAs of 32
+    // columns one.
+    static int tc_pick_nb(const mlb_session* s, int N, int na) {
         const int tiles_m = (N + kTcM - 1) / kTcM;
         const int cap = std::min(256, (s->B + 15) / 16 * 16);
-        for (int nb = 256; nb > 16; nb >>= 1) {
-            if (nb > cap) continue;
-            if (tiles_m * ((s->B + nb - 1) / nb) >= 120) return nb;
+        int best = 16;
+        long best_cost = -1;
+        for (int nb = 16; nb <= cap; nb <<= 1) {
+            const long ctas = (long)tiles_m * ((s->B + nb - 1) / nb);
+            const long waves = (ctas + s->sm_count - 1) / s->sm_count;
+            const long cost = waves * (na * kTcM + nb);
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = nb; }
         }
-        return std::min(cap, 16);
+        return best;
     }
     static int nb_index(int nb) { return nb == 16 ? 0 : nb == 32 ? 1 : nb == 64 ? 2 : nb == 128 ? 3 : 4; }
 
@@ -813,7 +821,7 @@ struct Chain {
     static int gemm_tc(mlb_session* s, const CUtensorMap& A, const CUtensorMap& A2, const CUtensorMap* Bmaps, int N, int K, float* y,
                        const float* resid, bf16_t* h16, Recorder* rec, const char* name) {
         GemmTcParams p;
-        const int nb = tc_pick_nb(s, N);
+        const int nb = tc_pick_nb(s, N, MODE == TC_SWIGLU ? 2 : 1);
         p.N = N; p.K = K; p.B = s->B; p.Nb = nb;
         const size_t stage_bytes = (size_t)(MODE == TC_SWIGLU ? 2 : 1) * kTcM * 128 + (size_t)nb * 128;
         p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, (200 * 1024) / stage_bytes));
