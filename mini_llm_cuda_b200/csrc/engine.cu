@@ -678,8 +678,13 @@ struct Chain {
     }
 
     template <int HD>
-    static int attn_g(mlb_session* s, const StepCtl& c, const AttnParams& p, int G) {
-        dim3 grid(s->splits, p.kv_heads, s->B);
+    static int attn_g(mlb_session* s, const StepCtl& c, const AttnParams& p0, int G) {
+        AttnParams p = p0;
+        p.hg = 1;
+        // few CTAs (small batch): two query heads per CTA, G/2 CTAs per kv head (cfg4 at batch 1: 1.28 -> 1.14 ms
+        // per step); with the GPU already full the extra CTAs only re-read K/V (62 -> 69 us at 64 sequences)
+        if (G >= 4 && G % 2 == 0 && s->splits * p.kv_heads * s->B < 2 * s->sm_count) { p.hg = G / 2; G = 2; }
+        dim3 grid(s->splits, p.kv_heads * p.hg, s->B);
         cudaError_t e;
         switch (G) {
             case 1: e = launch_chain(s->use_pdl, attn_decode_kernel<KVT, HD, 1>, grid, dim3(128), 0, s->stream, c, p); break;
@@ -1637,7 +1642,7 @@ static int session_create(mlb_model* m, int batch, int max_context, int kv_block
     int want = (4 * sm_count + c.kv_heads * batch - 1) / (c.kv_heads * batch);
     s->splits = std::max(1, std::min(std::min(want, 32), std::max(1, s->max_pages / 4)));
     SA(sess_alloc(s, (void**)&s->part, B * c.heads * s->splits * (c.head_dim + 2) * 4, true));
-    SA(sess_alloc(s, (void**)&s->attn_ticket, B * c.kv_heads * 4, true));
+    SA(sess_alloc(s, (void**)&s->attn_ticket, B * c.heads * 4, true));
     s->lm_rows = 16;
     // argmax partials per sequence: one per LM-head CTA of either GEMV form (the streamed form
     // launches up to one CTA per SM, whatever the vocabulary size)

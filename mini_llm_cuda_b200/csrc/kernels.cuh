@@ -643,8 +643,9 @@ struct AttnParams {
     float* abuf;            // [B][heads*hd]
     bf16_t* abuf16;         // same values as the bf16 operand of a tensor-core O projection, or null
     float* part;            // [B][heads][splits][hd+2]
-    int* ticket;            // [B*kv_heads]
+    int* ticket;            // [B * gridDim.y]
     int heads, kv_heads;
+    int hg;                 // CTAs per kv head along grid.y: each takes G of the kv head's query heads
 };
 
 template <typename KVT, int HD, int G>
@@ -654,7 +655,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     constexpr int PPI = 32 / LPR;                  // positions per warp iteration
     constexpr int NW = 4;
     static_assert(LPR <= 32 && PPI >= 1, "head_dim too large for one warp row");
-    const int b = blockIdx.z, kvh = blockIdx.y, split = blockIdx.x;
+    // With many query heads per kv head one CTA would hold all their accumulators (160+ registers,
+    // no room for a second chunk of loads in flight): hg CTAs share a kv head instead, G heads each;
+    // the K/V rows they re-read come from L2.
+    const int b = blockIdx.z, kvh = blockIdx.y / p.hg, split = blockIdx.x;
+    const int tslot = b * (int)gridDim.y + (int)blockIdx.y;
     pdl_launch_dependents();
     pdl_wait();                                    // q and this step's K/V row come from the projection kernel
     if (!seq_active(c, b)) return;                 // uniform for all CTAs of this sequence
@@ -674,7 +679,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
 
     __shared__ float sq[G][HD];
     __shared__ float sred[NW][G][HD + 2];
-    const int h0 = kvh * G;
+    const int h0 = kvh * G * p.hg + ((int)blockIdx.y % p.hg) * G;
     for (int i = tid; i < G * HD; i += blockDim.x)
         sq[i / HD][i % HD] = p.qbuf[((size_t)b * p.heads + h0) * HD + i];
     __syncthreads();
@@ -850,7 +855,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        int t = atomicAdd(&p.ticket[b * p.kv_heads + kvh], 1);
+        int t = atomicAdd(&p.ticket[tslot], 1);
         is_last = (t == S - 1);
     }
     __syncthreads();
@@ -883,7 +888,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
         p.abuf[((size_t)b * p.heads + h) * HD + e] = o;
         if (p.abuf16) p.abuf16[((size_t)b * p.heads + h) * HD + e] = __float2bfloat16_rn(o);
     }
-    if (tid == 0) p.ticket[b * p.kv_heads + kvh] = 0;
+    if (tid == 0) p.ticket[tslot] = 0;
 }
 
 // ------------------------------------------------------------------------------------
