@@ -1229,7 +1229,7 @@ static int setup_grid_path(mlb_session* s) {
     if (s->B != 1) return no("the whole-GPU step serves batch 1 only");
     // auto: only where it was measured faster than the kernel chain. Its ~4.5 us per phase beat the
     // chain's launches once the weights of a step take a few hundred microseconds to stream
-    // (1.05 vs 1.37 ms per token on a 1.2 GB FP8 model); on a 60 MB model the chain is ahead
+    // (1.05 vs 1.13 ms per token on a 1.2 GB FP8 model); on a 60 MB model the chain is ahead
     // (172 vs 200 us per token).
     if (mode == "auto" && mlb_model_weight_bytes(s->m) < (256ull << 20)) return MLB_OK;
     int coop = 0;
