@@ -299,10 +299,10 @@ class Session:
         return check(lib().mlb_session_launches_per_step(self._h))
 
     def grid_timers(self) -> np.ndarray:
-        """[CTAs][16] cycle counters of the single-kernel step (MLB_GRID_TIMERS=1), else empty."""
-        buf = np.zeros(1024 * 16, dtype=np.int64)
+        """[CTAs][20] cycle counters of the single-kernel step (MLB_GRID_TIMERS=1), else empty."""
+        buf = np.zeros(1024 * 32, dtype=np.int64)
         n = check(lib().mlb_session_grid_timers(self._h, _ptr(buf, C.c_longlong), buf.size))
-        return buf[:n * 16].reshape(n, 16).copy()
+        return buf[:n * 32].reshape(n, 32).copy()
 
     def close(self):
         if self._h:

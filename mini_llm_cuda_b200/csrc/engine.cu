@@ -17,7 +17,7 @@
 #include "kernels.cuh"
 #include "gemm_tc.cuh"
 #include "tc_host.h"
-#include "mega.cuh"
+#include "ring.cuh"
 #include "grid_params.h"
 #include "grid_host.h"
 #include "model_file.h"
@@ -452,12 +452,7 @@ struct mlb_session {
     bool force_sgemv = false;               // MLB_GEMV=stream: also for small matrices (tests)
     int sg_stage_kb = 48, sg_max_stages = 8; // ring geometry of the streamed GEMV (MLB_SG_STAGE_KB, MLB_SG_STAGES)
     int sm_count = 148;
-    // cluster-per-sequence single-kernel step (small batch)
-    bool use_cluster = false;
-    int cluster_size = 0;
-    size_t mega_smem = 0;
-    mlb::MegaLayer* mega_layers = nullptr;
-    mlb::MegaParams mega;
+    mlb::StepLayer* step_layers = nullptr;   // device table of per-layer pointers (single-kernel step)
     int* dev_err = nullptr;                 // set by a kernel whose bounded wait ran out
     // whole-GPU single-kernel step (batch 1)
     bool use_grid = false;
@@ -696,45 +691,6 @@ struct Chain {
         return MLB_OK;
     }
 
-    // One decode (or prefill) step as a single cluster kernel (plus the sampler for top-k).
-    static int run_cluster(mlb_session* s, int kind, const StepCtl& c, Recorder* rec, int* n_launches) {
-        MegaParams mp = s->mega;
-        mp.with_lm_head = kind == CHAIN_PREFILL ? 0 : 1;
-        mp.do_pick = kind == CHAIN_GREEDY ? 1 : 0;
-        int rc, launches = 0;
-        if (rec) {
-            uint64_t w, kv, st, rows;
-            mlb_session_step_bytes(s, &w, &kv, &st, &rows);
-            if ((rc = rec->begin("cluster_decode_step", (uint64_t)s->B * w + kv + st + rows, 0))) return rc;
-        }
-        cudaLaunchConfig_t cfg;
-        std::memset(&cfg, 0, sizeof cfg);
-        cfg.gridDim = dim3(s->cluster_size, s->B);
-        cfg.blockDim = dim3(kMegaThreads);
-        cfg.dynamicSmemBytes = s->mega_smem;
-        cfg.stream = s->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = s->cluster_size;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        CU(cudaLaunchKernelEx(&cfg, mega_decode_kernel<T, T2, KVT>, c, mp));
-        if (rec && (rc = rec->end())) return rc;
-        ++launches;
-        if (kind == CHAIN_TOPK) {
-            SampleParams sp;
-            sp.logits = s->logits; sp.V = s->m->cfg.vocab; sp.top_k = s->cur_topk; sp.temperature = s->cur_temp; sp.seeds = s->seeds;
-            if (rec && (rc = rec->begin("sample_topk_philox", (uint64_t)s->B * s->m->cfg.vocab * 4 * 5, 0))) return rc;
-            CU(launch_chain(false, sample_topk_kernel, dim3(s->B), dim3(256), 0, s->stream, c, sp));
-            if (rec && (rc = rec->end())) return rc;
-            ++launches;
-        }
-        if (n_launches) *n_launches = launches;
-        return MLB_OK;
-    }
-
     // Launch shape of the embedding kernel: with per-layer embeddings and a small batch, the rows
     // of a sequence are spread over several CTAs of 64 threads (one projection row per thread).
     static int embed_split(int B, int d, int ple) {
@@ -768,35 +724,6 @@ struct Chain {
             ++launches;
         }
         if (n_launches) *n_launches = launches;
-        return MLB_OK;
-    }
-
-    // Shared-memory need and occupancy of the cluster kernel; 0 clusters = not usable here.
-    static int cluster_probe(int cluster_size, size_t smem, int batch, int* max_clusters) {
-        *max_clusters = 0;
-        if (cudaFuncSetAttribute(mega_decode_kernel<T, T2, KVT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-            cudaFuncSetAttribute(mega_decode_kernel<T, T2, KVT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
-            cudaGetLastError();
-            return MLB_OK;
-        }
-        cudaLaunchConfig_t cfg;
-        std::memset(&cfg, 0, sizeof cfg);
-        cfg.gridDim = dim3(cluster_size, batch);
-        cfg.blockDim = dim3(kMegaThreads);
-        cfg.dynamicSmemBytes = smem;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = cluster_size;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, mega_decode_kernel<T, T2, KVT>, &cfg) != cudaSuccess) {
-            cudaGetLastError();
-            n = 0;
-        }
-        *max_clusters = n;
         return MLB_OK;
     }
 
@@ -985,7 +912,6 @@ struct Chain {
         const int d = cfg.dim, F = cfg.ffn_dim, B = s->B, p = cfg.ple_dim;
         int launches = 0, rc;
         if (s->use_grid) return run_grid(s, kind, c, rec, n_launches);
-        if (s->use_cluster) return run_cluster(s, kind, c, rec, n_launches);
         if (s->use_tc) return run_tc(s, kind, c, rec, n_launches);
 
         if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * (d * sizeof(T) + (uint64_t)p * sizeof(T2) + (uint64_t)d * 4) + (uint64_t)d * p * sizeof(T2), 0))) return rc;
@@ -1111,111 +1037,50 @@ static int chain_configure(mlb_session* s) {
 }
 
 // Device copy of the per-layer pointer table of the single-kernel steps.
-static int build_mega_layers(mlb_session* s) {
-    if (s->mega_layers) return MLB_OK;
+static int build_step_layers(mlb_session* s) {
+    if (s->step_layers) return MLB_OK;
     const mlb_config& c = s->m->cfg;
-    std::vector<MegaLayer> hl(c.layers);
+    std::vector<StepLayer> hl(c.layers);
     for (int i = 0; i < c.layers; ++i) {
         const DevLayer& L = s->m->layers[i];
-        MegaLayer& M = hl[i];
+        StepLayer& M = hl[i];
         std::memset(&M, 0, sizeof M);
         M.type = L.type; M.n_qkv = L.n_qkv; M.nq = L.nq; M.nk = L.nk; M.nv = L.nv; M.ng = L.ng; M.o_in = L.o_in;
         M.Wqkv = L.Wqkv; M.Sqkv = L.Sqkv; M.g1 = L.g1; M.g2 = L.g2; M.gq = L.gq; M.gk = L.gk;
         M.Wo = L.Wo; M.So = L.So; M.W1a = L.W1a; M.W1b = L.W1b; M.W2 = L.W2; M.S1a = L.S1a; M.S1b = L.S1b; M.S2 = L.S2;
         M.pleT = L.pleT; M.pleP = L.pleP; M.kpool = s->kpool[i]; M.vpool = s->vpool[i]; M.state = s->state[i];
     }
-    int rc = sess_alloc(s, (void**)&s->mega_layers, hl.size() * sizeof(MegaLayer), false);
+    int rc = sess_alloc(s, (void**)&s->step_layers, hl.size() * sizeof(StepLayer), false);
     if (rc) return rc;
-    CU(cudaMemcpy(s->mega_layers, hl.data(), hl.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice));
+    CU(cudaMemcpy(s->step_layers, hl.data(), hl.size() * sizeof(StepLayer), cudaMemcpyHostToDevice));
     return MLB_OK;
 }
 
-static int chain_cluster_probe(mlb_session* s, int cluster_size, size_t smem, int* max_clusters) {
-    const int w = s->m->cfg.weight_dtype, k = s->m->cfg.kv_dtype;
-    if (w == MLB_DT_F32 && k == MLB_DT_F32) return Chain<float, float, float>::cluster_probe(cluster_size, smem, s->B, max_clusters);
-    if (w == MLB_DT_F32 && k == MLB_DT_BF16) return Chain<float, float, bf16_t>::cluster_probe(cluster_size, smem, s->B, max_clusters);
-    if (w == MLB_DT_BF16 && k == MLB_DT_F32) return Chain<bf16_t, bf16_t, float>::cluster_probe(cluster_size, smem, s->B, max_clusters);
-    if (w == MLB_DT_BF16 && k == MLB_DT_BF16) return Chain<bf16_t, bf16_t, bf16_t>::cluster_probe(cluster_size, smem, s->B, max_clusters);
-    if (w == MLB_DT_FP8_E4M3 && k == MLB_DT_F32) return Chain<fp8_t, bf16_t, float>::cluster_probe(cluster_size, smem, s->B, max_clusters);
-    return Chain<fp8_t, bf16_t, bf16_t>::cluster_probe(cluster_size, smem, s->B, max_clusters);
-}
-
-// Decides whether the single-kernel cluster step serves this session and lays out its shared
-// memory. MLB_DECODE_PATH = chain | cluster | auto. The cluster step is opt-in: one cluster
-// lives in one GPC and is held to that GPC's share of the L2 bandwidth, which on B200 makes it
-// slower than the kernel chain (293 vs 180 us per token on the 1-GPU latency configuration).
-static int setup_cluster_path(mlb_session* s) {
-    const mlb_config& c = s->m->cfg;
-    const char* env = std::getenv("MLB_DECODE_PATH");
-    const std::string mode = env ? env : "auto";
-    s->use_cluster = false;
-    if (mode != "cluster") return MLB_OK;
-    auto up4 = [](int v) { return (v + 3) / 4 * 4; };
-    for (int C : {16, 8}) {
-        MegaParams mp;
-        std::memset(&mp, 0, sizeof mp);
-        const int S = std::max(1, C / c.kv_heads);
-        int n_proj = s->raw_stride;
-        for (const DevLayer& L : s->m->layers) n_proj = std::max(n_proj, L.n_qkv);
-        const int a_dim = std::max(c.heads * c.head_dim, c.heads * c.dn_value_dim);
-        const int tmp_n = std::max(std::max(c.head_dim, kMegaAttnWarps * (c.head_dim + 2)),
-                                   std::max(2 * c.heads * c.dn_key_dim + 2 * c.heads, 64));
-        int off = 0;
-        mp.off_x = off; off += up4(c.dim);
-        mp.off_xn = off; off += up4(c.dim);
-        mp.off_proj = off; off += up4(n_proj);
-        mp.off_parts = off; off += up4(c.heads * S * (c.head_dim + 2));
-        mp.off_a = off; off += up4(a_dim);
-        mp.off_h = off; off += up4(c.ffn_dim);
-        mp.off_tmp = off; off += up4(tmp_n);
-        mp.off_ple = off; off += up4(std::max(c.ple_dim, 4));
-        mp.off_pacc = off; off += up4(c.dim / 8 + 8);
-        mp.off_red = off; off += 32;
-        mp.off_lm = off; off += up4(2 * C);
-        off = (off + 31) / 32 * 32;
-        const int max_stages = 8;
-        mp.off_bar = off; off += max_stages * 2 * 2;              // 8-byte barriers: full[] then empty[]
-        off = (off + 31) / 32 * 32;
-        mp.off_ring = off;
-        // ring: 32 KB stages (whole rows), as many as fit below ~208 KB of shared memory
-        mp.stage_bytes = 32 * 1024;
-        const size_t fixed = (size_t)off * 4;
-        if (fixed + 3 * (size_t)mp.stage_bytes > 208 * 1024) continue;
-        mp.n_stages = (int)std::min<size_t>(max_stages, (208 * 1024 - fixed) / mp.stage_bytes);
-        {
-            // every row that is streamed must fit one stage
-            size_t widest = (size_t)std::max(std::max(c.dim, c.ffn_dim), std::max(c.heads * c.head_dim, c.heads * c.dn_value_dim)) *
-                            elt_size(c.weight_dtype);
-            if (widest > (size_t)mp.stage_bytes) continue;
-        }
-        const size_t smem = fixed + (size_t)mp.n_stages * mp.stage_bytes;
-        int max_clusters = 0;
-        int rc = chain_cluster_probe(s, C, smem, &max_clusters);
-        if (rc) return rc;
-        if (max_clusters < 1) continue;
-        int rc2 = build_mega_layers(s);
-        if (rc2) return rc2;
-        mp.layers = s->mega_layers; mp.n_layers = c.layers;
-        mp.d = c.dim; mp.F = c.ffn_dim; mp.V = c.vocab; mp.heads = c.heads; mp.kv_heads = c.kv_heads; mp.hd = c.head_dim;
-        mp.dk = c.dn_key_dim; mp.dv = c.dn_value_dim; mp.ple = c.ple_dim; mp.qk_norm = c.qk_norm;
-        mp.eps = c.rms_eps; mp.l2_eps = 1e-6f;
-        mp.E = s->m->E; mp.Es = s->m->Es; mp.g_final = s->m->g_final; mp.rope = s->m->rope;
-        mp.page_table = s->page_table; mp.pt_stride = s->max_pages; mp.logits = s->logits;
-        mp.attn_splits = S;
-        mp.err = s->dev_err;
-        s->mega = mp;
-        s->cluster_size = C;
-        s->mega_smem = smem;
-        s->use_cluster = true;
-        return MLB_OK;
+// Geometry of one exchanged vector of the whole-GPU step: N values from P producers, a slot of whole
+// 128-byte lines per producer (grid_params.h). `tab` is the shared-memory offset of its row table, -1
+// when every producer owns exactly N / P rows.
+static GridVec grid_vec(int N, int P, int tab) {
+    GridVec v;
+    std::memset(&v, 0, sizeof v);
+    v.N = N;
+    v.P = P;
+    v.rpc = (N + P - 1) / P;
+    v.slotw = (v.rpc + 15) / 16 * 16;
+    v.tab = tab;
+    v.inv_n = 1.0f / (float)N;
+    v.magic = 0;
+    if (v.rpc > 1) {
+        // q / rpc as one multiply-high, exact over the range the kernel uses (q < P * rpc < 2^16 * rpc)
+        v.magic = (unsigned)(((1ull << 32) + (unsigned)v.rpc - 1) / (unsigned)v.rpc);
+        for (unsigned q = 0; q < (unsigned)(P * v.rpc); ++q)
+            if ((unsigned)(((unsigned long long)q * v.magic) >> 32) != q / (unsigned)v.rpc) { v.N = -1; break; }     // never seen; the caller refuses
     }
-    if (mode == "cluster") return fail(MLB_E_UNSUPPORTED, "MLB_DECODE_PATH=cluster: no cluster configuration fits this model on this device");
-    return MLB_OK;
+    return v;
 }
 
 // Decides whether the whole-GPU single-kernel step serves this session (batch 1) and lays out
-// its shared memory and exchange buffers. MLB_DECODE_PATH = chain | cluster | grid | auto; auto
-// takes it whenever the model fits its constraints.
+// its shared memory and exchange buffers. MLB_DECODE_PATH = chain | grid | auto; auto takes it
+// whenever the model fits its constraints.
 static int setup_grid_path(mlb_session* s) {
     const mlb_config& c = s->m->cfg;
     const char* env = std::getenv("MLB_DECODE_PATH");
@@ -1227,65 +1092,81 @@ static int setup_grid_path(mlb_session* s) {
         return (int)MLB_OK;
     };
     if (s->B != 1) return no("the whole-GPU step serves batch 1 only");
-    // auto: only where it was measured faster than the kernel chain. Its ~4.5 us per phase beat the
-    // chain's launches once the weights of a step take a few hundred microseconds to stream
-    // (1.05 vs 1.13 ms per token on a 1.2 GB FP8 model); on a 60 MB model the chain is ahead
-    // (172 vs 200 us per token).
-    if (mode == "auto" && mlb_model_weight_bytes(s->m) < (256ull << 20)) return MLB_OK;
     int coop = 0;
     cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, s->m->device);
     if (!coop) return no("the device has no cooperative launch");
     const int epv = 16 / (int)elt_size(c.weight_dtype);
-    const int epv2 = c.weight_dtype == MLB_DT_F32 ? 4 : 8;
     bool has_attn = false, has_dn = false;
-    int n_proj = 0, min_rows = std::min(c.dim, c.ffn_dim), a_dim = 16;
+    int nqkv_attn = 0, nqkv_dn = 0, min_rows = std::min(c.dim, c.ffn_dim), a_dim = 16;
     for (const DevLayer& L : s->m->layers) {
-        n_proj = std::max(n_proj, L.n_qkv);
         min_rows = std::min(min_rows, L.n_qkv);
         a_dim = std::max(a_dim, L.o_in);
-        if (L.type == MLB_LAYER_ATTENTION) has_attn = true; else has_dn = true;
+        if (L.type == MLB_LAYER_ATTENTION) { has_attn = true; nqkv_attn = L.n_qkv; }
+        else { has_dn = true; nqkv_dn = L.n_qkv; }
         if (L.o_in % epv) return no("a projection width is not a multiple of the weight vector");
     }
-    if (c.dim % epv || c.ffn_dim % epv || (c.ple_dim > 0 && c.ple_dim % epv2)) return no("a projection width is not a multiple of the weight vector");
+    if (c.dim % epv || c.ffn_dim % epv) return no("a projection width is not a multiple of the weight vector");
     if (has_attn && c.head_dim != 64 && c.head_dim != 128) return no("head_dim must be 64 or 128");
     if (has_attn && (c.heads % c.kv_heads || c.heads / c.kv_heads > 8)) return no("more than 8 query heads per kv head");
     if (has_dn && c.dn_key_dim > 128) return no("delta-net key dim above 128");
-    const int C = std::min(s->sm_count, min_rows);
+    if (has_dn) min_rows = std::min(min_rows, c.heads * c.dn_value_dim);
+    min_rows = std::min(min_rows, c.vocab);
+    // Every CTA must own rows in every projection phase (the reuse rule of the exchange buffers)
+    int C = std::min(s->sm_count, min_rows);
+    if (const char* v = std::getenv("MLB_GRID_CTAS")) C = std::max(8, std::min(C, std::atoi(v)));
     if (C < 8) return no("the model is too small to split over the SMs");
+    if (has_attn && c.heads > C) return no("more heads than CTAs");
     const int G = has_attn ? c.heads / c.kv_heads : 1;
     auto up4 = [](int v) { return (v + 3) / 4 * 4; };
     GridParams gp;
     std::memset(&gp, 0, sizeof gp);
-    // context splits per kv head: enough items for every CTA; one head's partials fit 32 KB of shared memory
+    // context splits per kv head: at most one item per CTA; a head's partials fit 32 KB of shared memory
     gp.s_max = has_attn ? std::max(1, std::min(C / c.kv_heads, 8192 / (c.head_dim + 2))) : 1;
-    const int n_parts = has_attn ? c.heads * gp.s_max * (c.head_dim + 2) : 0;
-    const int tmp_n = std::max(std::max(G * c.head_dim + 2 * c.head_dim + kGridAttnWarps * (c.head_dim + 2), 2 * c.heads * c.dn_key_dim + 2 * c.heads),
-                               64);
+    gp.s_direct = has_attn ? std::max(1, std::min(gp.s_max, kGridDirectWords / (c.heads * (c.head_dim + 2)))) : 1;
+    gp.pages_per_split = 16;
+    if (const char* v = std::getenv("MLB_GRID_PAGES_PER_SPLIT")) gp.pages_per_split = std::max(1, std::min(256, std::atoi(v)));
+    const int rpc_d = (c.dim + C - 1) / C;
+    const int rpc_a = has_dn ? (c.heads * c.dn_value_dim + C - 1) / C : 0;
     int off = 0;
-    gp.off_x = off; off += up4(c.dim);
-    gp.off_x2 = off; off += up4(c.dim);
-    gp.off_xn = off; off += up4(c.dim);
-    gp.off_proj = off; off += up4(std::max(n_proj, a_dim));
+    // row tables (ints) of the vectors whose rows do not divide evenly
+    const int tab_d = off; off += up4(C + 1);
+    const int tab_f = off; off += up4(C + 1);
+    const int tab_qa = off; off += up4(C + 1);
+    const int tab_qd = off; off += up4(C + 1);
+    const int tab_a = off; off += up4(C + 1);
+    const int tab_ah = off; off += up4(C + 1);
+    const int tab_lm = off; off += up4(C + 1);
+    gp.vocab_tab = off; off += up4(C + 1);
+    gp.off_tabs = 0;
+    gp.xs_stride = up4(std::max(std::max(c.dim, c.ffn_dim), a_dim));
+    gp.off_xs = off; off += 2 * gp.xs_stride;
+    gp.off_xa = off; off += up4(c.dim);
+    gp.off_xb = off; off += up4(c.dim);
     gp.off_parts = off; off += up4(std::max(has_attn ? std::max(gp.s_max * (c.head_dim + 2), kGridDirectWords) : 0, 2 * C));
-    gp.off_a = off; off += up4(a_dim);
-    gp.off_h = off; off += up4(c.ffn_dim);
-    gp.off_tmp = off; off += up4(tmp_n);
-    gp.off_ple = off; off += up4(std::max(c.ple_dim, 4));
-    gp.off_pacc = off; off += up4(c.dim / C + 8);
-    gp.off_red = off; off += 32;
-    gp.off_layers = off; off += up4((int)(c.layers * sizeof(MegaLayer) / 4));
-    gp.off_timers = off; off += 2 * kGridTimers;
-    int n_phases = 1 + (c.ple_dim > 0 ? 1 : 0);      // LM head, embedding rows
-    for (int i = 0; i < c.layers; ++i) n_phases += 4 + (c.ple_dim > 0 && i + 1 < c.layers ? 1 : 0);
-    gp.off_phases = off; off += n_phases * (int)(sizeof(GridPhase) / 4);
+    gp.off_gate = off; off += up4(has_attn ? c.heads * c.head_dim : 4);
+    {
+        const int attn_n = has_attn ? G * c.head_dim + 2 * c.head_dim + kRingWarps * (c.head_dim + 2) : 0;
+        const int comb_n = has_attn ? std::max(c.heads * gp.s_direct, gp.s_max) : 0;
+        const int dn_n = has_dn ? 2 * c.heads * c.dn_key_dim + up4(rpc_a) + 2 * c.heads + 8 : 0;
+        gp.off_mix = off; off += up4(std::max(std::max(attn_n, comb_n), std::max(dn_n, 64)));
+    }
+    gp.off_pacc = off; off += up4(std::max(1, c.layers * rpc_d));
+    gp.off_red = off; off += 2 * kRingConsumers + 8;
+    off = (off + 1) / 2 * 2;
+    gp.off_layers = off; off += up4((int)(c.layers * sizeof(StepLayer) / 4));
+    gp.off_timers = off; off += 2 * kGridTimerSlots;
+    gp.off_plan = off; off += 12;
     off = (off + 31) / 32 * 32;
     const int max_stages = 12;
     gp.off_bar = off; off += max_stages * 2 * 2;              // 8-byte barriers: full[] then empty[]
     off = (off + 31) / 32 * 32;
     gp.off_ring = off;
-    // ring: stages of whole rows, 16 KB unless a row is longer, as many as fit below ~208 KB
-    const size_t widest = (size_t)std::max(std::max(c.dim, c.ffn_dim), a_dim) * elt_size(c.weight_dtype);
+    // ring: stages of whole rows (and whole KV pages), 16 KB unless a row is longer, as many as fit below ~208 KB
+    size_t widest = (size_t)std::max(std::max(c.dim, c.ffn_dim), a_dim) * elt_size(c.weight_dtype);
+    if (has_attn) widest = std::max(widest, (size_t)kKvBlock * c.head_dim * elt_size(c.kv_dtype));
+    if (has_dn) widest = std::max(widest, (size_t)c.dn_key_dim * 4);
     gp.stage_bytes = (int)std::max<size_t>(16 * 1024, (widest + 1023) / 1024 * 1024);
+    if (const char* v = std::getenv("MLB_GRID_STAGE_KB")) gp.stage_bytes = std::max(gp.stage_bytes, std::min(64, std::atoi(v)) * 1024);
     const size_t fixed = (size_t)off * 4;
     if (fixed + 3 * (size_t)gp.stage_bytes > 208 * 1024) return no("the activations leave too little shared memory for the weight ring");
     gp.n_stages = (int)std::min<size_t>(max_stages, (208 * 1024 - fixed) / gp.stage_bytes);
@@ -1293,124 +1174,38 @@ static int setup_grid_path(mlb_session* s) {
     int per_sm = 0, rc;
     if ((rc = grid_kernel_probe(c.weight_dtype, c.kv_dtype, smem, &per_sm))) return rc;
     if (per_sm < 1) return no("the kernel does not fit an SM");
-    if ((rc = build_mega_layers(s))) return rc;
-    // exchange buffers (zeroed: epoch 0 is never produced) and the epoch word
-    const size_t n_ll = (size_t)2 * c.dim + n_proj + n_parts + a_dim + c.ffn_dim + 2 * (size_t)C + 64;
+    if ((rc = build_step_layers(s))) return rc;
+    // exchanged vectors and their buffers (zeroed: epoch 0 is never produced)
+    gp.vx = grid_vec(c.dim, C, tab_d);
+    gp.vxb = grid_vec(c.dim, C, tab_d);
+    gp.vproj_attn = grid_vec(std::max(nqkv_attn, C), C, tab_qa);
+    gp.vproj_dn = grid_vec(std::max(nqkv_dn, C), C, tab_qd);
+    gp.vh = grid_vec(c.ffn_dim, C, tab_f);
+    gp.va_dn = grid_vec(has_dn ? c.heads * c.dn_value_dim : C, C, tab_a);
+    gp.va_head = grid_vec(has_attn ? c.heads * c.head_dim : 16, has_attn ? c.heads : 1, tab_ah);
+    gp.vlm = grid_vec(2 * C, C, tab_lm);
+    gp.parts_slotw = (G * (c.head_dim + 2) + 15) / 16 * 16;
+    GridVec* vecs[] = {&gp.vx, &gp.vxb, &gp.vproj_attn, &gp.vproj_dn, &gp.vh, &gp.va_dn, &gp.va_head, &gp.vlm};
+    size_t n_ll = (size_t)C * gp.parts_slotw + 64;
+    for (GridVec* v : vecs) {
+        if (v->N < 0) return no("a row split has no exact multiply-high divisor");
+        n_ll += (size_t)v->P * v->slotw;
+    }
     unsigned long long* ll = nullptr;
     if ((rc = sess_alloc(s, (void**)&ll, n_ll * 8, true))) return rc;
-    gp.ll_xa = ll; ll += c.dim;
-    gp.ll_xb = ll; ll += c.dim;
-    gp.ll_proj = ll; ll += n_proj;
-    gp.ll_parts = ll; ll += n_parts;
-    gp.ll_a = ll; ll += a_dim;
-    gp.ll_h = ll; ll += c.ffn_dim;
-    gp.ll_lm = ll; ll += 2 * (size_t)C;
+    for (GridVec* v : vecs) { v->buf = ll; ll += (size_t)v->P * v->slotw; }
+    gp.parts = ll;
     if ((rc = sess_alloc(s, (void**)&gp.epoch, 16, true))) return rc;
     if (const char* t = std::getenv("MLB_GRID_TIMERS"))
-        if (t[0] == '1' && (rc = sess_alloc(s, (void**)&gp.timers, (size_t)C * kGridTimers * 8, true))) return rc;
-    // the phase list of one step
-    {
-        std::vector<GridPhase> ph;
-        int e = 0;                          // epochs used so far (offsets from the step's base)
-        int e_x = 0;                        // epoch of the residual stream in ll_xa (0: local in shared memory)
-        const size_t esz = elt_size(c.weight_dtype), psz = c.weight_dtype == MLB_DT_F32 ? 4 : 2;
-        auto blank = [&]() {
-            GridPhase d;
-            std::memset(&d, 0, sizeof d);
-            d.resid_off = -1;
-            d.nsrc_off = gp.off_x;
-            d.xs_off = gp.off_xn;
-            return d;
-        };
-        if (c.ple_dim > 0) {
-            GridPhase d = blank();          // embedding row + the first layer's per-layer embedding
-            const DevLayer& L0 = s->m->layers[0];
-            d.W = L0.pleP; d.N = c.dim; d.K = c.ple_dim; d.row_bytes = (int)(c.ple_dim * psz);
-            d.ple_table = L0.pleT; d.flags = GP_T2 | GP_FILL_PLE;
-            d.mode = RJ_RESID; d.dst = gp.ll_xa; d.e_off = ++e; d.resid_off = gp.off_x2; d.xs_off = gp.off_ple;
-            e_x = e;
-            ph.push_back(d);
-        }
-        for (int i = 0; i < c.layers; ++i) {
-            const DevLayer& L = s->m->layers[i];
-            const bool ple_next = c.ple_dim > 0 && i + 1 < c.layers;
-            int e1, e_a, e3, e4;
-            {
-                GridPhase d = blank();      // QKV (or delta-net) projections of the normalised residual stream
-                d.W = L.Wqkv; d.scale = L.Sqkv; d.N = L.n_qkv; d.K = c.dim; d.row_bytes = (int)(c.dim * esz);
-                d.gain = L.g1; d.nsrc_off = gp.off_x; d.xs_off = gp.off_xn;
-                if (e_x) { d.g_src = gp.ll_xa; d.g_n = c.dim; d.g_e_off = e_x; d.g_dst_off = gp.off_x; }
-                d.mode = RJ_STORE; d.dst = gp.ll_proj; d.e_off = e1 = ++e;
-                d.layer = i;
-                if (L.type == MLB_LAYER_ATTENTION) {
-                    d.flags = GP_MIX_ATTN; d.mix_e2_off = ++e; d.mix_ea_off = e_a = ++e;
-                } else {
-                    d.flags = GP_MIX_DELTA; d.mix_ea_off = e_a = ++e;
-                }
-                ph.push_back(d);
-            }
-            {
-                GridPhase d = blank();      // output projection + residual
-                d.W = L.Wo; d.scale = L.So; d.N = c.dim; d.K = L.o_in; d.row_bytes = (int)(L.o_in * esz);
-                d.g_src = gp.ll_a; d.g_n = L.o_in; d.g_perm = L.o_in / epv; d.g_e_off = e_a; d.g_dst_off = gp.off_a;
-                d.flags = GP_SKIP_GATHER_IF_READY;
-                d.xs_off = gp.off_a; d.mode = RJ_RESID; d.resid_off = gp.off_x; d.dst = gp.ll_xb; d.e_off = e3 = ++e;
-                d.layer = i;
-                ph.push_back(d);
-            }
-            {
-                GridPhase d = blank();      // FFN gate/up + SwiGLU
-                d.W = L.W1a; d.W2 = L.W1b; d.scale = L.S1a; d.scale2 = L.S1b; d.N = c.ffn_dim; d.K = c.dim; d.row_bytes = (int)(c.dim * esz);
-                d.g_src = gp.ll_xb; d.g_n = c.dim; d.g_e_off = e3; d.g_dst_off = gp.off_x2;
-                d.gain = L.g2; d.nsrc_off = gp.off_x2; d.xs_off = gp.off_xn;
-                d.flags = GP_PAIR; d.mode = RJ_SWIGLU; d.dst = gp.ll_h; d.e_off = e4 = ++e;
-                d.layer = i;
-                ph.push_back(d);
-            }
-            if (ple_next) {
-                GridPhase d = blank();      // the next layer's per-layer embedding, this CTA's rows
-                const DevLayer& Ln = s->m->layers[i + 1];
-                d.W = Ln.pleP; d.N = c.dim; d.K = c.ple_dim; d.row_bytes = (int)(c.ple_dim * psz);
-                d.ple_table = Ln.pleT; d.flags = GP_T2 | GP_FILL_PLE;
-                d.mode = RJ_PACC; d.xs_off = gp.off_ple;
-                d.layer = i;
-                ph.push_back(d);
-            }
-            {
-                GridPhase d = blank();      // FFN down + residual (+ that per-layer embedding)
-                d.W = L.W2; d.scale = L.S2; d.N = c.dim; d.K = c.ffn_dim; d.row_bytes = (int)(c.ffn_dim * esz);
-                d.g_src = gp.ll_h; d.g_n = c.ffn_dim; d.g_perm = c.ffn_dim / epv; d.g_e_off = e4; d.g_dst_off = gp.off_h;
-                d.xs_off = gp.off_h; d.mode = RJ_RESID; d.resid_off = gp.off_x2; d.dst = gp.ll_xa; d.e_off = ++e;
-                d.flags = ple_next ? GP_PACC_IN : 0;
-                d.layer = i;
-                e_x = e;
-                ph.push_back(d);
-            }
-        }
-        gp.e_total_nolm = e;
-        {
-            GridPhase d = blank();          // final norm + tied LM head
-            d.W = s->m->E; d.scale = s->m->Es; d.N = c.vocab; d.K = c.dim; d.row_bytes = (int)(c.dim * esz);
-            d.gain = s->m->g_final; d.nsrc_off = gp.off_x; d.xs_off = gp.off_xn;
-            if (e_x) { d.g_src = gp.ll_xa; d.g_n = c.dim; d.g_e_off = e_x; d.g_dst_off = gp.off_x; }
-            d.mode = RJ_LM; d.logits = s->logits; d.e_off = ++e; d.flags = GP_LM;
-            ph.push_back(d);
-        }
-        gp.e_total = e;
-        if ((int)ph.size() != n_phases) return fail(MLB_E_INVALID, "phase list of %zu entries, %d expected", ph.size(), n_phases);
-        GridPhase* dev = nullptr;
-        if ((rc = sess_alloc(s, (void**)&dev, ph.size() * sizeof(GridPhase), false))) return rc;
-        CU(cudaMemcpy(dev, ph.data(), ph.size() * sizeof(GridPhase), cudaMemcpyHostToDevice));
-        gp.phases = dev;
-        gp.n_phases = n_phases;
-    }
-    gp.layers = s->mega_layers; gp.n_layers = c.layers;
+        if (t[0] == '1' && (rc = sess_alloc(s, (void**)&gp.timers, (size_t)C * kGridTimerSlots * 8, true))) return rc;
+    gp.layers = s->step_layers; gp.n_layers = c.layers;
     gp.d = c.dim; gp.F = c.ffn_dim; gp.V = c.vocab; gp.heads = c.heads; gp.kv_heads = c.kv_heads; gp.hd = c.head_dim;
     gp.dk = c.dn_key_dim; gp.dv = c.dn_value_dim; gp.ple = c.ple_dim; gp.qk_norm = c.qk_norm;
     gp.eps = c.rms_eps; gp.l2_eps = 1e-6f;
     gp.E = s->m->E; gp.Es = s->m->Es; gp.g_final = s->m->g_final; gp.rope = s->m->rope;
-    gp.page_table = s->page_table; gp.pt_stride = s->max_pages; gp.logits = s->logits;
+    gp.page_table = s->page_table; gp.logits = s->logits;
     gp.err = s->dev_err;
+    gp.tok_arg = -1;
     gp.backoff_ns = 100;
     if (const char* v = std::getenv("MLB_GRID_BACKOFF_NS")) gp.backoff_ns = std::max(0, std::min(10000, std::atoi(v)));
     s->grid = gp;
@@ -1426,7 +1221,7 @@ static int setup_tc_path(mlb_session* s) {
     s->use_tc = false;
     const char* env = std::getenv("MLB_GEMM");
     const std::string mode = env ? env : "auto";
-    if (!s->parent && (mode == "simt" || s->use_cluster || s->use_grid)) return MLB_OK;
+    if (!s->parent && (mode == "simt" || s->use_grid)) return MLB_OK;
     if (c.weight_dtype != MLB_DT_BF16) {
         if (mode == "tc") return fail(MLB_E_UNSUPPORTED, "MLB_GEMM=tc needs bf16 weights");
         return MLB_OK;
@@ -1697,8 +1492,7 @@ static int session_create(mlb_model* m, int batch, int max_context, int kv_block
     SA(sess_alloc(s, (void**)&s->dev_err, 4, true));
     SA(chain_configure(s));
     if (!parent) {
-        SA(setup_cluster_path(s));
-        if (!s->use_cluster) SA(setup_grid_path(s));
+        SA(setup_grid_path(s));
     }
     SA(setup_tc_path(s));
     if (parent && !s->use_tc) {
@@ -1946,7 +1740,7 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
             s->pinned_tok[b] = in_tokens[b];
         }
     }
-    if (n == 1 && !step_ms && !s->use_grid && !s->use_cluster) {
+    if (n == 1 && !step_ms && !s->use_grid) {
         // the one-token call: one graph launch, one synchronisation
         if ((rc = ensure_token_graph(s, kind, in_tokens != nullptr))) return rc;
         CU(cudaGraphLaunch(s->tgraphs[kind * 2 + (in_tokens ? 1 : 0)], s->stream));
@@ -2114,7 +1908,7 @@ extern "C" int mlb_session_grid_timers(mlb_session* s, long long* out, int cap) 
     if (!s || !out) return fail(MLB_E_INVALID, "null argument");
     if (!s->use_grid || !s->grid.timers) return 0;
     CU(cudaSetDevice(s->m->device));
-    const int n = s->grid_ctas * kGridTimers;
+    const int n = s->grid_ctas * kGridTimerSlots;
     if (cap < n) return fail(MLB_E_INVALID, "room for %d counters needed, %d given", n, cap);
     CU(cudaStreamSynchronize(s->stream));
     CU(cudaMemcpy(out, s->grid.timers, (size_t)n * 8, cudaMemcpyDeviceToHost));

@@ -18,7 +18,7 @@
 #pragma once
 #include <cuda.h>
 
-#include "mega.cuh"   // mbarrier / TMA wrappers
+#include "ring.cuh"   // mbarrier / TMA wrappers
 
 namespace mlb {
 

@@ -16,7 +16,7 @@ static int probe_one(size_t smem, int* per_sm) {
         return 0;
     }
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, grid_decode_kernel<T, T2, KVT>, kMegaThreads, smem) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, grid_decode_kernel<T, T2, KVT>, kRingThreads, smem) != cudaSuccess) {
         cudaGetLastError();
         n = 0;
     }
@@ -29,7 +29,7 @@ static cudaError_t launch_one(int ctas, size_t smem, cudaStream_t st, const Step
     cudaLaunchConfig_t cfg;
     std::memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = dim3(ctas);
-    cfg.blockDim = dim3(kMegaThreads);
+    cfg.blockDim = dim3(kRingThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];

@@ -5,63 +5,55 @@
 
 namespace mlb {
 
-struct MegaLayer;
+struct StepLayer;
 
-// How the rows of a phase are finished: published as they are, added to the residual stream, kept
-// as this CTA's per-layer-embedding contribution, SiLU(gate) * up, or logits with a running argmax.
-enum { RJ_STORE = 0, RJ_RESID = 1, RJ_PACC = 2, RJ_SWIGLU = 3, RJ_LM = 4 };
-
-// One phase of the step that streams weights: what to fetch first, what to normalise, which rows to
-// multiply and how to finish them. The host fills the list once per session (the step is the same
-// list every time); the kernel copies it to shared memory and adds this CTA's row range.
-enum {
-    GP_PAIR = 1,          // gate and up matrices, chunk-interleaved
-    GP_T2 = 2,            // rows of a per-layer-embedding projection (its own element type)
-    GP_PACC_IN = 4,       // add this CTA's per-layer-embedding contribution to the rows
-    GP_FILL_PLE = 8,      // starts with the table row of the pending token
-    GP_MIX_ATTN = 16,     // followed by the attention items and the split combine
-    GP_MIX_DELTA = 32,    // followed by the gated delta-net update
-    GP_SKIP_GATHER_IF_READY = 64,   // the input may already stand in shared memory (direct combine)
-    GP_LM = 128           // the LM head (left out of the prompt chain)
+// One exchanged vector: N values made by the first P CTAs, CTA c owning the contiguous rows
+// [r0(c), r0(c+1)) with r0(c) = floor(c * N / P). A producer's rows stand in a slot of its own
+// (slotw 8-byte words, a multiple of 16: whole 128-byte lines), so that a line has one writer.
+// Measured on B200: with the words packed densely (several writers per line) an all-to-all of 512
+// words among 148 CTAs costs 2.4 us, with one slot per writer 1.2 us.
+struct GridVec {
+    unsigned long long* buf;
+    int N, P;
+    int rpc;               // most rows per producer, ceil(N / P)
+    int slotw;             // 8-byte words per slot
+    unsigned magic;        // q / rpc == __umulhi(q, magic) for every q < P * rpc (checked on the host); 0: rpc == 1
+    int tab;               // shared-memory float offset of the row table r0[0..P] (ints, filled by the kernel)
+    float inv_n;           // 1 / N
+    int pad;
 };
-struct alignas(16) GridPhase {
-    const void* W; const void* W2;                    // row-major weights (W2: the up matrix)
-    const float* scale; const float* scale2;          // FP8 row scales or null
-    const float* gain; const void* ple_table;         // RMS-norm gain or null; per-layer-embedding table
-    const unsigned long long* g_src; unsigned long long* dst;   // exchange words to fetch first / to publish
-    float* logits; long long reserved;
-    int N, K, row_bytes, mode;                        // rows of the matrix, row length, bytes per row, RJ_*
-    int g_n, g_perm, g_e_off, g_dst_off;              // fetch: words, GEMV-layout vectors (0: linear), epoch, shared-memory offset
-    int e_off, resid_off, xs_off, nsrc_off;           // epoch of the output; residual, input, norm source offsets (-1: none)
-    int flags, layer, mix_e2_off, mix_ea_off;         // GP_*; layer; epochs of the mixer's partials and output
-    int r0, rows, pad0, pad1;                         // this CTA's rows (filled in the kernel)
-};
-static_assert(sizeof(GridPhase) == 160, "GridPhase is copied in 16-byte words");
+constexpr int kGridVecs = 8;   // the vectors of GridParams, vx first, stand one after the other
 
 struct GridParams {
-    const GridPhase* phases;
-    int n_phases;                  // with the LM head as the last one
-    int e_total, e_total_nolm;     // epochs one step takes (decode / prompt chain)
-    int off_phases;                // shared-memory copy of the list (16-byte aligned)
-    const MegaLayer* layers;
+    const StepLayer* layers;
     int n_layers;
     int d, F, V, heads, kv_heads, hd, dk, dv, ple, qk_norm;
     float eps, l2_eps;
     const void* E; const float* Es; const float* g_final; const float* rope;
-    const int* page_table; int pt_stride;
+    const int* page_table;
     float* logits;                 // [V]
     int* err;                      // device word: 0 = ok, else the code of the wait that ran out
     int with_lm_head;              // 0 in the prompt chain
     int do_pick;                   // greedy pick + advance inside the kernel
-    // exchange buffers in global memory, 8-byte {value bits, epoch} words
-    unsigned long long *ll_xa, *ll_xb, *ll_proj, *ll_parts, *ll_a, *ll_h, *ll_lm;
+    int tok_arg;                   // >= 0: the pending token, passed with the launch instead of read from StepCtl::tok
     unsigned int* epoch;           // epoch of the last phase of the previous step
-    int s_max;                     // most context splits per kv head the partial buffers hold
-    long long* timers;             // diagnostic: [CTA][kGridTimers] cycle counters, or null
+    // exchanged vectors (kGridVecs of them, contiguous, vx first)
+    GridVec vx, vxb;               // residual stream after the FFN / after the mixer (N = d)
+    GridVec vproj_attn, vproj_dn;  // raw projections of an attention / a delta-net layer (N = n_qkv)
+    GridVec vh;                    // FFN hidden (N = F)
+    GridVec va_dn;                 // delta-net output (N = heads * dv)
+    GridVec va_head;               // attention output combined by the heads' owners (N = heads * hd, P = heads)
+    GridVec vlm;                   // per-CTA argmax pairs (N = 2 * C)
+    unsigned long long* parts;     // flash-decode partials: item i at parts + i * parts_slotw, G * (hd + 2) words
+    int parts_slotw;
+    int vocab_tab;                 // row table of the LM head (shared-memory float offset)
+    int s_max;                     // most context splits per kv head (two-level combine)
+    int s_direct;                  // most splits whose partials every CTA fetches itself
+    int pages_per_split;           // target pages per attention item
+    long long* timers;             // diagnostic: [CTA][kGridTimerSlots] or null
     // shared-memory layout (float offsets), identical in every CTA
-    int off_x, off_x2, off_xn, off_proj, off_parts, off_a, off_h, off_tmp, off_ple, off_pacc, off_red;
-    int off_layers;                // copy of the per-layer table (8-byte aligned)
-    int off_timers;                // kGridTimers 8-byte counters (8-byte aligned)
+    int xs_stride;                 // floats between the two input buffers at off_xs
+    int off_xs, off_xa, off_xb, off_parts, off_gate, off_mix, off_pacc, off_red, off_tabs, off_layers, off_timers, off_plan;
     int off_bar;                   // mbarriers: full[nst] then empty[nst] (8 bytes each)
     int off_ring;                  // ring stages (128-byte aligned)
     int n_stages, stage_bytes;
@@ -69,11 +61,13 @@ struct GridParams {
 };
 
 constexpr uint32_t kGridSpinLimit = 1u << 21;       // polls of one word group before giving up (~1 s)
-constexpr int kGridAttnWarps = 8;
 constexpr int kGridDirectWords = 4096;              // partials every CTA may fetch itself (else the heads' owners combine)
-// Diagnostic cycle counters of thread 0 of every CTA, summed over the steps (kept only by a
-// build with -DMLB_GRID_TIMERS): 0 whole step, 1 gathers, 2 norms, 3 rows, 4 attention items,
-// 5 split combine, 6 delta-net phase, 8 phase set-up, 14 waiting for weight chunks, 15 repeated polls.
-constexpr int kGridTimers = 16;
+// Diagnostic cycle counters of thread 0 of every CTA, summed over the steps (a session made with
+// MLB_GRID_TIMERS=1 allocates them): per phase kind the cycles spent waiting for the input, and the cycles
+// from the input's arrival to the end of the phase.
+//   0 whole step   1 prologue
+//   2/3 projection rows (wait / work)   4/5 attention items   6/7 head-owner combine   8/9 output projection
+//   10/11 delta-net   12/13 gate+up   14/15 down   16/17 LM head   18 waiting for weight chunks
+constexpr int kGridTimerSlots = 32;
 
 }  // namespace mlb

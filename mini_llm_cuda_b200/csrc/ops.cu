@@ -5,7 +5,7 @@
 #include "../../include/mlb.h"
 #include "errors.h"
 #include "kernels.cuh"
-#include "mega.cuh"
+#include "ring.cuh"
 #include "tc_host.h"
 
 using namespace mlb;

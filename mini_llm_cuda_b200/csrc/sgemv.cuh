@@ -13,7 +13,7 @@
 // KV append (one head per CTA), LM head with argmax partials and last-CTA pick.
 // grid = (slabs, B); every mbarrier wait is bounded (Ring::wait).
 #pragma once
-#include "mega.cuh"
+#include "ring.cuh"
 
 namespace mlb {
 
@@ -56,7 +56,6 @@ __global__ void __launch_bounds__(kSgThreads, 1) sgemv_kernel(StepCtl c, GemvPar
     ring.phase = 0;
     ring.dead = dead;
     ring.err = g.err;
-    ring.wait_cycles = 0;
     ring.backoff_ns = 0;
     if (tid == 0) {
         *dead = 0;

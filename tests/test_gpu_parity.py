@@ -60,14 +60,14 @@ def tol_of(spec):
     return TOL_FP32 if spec.weight_dtype == "float32" and spec.kv_dtype == "float32" else TOL_LOWP
 
 
-@pytest.mark.parametrize("path_mode", ["grid", "cluster", "chain", "chain_thread"])
+@pytest.mark.parametrize("path_mode", ["grid", "chain", "chain_thread"])
 @pytest.mark.parametrize("name", list(SPECS))
 def test_greedy_rollout_matches_oracle(api, tmp_path, monkeypatch, name, path_mode):
     """Batch 1: 20-token prompt, 48 greedy tokens: identical ids, logits within tolerance at
     every step (context crosses three KV pages). Run through the decode paths: the whole-GPU
-    single-kernel step, the single-kernel cluster step, the kernel chain with TMA-streamed GEMVs,
-    the chain with per-thread-load GEMVs."""
-    monkeypatch.setenv("MLB_DECODE_PATH", path_mode if path_mode in ("grid", "cluster") else "chain")
+    single-kernel step, the kernel chain with TMA-streamed GEMVs, the chain with per-thread-load
+    GEMVs."""
+    monkeypatch.setenv("MLB_DECODE_PATH", "grid" if path_mode == "grid" else "chain")
     monkeypatch.setenv("MLB_GEMV", "thread" if path_mode == "chain_thread" else "auto")
     spec = SPECS[name]
     path = write_model(tmp_path, spec, seed=3)
@@ -113,10 +113,10 @@ def test_grid_step_long_context_matches_oracle(api, tmp_path, monkeypatch, name)
     model.close()
 
 
-@pytest.mark.parametrize("name,batch,path_mode", [("attn_fp32", 3, "cluster"), ("attn_fp32", 3, "chain"),
-                                                  ("mixed_ple", 9, "auto"), ("mixed_ple", 7, "cluster"),
-                                                  ("bf16", 5, "cluster"), ("bf16", 5, "chain"), ("gqa", 17, "auto"),
-                                                  ("fp8", 4, "cluster"), ("qknorm_gating", 8, "cluster"),
+@pytest.mark.parametrize("name,batch,path_mode", [("attn_fp32", 3, "chain"),
+                                                  ("mixed_ple", 9, "auto"), ("mixed_ple", 7, "chain"),
+                                                  ("bf16", 5, "chain"), ("gqa", 17, "auto"),
+                                                  ("qknorm_gating", 8, "chain"),
                                                   ("fp8", 4, "chain"), ("mixed_ple", 2, "chain_thread"),
                                                   ("gqa", 4, "chain_thread")])
 def test_ragged_batch_matches_oracle(api, tmp_path, monkeypatch, name, batch, path_mode):
@@ -464,13 +464,13 @@ def test_cfg1_latency_config_bf16(api, tmp_path):
     assert (ms > 0).all()
     stats = sess.profile(2, False)
     names = {s["name"] for s in stats}
-    assert names == {"grid_decode_step"} or names == {"cluster_decode_step"} or names >= {"qkv_gemv_norm_rope_kvappend", "attn_flash_decode_paged",
+    assert names == {"grid_decode_step"} or names >= {"qkv_gemv_norm_rope_kvappend", "attn_flash_decode_paged",
                                                          "deltanet_state_update", "lmhead_gemv_norm_argmax"}
     sess.close()
     model.close()
 
 
-@pytest.mark.parametrize("path_mode", ["chain", "cluster"])
+@pytest.mark.parametrize("path_mode", ["chain", "grid"])
 def test_cfg4_dims_fp8_gqa_reduced_depth(api, tmp_path, monkeypatch, path_mode):
     """The quantised larger configuration at its real widths (d=2048, 16 query / 4 kv heads of 128,
     ffn 5632, PLE 128, FP8 e4m3 weights with per-row scales, bf16 KV) with 4 of its 24 layers and
