@@ -20,6 +20,8 @@
 #include "ring.cuh"
 #include "grid_params.h"
 #include "grid_host.h"
+#include "lean_params.h"
+#include "lean_host.h"
 #include "model_file.h"
 #include "sgemv.cuh"
 
@@ -459,6 +461,11 @@ struct mlb_session {
     int grid_ctas = 0;
     size_t grid_smem = 0;
     mlb::GridParams grid;
+    // the same step with compile-time shapes, for the models it is built for
+    bool use_lean = false;
+    int lean_idx = -1;
+    size_t lean_smem = 0;
+    mlb::LeanParams lean;
     // tensor-core projections (bf16 weights, batch >= 16)
     bool use_tc = false;
     int tc_nb = 0, tc_stages = 0, tc_stages_swiglu = 0;
@@ -703,16 +710,23 @@ struct Chain {
     // One decode (or prefill) step of a batch-1 session as a single cooperative kernel over all
     // SMs (plus the sampler for top-k).
     static int run_grid(mlb_session* s, int kind, const StepCtl& c, Recorder* rec, int* n_launches) {
-        GridParams gp = s->grid;
-        gp.with_lm_head = kind == CHAIN_PREFILL ? 0 : 1;
-        gp.do_pick = kind == CHAIN_GREEDY ? 1 : 0;
         int rc, launches = 0;
         if (rec) {
             uint64_t w, kv, st, rows;
             mlb_session_step_bytes(s, &w, &kv, &st, &rows);
             if ((rc = rec->begin("grid_decode_step", w + kv + st + rows, 0))) return rc;
         }
-        CU(grid_kernel_launch(s->m->cfg.weight_dtype, s->m->cfg.kv_dtype, s->grid_ctas, s->grid_smem, s->stream, c, gp));
+        if (s->use_lean) {
+            LeanParams lp = s->lean;
+            lp.with_lm_head = kind == CHAIN_PREFILL ? 0 : 1;
+            lp.do_pick = kind == CHAIN_GREEDY ? 1 : 0;
+            CU(lean_kernel_launch(s->lean_idx, s->m->cfg.kv_dtype, s->lean_smem, s->stream, c, lp));
+        } else {
+            GridParams gp = s->grid;
+            gp.with_lm_head = kind == CHAIN_PREFILL ? 0 : 1;
+            gp.do_pick = kind == CHAIN_GREEDY ? 1 : 0;
+            CU(grid_kernel_launch(s->m->cfg.weight_dtype, s->m->cfg.kv_dtype, s->grid_ctas, s->grid_smem, s->stream, c, gp));
+        }
         if (rec && (rc = rec->end())) return rc;
         ++launches;
         if (kind == CHAIN_TOPK) {
@@ -911,7 +925,7 @@ struct Chain {
         const StepCtl c = make_ctl(s, kind);
         const int d = cfg.dim, F = cfg.ffn_dim, B = s->B, p = cfg.ple_dim;
         int launches = 0, rc;
-        if (s->use_grid) return run_grid(s, kind, c, rec, n_launches);
+        if (s->use_lean || s->use_grid) return run_grid(s, kind, c, rec, n_launches);
         if (s->use_tc) return run_tc(s, kind, c, rec, n_launches);
 
         if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * (d * sizeof(T) + (uint64_t)p * sizeof(T2) + (uint64_t)d * 4) + (uint64_t)d * p * sizeof(T2), 0))) return rc;
@@ -1053,6 +1067,88 @@ static int build_step_layers(mlb_session* s) {
     int rc = sess_alloc(s, (void**)&s->step_layers, hl.size() * sizeof(StepLayer), false);
     if (rc) return rc;
     CU(cudaMemcpy(s->step_layers, hl.data(), hl.size() * sizeof(StepLayer), cudaMemcpyHostToDevice));
+    return MLB_OK;
+}
+
+// The whole-GPU step with compile-time shapes (lean.cuh), for batch-1 sessions of the models it is built
+// for. MLB_DECODE_PATH = auto (this kernel where it fits, else the generic one) | lean | grid | chain.
+static int setup_lean_path(mlb_session* s) {
+    const mlb_config& c = s->m->cfg;
+    const char* env = std::getenv("MLB_DECODE_PATH");
+    const std::string mode = env ? env : "auto";
+    s->use_lean = false;
+    if (mode != "lean" && mode != "auto") return MLB_OK;
+    auto no = [&](const char* why) {
+        if (mode == "lean") return fail(MLB_E_UNSUPPORTED, "MLB_DECODE_PATH=lean: %s", why);
+        return (int)MLB_OK;
+    };
+    if (s->B != 1) return no("the whole-GPU step serves batch 1 only");
+    const int idx = lean_find_shape(c);
+    if (idx < 0) return no("no specialised kernel is built for this model's shape");
+    const LeanShapeInfo& si = lean_shape_info(idx);
+    int coop = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, s->m->device);
+    if (!coop || s->sm_count < si.C) return no("the device cannot keep the kernel's CTAs resident");
+    for (const DevLayer& L : s->m->layers)
+        if (L.o_in != si.H * si.HD) return no("a layer's output projection has another input width");
+    auto up4 = [](int v) { return (v + 3) / 4 * 4; };
+    LeanParams lp;
+    std::memset(&lp, 0, sizeof lp);
+    int off = 0;
+    lp.xs_stride = up4(si.xs_floats);
+    lp.off_xs = off; off += 2 * lp.xs_stride;
+    lp.off_xa = off; off += up4(si.D);
+    lp.off_xb = off; off += up4(si.D);
+    lp.off_parts = off; off += up4(si.parts_floats);
+    lp.off_mix = off; off += up4(si.mix_floats);
+    lp.off_pacc = off; off += up4(std::max(1, c.layers * si.rx));
+    lp.off_red = off; off += 2 * kLeanWarps + 8;
+    off = (off + 1) / 2 * 2;
+    lp.off_layers = off; off += up4((int)(c.layers * sizeof(StepLayer) / 4));
+    lp.off_timers = off; off += 2 * kGridTimerSlots;
+    lp.off_plan = off; off += 12;
+    off = (off + 31) / 32 * 32;
+    const int max_stages = 12;
+    lp.off_bar = off; off += max_stages * 2 * 2;
+    off = (off + 31) / 32 * 32;
+    lp.off_ring = off;
+    const size_t fixed = (size_t)off * 4;
+    if (fixed + 4 * (size_t)kLeanStage > 208 * 1024) return no("too little shared memory is left for the weight ring");
+    lp.n_stages = (int)std::min<size_t>(max_stages, (208 * 1024 - fixed) / kLeanStage);
+    const size_t smem = fixed + (size_t)lp.n_stages * kLeanStage;
+    int per_sm = 0, rc;
+    if ((rc = lean_kernel_probe(idx, c.kv_dtype, smem, &per_sm))) return rc;
+    if (per_sm < 1) return no("the kernel does not fit an SM");
+    if ((rc = build_step_layers(s))) return rc;
+    // exchange buffers (zeroed: epoch 0 is never produced)
+    const size_t C = (size_t)si.C;
+    const size_t n_ll = C * (2 * (size_t)si.slot_x + si.slot_qa + si.slot_qd + si.slot_parts + si.slot_a + si.slot_ah + si.slot_h + 16) + 64;
+    unsigned long long* ll = nullptr;
+    if ((rc = sess_alloc(s, (void**)&ll, n_ll * 8, true))) return rc;
+    lp.x = ll; ll += C * si.slot_x;
+    lp.xb = ll; ll += C * si.slot_x;
+    lp.pj = ll; ll += C * std::max(si.slot_qa, si.slot_qd);
+    ll += C * std::min(si.slot_qa, si.slot_qd);
+    lp.parts = ll; ll += C * si.slot_parts;
+    lp.a = ll; ll += C * si.slot_a;
+    lp.ah = ll; ll += C * si.slot_ah;
+    lp.h = ll; ll += C * si.slot_h;
+    lp.lm = ll; ll += C * 16;
+    if ((rc = sess_alloc(s, (void**)&lp.epoch, 16, true))) return rc;
+    if (const char* t = std::getenv("MLB_GRID_TIMERS"))
+        if (t[0] == '1' && (rc = sess_alloc(s, (void**)&lp.timers, C * kGridTimerSlots * 8, true))) return rc;
+    lp.layers = s->step_layers; lp.n_layers = c.layers;
+    lp.E = s->m->E; lp.g_final = s->m->g_final; lp.rope = s->m->rope; lp.page_table = s->page_table;
+    lp.logits = s->logits; lp.err = s->dev_err;
+    lp.tok_arg = -1;
+    lp.eps = c.rms_eps; lp.l2_eps = 1e-6f;
+    lp.pages_per_split = 16;
+    if (const char* v = std::getenv("MLB_GRID_PAGES_PER_SPLIT")) lp.pages_per_split = std::max(1, std::min(256, std::atoi(v)));
+    s->lean = lp;
+    s->lean_idx = idx;
+    s->lean_smem = smem;
+    s->grid_ctas = si.C;
+    s->use_lean = true;
     return MLB_OK;
 }
 
@@ -1221,7 +1317,7 @@ static int setup_tc_path(mlb_session* s) {
     s->use_tc = false;
     const char* env = std::getenv("MLB_GEMM");
     const std::string mode = env ? env : "auto";
-    if (!s->parent && (mode == "simt" || s->use_grid)) return MLB_OK;
+    if (!s->parent && (mode == "simt" || s->use_grid || s->use_lean)) return MLB_OK;
     if (c.weight_dtype != MLB_DT_BF16) {
         if (mode == "tc") return fail(MLB_E_UNSUPPORTED, "MLB_GEMM=tc needs bf16 weights");
         return MLB_OK;
@@ -1281,7 +1377,7 @@ static int ensure_graph(mlb_session* s, int kind) {
         s->graphs[kind] = nullptr;
     }
     if (s->graphs[kind]) return MLB_OK;
-    if (s->use_grid) {
+    if (s->use_grid || s->use_lean) {
         // one cooperative launch per step (plus the sampler): launched directly, nothing to capture
         s->launches_per_step[kind] = kind == CHAIN_TOPK ? 2 : 1;
         if (kind == CHAIN_TOPK) { s->g_topk = s->cur_topk; s->g_temp = s->cur_temp; }
@@ -1334,7 +1430,7 @@ static int ensure_token_graph(mlb_session* s, int kind, bool with_input) {
 
 // One step on the session's stream: the captured chain, or the single cooperative kernel.
 static int launch_step(mlb_session* s, int kind) {
-    if (s->use_grid) return chain_run(s, kind, nullptr, nullptr);
+    if (s->use_grid || s->use_lean) return chain_run(s, kind, nullptr, nullptr);
     CU(cudaGraphLaunch(s->graphs[kind], s->stream));
     return MLB_OK;
 }
@@ -1492,7 +1588,8 @@ static int session_create(mlb_model* m, int batch, int max_context, int kv_block
     SA(sess_alloc(s, (void**)&s->dev_err, 4, true));
     SA(chain_configure(s));
     if (!parent) {
-        SA(setup_grid_path(s));
+        SA(setup_lean_path(s));
+        if (!s->use_lean) SA(setup_grid_path(s));
     }
     SA(setup_tc_path(s));
     if (parent && !s->use_tc) {
@@ -1740,7 +1837,7 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
             s->pinned_tok[b] = in_tokens[b];
         }
     }
-    if (n == 1 && !step_ms && !s->use_grid) {
+    if (n == 1 && !step_ms && !s->use_grid && !s->use_lean) {
         // the one-token call: one graph launch, one synchronisation
         if ((rc = ensure_token_graph(s, kind, in_tokens != nullptr))) return rc;
         CU(cudaGraphLaunch(s->tgraphs[kind * 2 + (in_tokens ? 1 : 0)], s->stream));
@@ -1906,13 +2003,14 @@ extern "C" int mlb_session_step_bytes(mlb_session* s, uint64_t* weights, uint64_
 
 extern "C" int mlb_session_grid_timers(mlb_session* s, long long* out, int cap) {
     if (!s || !out) return fail(MLB_E_INVALID, "null argument");
-    if (!s->use_grid || !s->grid.timers) return 0;
+    long long* timers = s->use_lean ? s->lean.timers : (s->use_grid ? s->grid.timers : nullptr);
+    if (!timers) return 0;
     CU(cudaSetDevice(s->m->device));
     const int n = s->grid_ctas * kGridTimerSlots;
     if (cap < n) return fail(MLB_E_INVALID, "room for %d counters needed, %d given", n, cap);
     CU(cudaStreamSynchronize(s->stream));
-    CU(cudaMemcpy(out, s->grid.timers, (size_t)n * 8, cudaMemcpyDeviceToHost));
-    CU(cudaMemset(s->grid.timers, 0, (size_t)n * 8));
+    CU(cudaMemcpy(out, timers, (size_t)n * 8, cudaMemcpyDeviceToHost));
+    CU(cudaMemset(timers, 0, (size_t)n * 8));
     return s->grid_ctas;
 }
 

@@ -172,7 +172,7 @@ __device__ __noinline__ float ll_gather_vec(const GridVec* vp, uint32_t e, const
 }
 
 // Rows [row0, row0 + n) of a vector to dst[0..n).
-__device__ __noinline__ void ll_gather_rows(const GridVec* vp, int row0, int n, uint32_t e, float* dst, const int* tabs, volatile int* dead,
+static __device__ __noinline__ void ll_gather_rows(const GridVec* vp, int row0, int n, uint32_t e, float* dst, const int* tabs, volatile int* dead,
                                             int* err) {
     const int P = vp->P, slotw = vp->slotw, tab = vp->tab;
     const float pn = (float)P * vp->inv_n;

@@ -113,6 +113,39 @@ def test_grid_step_long_context_matches_oracle(api, tmp_path, monkeypatch, name)
     model.close()
 
 
+@pytest.mark.parametrize("kv_dtype,prompt_len,pages_per_split", [("bfloat16", 40, 16), ("float32", 40, 16), ("bfloat16", 300, 16),
+                                                                  ("bfloat16", 300, 1), ("bfloat16", 200, 2)])
+def test_shape_specialised_step_matches_oracle(api, tmp_path, monkeypatch, kv_dtype, prompt_len, pages_per_split):
+    """The whole-GPU step with compile-time shapes (the 1-GPU latency configuration's widths: d=512,
+    8 heads of 64, ffn 1408, PLE 64, vocab 8192, bf16 weights) on 4 layers, attention and delta-net
+    alternating: short and long contexts, few context splits (every CTA combines them) and many (the
+    heads' owners combine them)."""
+    monkeypatch.setenv("MLB_DECODE_PATH", "lean")
+    monkeypatch.setenv("MLB_PREFILL", "step")
+    monkeypatch.setenv("MLB_GRID_PAGES_PER_SPLIT", str(pages_per_split))
+    spec = ModelSpec(dim=512, layers=4, heads=8, head_dim=64, ffn_dim=1408, vocab=8192, max_context=512, rms_eps=1e-5,
+                     ple_dim=64, layer_types=periodic_layer_types(4, 2), weight_dtype="bfloat16", kv_dtype=kv_dtype)
+    path = write_model(tmp_path, spec, seed=5)
+    oracle = load_oracle(path)
+    prompt = random_prompts(spec.vocab, [prompt_len], seed=6)[0]
+    want_tok, want_logits = oracle_rollout(oracle, prompt, 24)
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    sess.prefill([prompt])
+    assert sess.launches_per_step() == 1
+    got = []
+    worst = 0.0
+    for i in range(24):
+        got.append(int(sess.decode_step()[0]))
+        worst = max(worst, logits_error(sess.logits()[0], want_logits[i]))
+        if got[-1] != want_tok[i]:
+            break
+    assert worst < TOL_LOWP, f"logits error {worst}"
+    assert got == want_tok[:len(got)].tolist() and len(got) == 24
+    sess.close()
+    model.close()
+
+
 @pytest.mark.parametrize("name,batch,path_mode", [("attn_fp32", 3, "chain"),
                                                   ("mixed_ple", 9, "auto"), ("mixed_ple", 7, "chain"),
                                                   ("bf16", 5, "chain"), ("gqa", 17, "auto"),
