@@ -158,12 +158,16 @@ int mlb_session_step_bytes(mlb_session* s, uint64_t* weights, uint64_t* kv, uint
                            uint64_t* rows);
 /* Kernels launched per decode step by the current configuration. */
 int mlb_session_launches_per_step(mlb_session* s);
-/* Diagnostic of the batch-1 single-kernel step (no counterpart in the reference). When the
- * session was created with MLB_GRID_TIMERS=1 in the environment, copies 16 cycle counters per
- * CTA (summed over the steps since the last call; what each one covers is listed beside
- * kGridTimers in csrc/grid.cuh), clears them and returns the number of CTAs; returns 0 when the
- * session does not run that step or keeps no counters. */
+/* Diagnostics of the batch-1 single-kernel step (no counterpart in the reference). When the
+ * session was created with MLB_GRID_TIMERS=1 in the environment, mlb_session_grid_timers copies
+ * 32 cycle counters per CTA (summed over the steps since the last call; what each one covers is
+ * listed beside kGridTimerSlots in csrc/grid_params.h), clears them and returns the number of
+ * CTAs; returns 0 when the session does not run that step or keeps no counters.
+ * mlb_session_grid_trace copies 256 events per CTA of the last step of the shape-specialised
+ * kernel: (global nanosecond timer << 8) | counter index at every point where a counter is
+ * updated; 0 when no trace is kept. */
 int mlb_session_grid_timers(mlb_session* s, long long* out, int cap);
+int mlb_session_grid_trace(mlb_session* s, long long* out, int cap);
 
 /* Host-only page allocator of the KV cache, exposed so that its failure paths can be
  * tested without a device. */

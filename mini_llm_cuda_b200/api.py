@@ -85,6 +85,7 @@ def lib() -> C.CDLL:
         "mlb_session_step_bytes": (C.c_int, [vp, u64p, u64p, u64p, u64p]),
         "mlb_session_launches_per_step": (C.c_int, [vp]),
         "mlb_session_grid_timers": (C.c_int, [vp, C.POINTER(C.c_longlong), C.c_int]),
+        "mlb_session_grid_trace": (C.c_int, [vp, C.POINTER(C.c_longlong), C.c_int]),
         "mlb_op_wait_probe": (C.c_int, [C.c_int, C.c_uint32]),
         "mlb_score_tokens": (C.c_int, [vp, C.POINTER(C.c_int32), C.c_int, C.POINTER(C.c_float)]),
         "mlb_kv_alloc_new": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
@@ -297,6 +298,12 @@ class Session:
 
     def launches_per_step(self) -> int:
         return check(lib().mlb_session_launches_per_step(self._h))
+
+    def grid_trace(self) -> np.ndarray:
+        """[CTAs][256] trace events of the last single-kernel step (MLB_GRID_TIMERS=1), else empty."""
+        buf = np.zeros(1024 * 256, dtype=np.int64)
+        n = check(lib().mlb_session_grid_trace(self._h, _ptr(buf, C.c_longlong), buf.size))
+        return buf[:n * 256].reshape(n, 256).copy()
 
     def grid_timers(self) -> np.ndarray:
         """[CTAs][20] cycle counters of the single-kernel step (MLB_GRID_TIMERS=1), else empty."""

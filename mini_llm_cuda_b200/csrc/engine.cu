@@ -1102,7 +1102,7 @@ static int setup_lean_path(mlb_session* s) {
     lp.off_parts = off; off += up4(si.parts_floats);
     lp.off_mix = off; off += up4(si.mix_floats);
     lp.off_pacc = off; off += up4(std::max(1, c.layers * si.rx));
-    lp.off_red = off; off += 2 * kLeanWarps + 8;
+    lp.off_red = off; off += 2 * kLeanWarps + 4 + 128;      // + the dead flag, the finished-row counter, the finished rows
     off = (off + 1) / 2 * 2;
     lp.off_layers = off; off += up4((int)(c.layers * sizeof(StepLayer) / 4));
     lp.off_timers = off; off += 2 * kGridTimerSlots;
@@ -1137,6 +1137,7 @@ static int setup_lean_path(mlb_session* s) {
     if ((rc = sess_alloc(s, (void**)&lp.epoch, 16, true))) return rc;
     if (const char* t = std::getenv("MLB_GRID_TIMERS"))
         if (t[0] == '1' && (rc = sess_alloc(s, (void**)&lp.timers, C * kGridTimerSlots * 8, true))) return rc;
+    if (lp.timers && (rc = sess_alloc(s, (void**)&lp.trace, C * kLeanTraceLen * 8, true))) return rc;
     lp.layers = s->step_layers; lp.n_layers = c.layers;
     lp.E = s->m->E; lp.g_final = s->m->g_final; lp.rope = s->m->rope; lp.page_table = s->page_table;
     lp.logits = s->logits; lp.err = s->dev_err;
@@ -2011,6 +2012,17 @@ extern "C" int mlb_session_grid_timers(mlb_session* s, long long* out, int cap) 
     CU(cudaStreamSynchronize(s->stream));
     CU(cudaMemcpy(out, timers, (size_t)n * 8, cudaMemcpyDeviceToHost));
     CU(cudaMemset(timers, 0, (size_t)n * 8));
+    return s->grid_ctas;
+}
+
+extern "C" int mlb_session_grid_trace(mlb_session* s, long long* out, int cap) {
+    if (!s || !out) return fail(MLB_E_INVALID, "null argument");
+    if (!s->use_lean || !s->lean.trace) return 0;
+    CU(cudaSetDevice(s->m->device));
+    const int n = s->grid_ctas * kLeanTraceLen;
+    if (cap < n) return fail(MLB_E_INVALID, "room for %d events needed, %d given", n, cap);
+    CU(cudaStreamSynchronize(s->stream));
+    CU(cudaMemcpy(out, s->lean.trace, (size_t)n * 8, cudaMemcpyDeviceToHost));
     return s->grid_ctas;
 }
 

@@ -145,9 +145,14 @@ enum { LM_STORE = 0, LM_RESID = 1, LM_SWIGLU = 2, LM_LOGITS = 3 };
 // This CTA's rows (at most ROWS, `rows` here) of a matrix with rows of K elements, out of the ring.
 // Local row r belongs to warp r % 16. MODE says how a row is finished. The chunk geometry is the
 // producer's: whole rows per 16 KB stage, gate and up chunks alternating (PAIR).
+// The finished rows are collected in shared memory (`obuf`) and the warp that finishes the last one
+// (`ocnt` counts them) publishes the whole slot with ONE store instruction: a line that all CTAs
+// poll must change once. (Measured on B200: with the rows of a slot stored one by one by their warps,
+// a few dozen cycles apart, an exchange costs 3-4 us instead of 1.2 us.)
 template <int K, int ROWS, int MODE, bool PAIR>
 __device__ __forceinline__ void lean_rows(Ring& r, int rows, int row0, const float* xs, float rn, unsigned long long* dst, uint32_t e,
-                                          const float* resid, const float* pacc, float* logits, int warp, int lane, float& bv, int& bi) {
+                                          const float* resid, const float* pacc, float* logits, float* obuf, int* ocnt, int warp, int lane, float& bv, int& bi,
+                                          long long* tm = nullptr) {
     constexpr int RPS = kLeanStage / (K * 2);        // rows per stage
     static_assert(RPS >= 1, "a row must fit a ring stage");
     constexpr int NCH = (ROWS + RPS - 1) / RPS;
@@ -157,6 +162,7 @@ __device__ __forceinline__ void lean_rows(Ring& r, int rows, int row0, const flo
         if (c0 >= rows) break;
         const int n = min(RPS, rows - c0);
         const int ia = r.idx;
+        const long long tw = tm ? clock64() : 0;
         r.wait(r.full0 + 8u * r.idx, r.phase, 2);
         r.advance();
         int ib = ia;
@@ -165,6 +171,8 @@ __device__ __forceinline__ void lean_rows(Ring& r, int rows, int row0, const flo
             r.wait(r.full0 + 8u * r.idx, r.phase, 2);
             r.advance();
         }
+        const long long td = tm ? clock64() : 0;
+        if (tm && threadIdx.x == 0) tm[18] += td - tw;
         const bf16_t* A = reinterpret_cast<const bf16_t*>(r.stages + (size_t)ia * kLeanStage);
         const bf16_t* Bm = reinterpret_cast<const bf16_t*>(r.stages + (size_t)ib * kLeanStage);
 #pragma unroll 1
@@ -175,6 +183,7 @@ __device__ __forceinline__ void lean_rows(Ring& r, int rows, int row0, const flo
                 const float u = lean_dot<K>(Bm + lr * K, xs, lane) * rn;
                 v = __fdividef(v, 1.0f + __expf(-v)) * u;      // applySiluToFFN + hadamardMultiplyFFN, inference.cu:262-281
             }
+            int last = 0;
             if (lane == 0) {
                 if (MODE == LM_RESID) {
                     v += resid[row0 + wrow];
@@ -185,10 +194,23 @@ __device__ __forceinline__ void lean_rows(Ring& r, int rows, int row0, const flo
                     logits[row] = v;
                     if (v > bv || (v == bv && row < bi)) { bv = v; bi = row; }
                 } else {
-                    ll_store(dst + wrow, v, e);
+                    obuf[wrow] = v;
+                    __threadfence_block();
+                    last = atomicAdd(ocnt, 1) == rows - 1;
+                }
+            }
+            if (MODE != LM_LOGITS) {
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence_block();
+#pragma unroll
+                    for (int j0 = 0; j0 < ROWS; j0 += 32)
+                        if (j0 + lane < rows) ll_store(dst + j0 + lane, obuf[j0 + lane], e);
+                    if (lane == 0) *ocnt = 0;
                 }
             }
         }
+        if (tm && threadIdx.x == 0) tm[19] += clock64() - td;
         __syncwarp();
         if (lane == 0) {
             mbar_arrive(r.empty0 + 8u * ia);
@@ -220,9 +242,9 @@ __device__ __forceinline__ void lean_issue(Ring& r, const unsigned char* a, cons
 
 // Flash-decode of this CTA's item out of shared memory (grid_attention with compile-time shapes,
 // no QK-norm): 16/G warps per query head. Publishes G partials in the item's slot.
-template <typename S, typename KVT>
+template <typename S, typename KVT, typename Mark>
 __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLayer& L, const GridPlan& it, Ring& ring, float* mix, int rank,
-                                               int pos, uint32_t e_proj, uint32_t e_out, int tid, volatile int* dead, int* err) {
+                                               int pos, uint32_t e_proj, uint32_t e_out, int tid, volatile int* dead, int* err, Mark&& mark) {
     constexpr int HD = S::HD, G = S::G, W = S::W;
     constexpr int EPL = 16 / (int)sizeof(KVT), LPR = HD / EPL, PPI = 32 / LPR;
     constexpr int WPH = kLeanWarps / G;               // warps per query head
@@ -246,6 +268,7 @@ __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLa
         lean_gather_rows<S::RQA>(p.pj, S::H * HD + S::KVH * HD + kvh * HD, HD, e_proj, tv, tid, dead, err);
     }
     consumer_sync<kLeanWarps>();
+    mark(20);
     // RoPE on adjacent pairs (inference.cu:113-134): one warp per vector; the new K/V row goes to the pool
     {
         const int nvecs = G + (it.cur_here ? 1 : 0);
@@ -279,6 +302,7 @@ __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLa
         }
     }
     consumer_sync<kLeanWarps>();
+    mark(21);
     const float inv_div = rsqrtf((float)HD);          // scores are divided by sqrt(hd), inference.cu:154
     float q[EPL], acc[EPL], m = kNegBig, l = 0.f;
 #pragma unroll
@@ -324,6 +348,7 @@ __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLa
             mbar_arrive(ring.empty0 + 8u * ib);
         }
     }
+    mark(22);
     if (it.cur_here && sub == 0) {
         // the current position, from shared memory
         float s = 0.f;
@@ -362,6 +387,7 @@ __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLa
         if (lr == 0) { w[HD] = m; w[HD + 1] = l; }
     }
     consumer_sync<kLeanWarps>();
+    mark(23);
     // merge the warps of each head; one thread per element of the item's partials
     unsigned long long* dst = p.parts + (size_t)rank * lean_slot(G * W);
 #pragma unroll 1
@@ -429,7 +455,7 @@ __device__ __forceinline__ void lean_combine(const LeanParams& p, int Ssp, int h
 // Gated delta-net step on this CTA's rows of the state (grid_delta_net with compile-time shapes).
 template <typename S>
 __device__ __forceinline__ void lean_delta_net(const LeanParams& p, const StepLayer& L, Ring& ring, float* mix, int rank, uint32_t e_proj,
-                                               uint32_t e_out, int tid, volatile int* dead, int* err) {
+                                               uint32_t e_out, float* obuf, int* ocnt, int tid, volatile int* dead, int* err) {
     constexpr int H = S::H, DK = S::DK, DV = S::DV, RAD = S::RAD;
     constexpr int RPS = kLeanStage / (DK * 4);
     static_assert(DK % 32 == 0 && DK <= 128 && RAD <= RPS, "delta-net shape not supported");
@@ -490,7 +516,19 @@ __device__ __forceinline__ void lean_delta_net(const LeanParams& p, const StepLa
             Srow[lane + 32 * i] = s[i];
         }
         d2 = warp_sum(d2);
-        if (lane == 0) ll_store(dst + wrow, d2, e_out);
+        // the warp that finishes the CTA's last row publishes the slot with one store instruction
+        int last = 0;
+        if (lane == 0) {
+            obuf[wrow] = d2;
+            __threadfence_block();
+            last = atomicAdd(ocnt, 1) == rows - 1;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            __threadfence_block();
+            for (int j = lane; j < rows; j += 32) ll_store(dst + j, obuf[j], e_out);
+            if (lane == 0) *ocnt = 0;
+        }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(ring.empty0 + 8u * ia);
@@ -625,6 +663,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
     }
     if (tid == 0) {
         *dead = 0;
+        dead[1] = 0;                     // the finished-row counter
         for (int i = 0; i < p.n_stages; ++i) {
             mbar_init(ring.full0 + 8u * i, 1);
             mbar_init(ring.empty0 + 8u * i, kLeanWarps);
@@ -641,6 +680,8 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
     constexpr int D = S::D, F = S::F, RX = S::RX;
     float* xsb[2] = {smem + p.off_xs, smem + p.off_xs + p.xs_stride};
     float* redb[2] = {smem + p.off_red, smem + p.off_red + kLeanWarps};
+    int* ocnt = reinterpret_cast<int*>(smem + p.off_red + 2 * kLeanWarps + 1);
+    float* obuf = smem + p.off_red + 2 * kLeanWarps + 4;      // finished rows of the current phase
     float* xa = smem + p.off_xa;
     float* xb = smem + p.off_xb;
     float* pacc = smem + p.off_pacc;    // [layer][RX]
@@ -652,11 +693,17 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
         if (tid == 0) for (int i = 0; i < kGridTimerSlots; ++i) tm[i] = 0;
         tstart = tmark = clock64();
     }
+    int n_trace = 0;
     auto mark = [&](int i) {
         if (tm != nullptr && tid == 0) {
             const long long n = clock64();
             tm[i] += n - tmark;
             tmark = n;
+            if (p.trace != nullptr && n_trace < kLeanTraceLen) {
+                unsigned long long g;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g));
+                p.trace[(size_t)rank * kLeanTraceLen + n_trace++] = (long long)((g << 8) | (unsigned long long)i);
+            }
         }
     };
     float bv = -INFINITY;
@@ -709,11 +756,11 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
             if (attn) {
                 const int r0 = min(rank * S::RQA, S::NQ_A), rows = min(S::RQA, S::NQ_A - r0);
                 lean_rows<D, S::RQA, LM_STORE, false>(ring, rows, r0, xs, rn, p.pj + (size_t)rank * lean_slot(S::RQA), e_proj,
-                                                      nullptr, nullptr, nullptr, warp, lane, bv, bi);
+                                                      nullptr, nullptr, nullptr, obuf, ocnt, warp, lane, bv, bi, tm);
             } else {
                 const int r0 = min(rank * S::RQD, S::NQ_D), rows = min(S::RQD, S::NQ_D - r0);
                 lean_rows<D, S::RQD, LM_STORE, false>(ring, rows, r0, xs, rn, p.pj + (size_t)rank * lean_slot(S::RQD), e_proj,
-                                                      nullptr, nullptr, nullptr, warp, lane, bv, bi);
+                                                      nullptr, nullptr, nullptr, obuf, ocnt, warp, lane, bv, bi, tm);
             }
             mark(3);
         }
@@ -724,7 +771,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
                 const GridPlan& it = *plan;
                 const uint32_t e_parts = ++e;
                 if (it.has) {
-                    lean_attention<S, KVT>(p, L, it, ring, mix, rank, pos, e_proj, e_parts, tid, dead, p.err);
+                    lean_attention<S, KVT>(p, L, it, ring, mix, rank, pos, e_proj, e_parts, tid, dead, p.err, mark);
                     mark(5);
                 }
                 if (it.direct) {
@@ -737,14 +784,14 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
                 }
             } else {
                 const uint32_t e_a = ++e;
-                lean_delta_net<S>(p, L, ring, mix, rank, e_proj, e_a, tid, dead, p.err);
+                lean_delta_net<S>(p, L, ring, mix, rank, e_proj, e_a, obuf, ocnt, tid, dead, p.err);
                 mark(11);
                 lean_gather<S::NA_D, S::RAD, false, false>(p.a, e_a, nullptr, nullptr, xs, tid, dead, p.err);
             }
             consumer_sync<kLeanWarps>();
             mark(8);
             ++e;
-            lean_rows<S::NA_A, RX, LM_RESID, false>(ring, RX, xr0, xs, 1.0f, p.xb + (size_t)rank * lean_slot(RX), e, xa, nullptr, nullptr, warp, lane, bv, bi);
+            lean_rows<S::NA_A, RX, LM_RESID, false>(ring, RX, xr0, xs, 1.0f, p.xb + (size_t)rank * lean_slot(RX), e, xa, nullptr, nullptr, obuf, ocnt, warp, lane, bv, bi, tm);
             mark(9);
         }
         // ---- FFN gate/up + SwiGLU ----
@@ -759,7 +806,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
             const float rn = lean_rnorm<D>(red, lane, p.eps);
             ++e;
             const int r0 = min(rank * S::RH, F), rows = min(S::RH, F - r0);
-            lean_rows<D, S::RH, LM_SWIGLU, true>(ring, rows, r0, xs, rn, p.h + (size_t)rank * lean_slot(S::RH), e, nullptr, nullptr, nullptr, warp, lane, bv, bi);
+            lean_rows<D, S::RH, LM_SWIGLU, true>(ring, rows, r0, xs, rn, p.h + (size_t)rank * lean_slot(S::RH), e, nullptr, nullptr, nullptr, obuf, ocnt, warp, lane, bv, bi, tm);
             mark(13);
         }
         // ---- FFN down + residual (+ the next layer's per-layer embedding) ----
@@ -770,7 +817,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
             mark(14);
             ++e;
             lean_rows<F, RX, LM_RESID, false>(ring, RX, xr0, xs, 1.0f, p.x + (size_t)rank * lean_slot(RX), e, xb,
-                                              (S::PLE > 0 && li + 1 < p.n_layers) ? pacc + (li + 1) * RX : nullptr, nullptr, warp, lane, bv, bi);
+                                              (S::PLE > 0 && li + 1 < p.n_layers) ? pacc + (li + 1) * RX : nullptr, nullptr, obuf, ocnt, warp, lane, bv, bi, tm);
             e_x = e;
             mark(15);
         }
@@ -785,7 +832,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
         mark(16);
         const float rn = lean_rnorm<D>(red, lane, p.eps);
         const int r0 = min(rank * S::RV, S::V), rows = min(S::RV, S::V - r0);
-        lean_rows<D, S::RV, LM_LOGITS, false>(ring, rows, r0, xs, rn, nullptr, 0, nullptr, nullptr, p.logits, warp, lane, bv, bi);
+        lean_rows<D, S::RV, LM_LOGITS, false>(ring, rows, r0, xs, rn, nullptr, 0, nullptr, nullptr, p.logits, obuf, ocnt, warp, lane, bv, bi, tm);
         // reduce the warps' argmax picks (lane 0 of each warp holds them), then (in CTA 0) the grid's
         if (lane == 0) { mix[2 * warp] = bv; mix[2 * warp + 1] = __int_as_float(bi); }
         consumer_sync<kLeanWarps>();
@@ -796,9 +843,11 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
                 const int ix = __float_as_int(mix[2 * w + 1]);
                 if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
             }
-            ll_store(p.lm + (size_t)rank * 16, bv, e);
-            ll_store(p.lm + (size_t)rank * 16 + 1, __int_as_float(bi), e);
+            mix[0] = bv;
+            mix[1] = __int_as_float(bi);
         }
+        __syncwarp();
+        if (tid < 2) ll_store(p.lm + (size_t)rank * 16 + tid, mix[tid], e);      // one store instruction for the pair
         mark(17);
     }
     if (tm != nullptr && tid == 0) {

@@ -12,6 +12,7 @@ constexpr int kLeanConsumers = kLeanWarps * 32;
 constexpr int kLeanThreads = kLeanConsumers + 32;    // + the producer warp
 constexpr int kLeanStage = 16 * 1024;                // ring stage
 constexpr int kLeanDirectWords = 4096;
+constexpr int kLeanTraceLen = 256;                 // events per CTA of the diagnostic trace
 
 __host__ __device__ constexpr int lean_slot(int rpc) { return (rpc + 15) / 16 * 16; }
 
@@ -29,6 +30,7 @@ struct LeanParams {
     int pages_per_split;
     int n_stages;                  // ring stages of kLeanStage bytes
     long long* timers;             // [C][kGridTimerSlots] or null
+    long long* trace;              // [C][kLeanTraceLen] (globaltimer << 8 | event) of the last step, or null
     // shared-memory float offsets
     int off_xs, xs_stride, off_xa, off_xb, off_parts, off_mix, off_pacc, off_red, off_layers, off_plan, off_timers, off_bar, off_ring;
 };
