@@ -220,6 +220,8 @@ struct RowsJob {
     int norm_n;                    // > 0: scale by 1 / sqrt(sum(red[0..479]) / norm_n + eps) (the RMS norm, applied late)
     float eps;
     const float* red;
+    float* obuf;                   // finished rows of this phase, by local row (shared memory)
+    int* ocnt;                     // how many of them are finished (shared memory, zero between phases)
 };
 
 template <typename T>
@@ -243,9 +245,9 @@ __device__ __forceinline__ float smem_row_dot(const T* row, int nvec, const floa
 
 template <typename T>
 __device__ __forceinline__ void consume_rows(Ring& r, const RowsJob& j, bool pair, int warp, int lane, float& bv, int& bi, long long* tm) {
+    (void)tm;
     constexpr int EPV = Elem<T>::EPV;
     constexpr int NW = kRingWarps;
-    const long long t_in = tm ? clock64() : 0;
     const int K = j.K, rows = j.rows, nvec = K / EPV;
     const int rpc = max(1, r.stage_bytes / (K * (int)sizeof(T)));
     // the norm of the input (inference.cu:24-50, :83-95): every warp adds up the threads' sums of squares
@@ -257,12 +259,10 @@ __device__ __forceinline__ void consume_rows(Ring& r, const RowsJob& j, bool pai
         rn = rsqrtf(__fdividef(warp_sum(t), (float)j.norm_n) + j.eps);
     }
     int wrow = warp;                       // this warp's next local row
-    if (tm && threadIdx.x == 0) tm[20] += clock64() - t_in;
 #pragma unroll 1
     for (int c0 = 0; c0 < rows; c0 += rpc) {
         const int n = min(rpc, rows - c0);
         const int ia = r.idx;
-        const long long tw = tm ? clock64() : 0;
         r.wait(r.full0 + 8u * r.idx, r.phase, 2);
         r.advance();
         int ib = ia;
@@ -271,10 +271,8 @@ __device__ __forceinline__ void consume_rows(Ring& r, const RowsJob& j, bool pai
             r.wait(r.full0 + 8u * r.idx, r.phase, 2);
             r.advance();
         }
-        if (tm && threadIdx.x == 0) tm[18] += clock64() - tw;      // diagnostic: cycles spent waiting for weight chunks
         const T* A = reinterpret_cast<const T*>(r.stages + (size_t)ia * r.stage_bytes);
         const T* Bm = reinterpret_cast<const T*>(r.stages + (size_t)ib * r.stage_bytes);
-        const long long td = tm ? clock64() : 0;
 #pragma unroll 1
         for (; wrow < c0 + n; wrow += NW) {
             const size_t off = (size_t)(wrow - c0) * K;
@@ -285,6 +283,11 @@ __device__ __forceinline__ void consume_rows(Ring& r, const RowsJob& j, bool pai
             float v = smem_row_dot<T>(A + off, nvec, j.xs, lane);
             float u = 0.f;
             if (pair) u = smem_row_dot<T>(Bm + off, nvec, j.xs, lane);
+            // The finished rows are collected in shared memory and the warp that finishes the CTA's last
+            // one publishes the whole slot with one store instruction per 32 rows: a line that every CTA
+            // polls must change once. (Measured on B200: rows stored one by one by their warps, a few
+            // dozen cycles apart, make an exchange cost 3-4 us instead of 1.2 us.)
+            int last = 0;
             if (lane == 0) {
                 v = (v * sv) * rn;
                 if (j.mode == RJ_SWIGLU) {
@@ -298,20 +301,27 @@ __device__ __forceinline__ void consume_rows(Ring& r, const RowsJob& j, bool pai
                     j.logits[row] = v;
                     if (v > bv || (v == bv && row < bi)) { bv = v; bi = row; }
                 } else {
-                    ll_store(j.dst + wrow, v, j.epoch);
+                    j.obuf[wrow] = v;
+                    __threadfence_block();
+                    last = atomicAdd(j.ocnt, 1) == rows - 1;
+                }
+            }
+            if (j.mode != RJ_LM) {
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence_block();
+#pragma unroll 1
+                    for (int q = lane; q < rows; q += 32) ll_store(j.dst + q, j.obuf[q], j.epoch);
+                    if (lane == 0) *j.ocnt = 0;
                 }
             }
         }
-        const long long te = tm ? clock64() : 0;
-        if (tm && threadIdx.x == 0) tm[19] += te - td;      // diagnostic: cycles in the row loop
         __syncwarp();
         if (lane == 0) {
             mbar_arrive(r.empty0 + 8u * ia);
             if (pair) mbar_arrive(r.empty0 + 8u * ib);
         }
-        if (tm && threadIdx.x == 0) tm[21] += clock64() - te;
     }
-    if (tm && threadIdx.x == 0) tm[22] += clock64() - t_in;
 }
 
 // ---- attention ---------------------------------------------------------------------------------------
@@ -589,7 +599,7 @@ __device__ __forceinline__ void grid_combine(const GridParams& p, const StepLaye
 
 // Gated delta-net step on this CTA's rows of the state (the arithmetic of delta_net_kernel); the
 // rows come out of the ring, the new rows go back to global memory.
-__device__ __forceinline__ void grid_delta_net(const GridParams& p, const StepLayer& L, GridCtx& k, uint32_t e_proj, uint32_t e_out) {
+__device__ __forceinline__ void grid_delta_net(const GridParams& p, const StepLayer& L, GridCtx& k, uint32_t e_proj, uint32_t e_out, float* obuf, int* ocnt) {
     constexpr int NW = kRingWarps;
     const int H = p.heads, dk = p.dk, dv = p.dv, lane = k.lane, warp = k.warp;
     int r0, r1;
@@ -661,7 +671,20 @@ __device__ __forceinline__ void grid_delta_net(const GridParams& p, const StepLa
                 }
             }
             d2 = warp_sum(d2);
-            if (lane == 0) ll_store(dst + wrow, d2, e_out);
+            // the warp that finishes the CTA's last row publishes the slot (see consume_rows)
+            int last = 0;
+            if (lane == 0) {
+                obuf[wrow] = d2;
+                __threadfence_block();
+                last = atomicAdd(ocnt, 1) == rows - 1;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence_block();
+#pragma unroll 1
+                for (int q = lane; q < rows; q += 32) ll_store(dst + q, obuf[q], e_out);
+                if (lane == 0) *ocnt = 0;
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(ring.empty0 + 8u * ia);
@@ -832,6 +855,8 @@ __device__ __forceinline__ void grid_consumer(const StepCtl& c, const GridParams
     RowsJob job;
     job.eps = p.eps;
     job.logits = p.logits;
+    job.ocnt = reinterpret_cast<int*>(smem + p.off_red + 2 * kRingConsumers + 1);
+    job.obuf = smem + p.off_obuf;
 #pragma unroll 1
     for (int itn = 0; itn < n_it; ++itn) {
         const int li = min(itn >> 2, p.n_layers - 1);
@@ -882,7 +907,7 @@ __device__ __forceinline__ void grid_consumer(const StepCtl& c, const GridParams
                 }
             } else {
                 e_in = ++e;
-                grid_delta_net(p, L, k, e_proj, e_in);
+                grid_delta_net(p, L, k, e_proj, e_in, job.obuf, job.ocnt);
                 grid_mark(k, 11);
                 vin = &p.va_dn;
             }
@@ -925,7 +950,6 @@ __device__ __forceinline__ void grid_consumer(const StepCtl& c, const GridParams
         }
         job.rows = r1 - r0; job.K = K; job.r0 = r0; job.xs = xs;
         job.norm_n = gain ? d : 0; job.red = red;
-        if (k.tm && tid == 0) k.tm[23] += clock64() - k.tmark;
         consume_rows<T>(ring, job, pair, warp, lane, bv, bi, k.tm);
         e_in = e;
         if (ph == PH_PROJ) e_proj = e;
@@ -944,10 +968,11 @@ __device__ __forceinline__ void grid_consumer(const StepCtl& c, const GridParams
                 const int ix = __float_as_int(tmp[2 * w + 1]);
                 if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
             }
-            unsigned long long* dst = vec_slot(p.vlm, rank);
-            ll_store(dst, bv, e);
-            ll_store(dst + 1, __int_as_float(bi), e);
+            tmp[0] = bv;
+            tmp[1] = __int_as_float(bi);
         }
+        __syncwarp();
+        if (tid < 2) ll_store(vec_slot(p.vlm, rank) + tid, tmp[tid], e);      // one store instruction for the pair
     }
     if (k.tm != nullptr && tid == 0) {
         k.tm[0] += clock64() - tstart;
@@ -959,15 +984,22 @@ __device__ __forceinline__ void grid_consumer(const StepCtl& c, const GridParams
             float* lm = smem + p.off_parts;          // free by now
             ll_gather_rows(&p.vlm, 0, 2 * C, e, lm, k.tabs, k.dead, k.err);
             consumer_sync();
-            if (tid == 0 && p.do_pick) {
-                float best = lm[0];
-                int at = __float_as_int(lm[1]);
-                for (int r = 1; r < C; ++r) {
+            if (warp == 0 && p.do_pick) {
+                // lowest index among the largest values (the host loop of inference_orchestrator.cu:77-84 keeps the first)
+                float best = -INFINITY;
+                int at = 0x7fffffff;
+                for (int r = lane; r < C; r += 32) {
                     const float v = lm[2 * r];
                     const int ix = __float_as_int(lm[2 * r + 1]);
                     if (v > best || (v == best && ix < at)) { best = v; at = ix; }
                 }
-                advance_seq(c, 0, at);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float vo = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int io = __shfl_xor_sync(0xffffffffu, at, o);
+                    if (vo > best || (vo == best && io < at)) { best = vo; at = io; }
+                }
+                if (lane == 0) advance_seq(c, 0, at);
             }
         } else if (tid == 0) {
             advance_seq(c, 0, -1);
@@ -1034,6 +1066,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) grid_decode_kernel(const __gr
     }
     if (threadIdx.x == 0) {
         *dead = 0;
+        dead[1] = 0;                     // the finished-row counter
         if (k.tm)
             for (int i = 0; i < kGridTimerSlots; ++i) k.tm[i] = 0;
         for (int i = 0; i < p.n_stages; ++i) {

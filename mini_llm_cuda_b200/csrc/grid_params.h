@@ -53,7 +53,7 @@ struct GridParams {
     long long* timers;             // diagnostic: [CTA][kGridTimerSlots] or null
     // shared-memory layout (float offsets), identical in every CTA
     int xs_stride;                 // floats between the two input buffers at off_xs
-    int off_xs, off_xa, off_xb, off_parts, off_gate, off_mix, off_pacc, off_red, off_tabs, off_layers, off_timers, off_plan;
+    int off_xs, off_xa, off_xb, off_parts, off_gate, off_mix, off_pacc, off_red, off_tabs, off_layers, off_timers, off_plan, off_obuf;
     int off_bar;                   // mbarriers: full[nst] then empty[nst] (8 bytes each)
     int off_ring;                  // ring stages (128-byte aligned)
     int n_stages, stage_bytes;

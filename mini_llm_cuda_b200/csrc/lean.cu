@@ -21,7 +21,7 @@ static LeanShapeInfo info_of() {
     const int s_cap = S::C / S::KVH;
     i.parts_floats = kLeanDirectWords > s_cap * S::W ? kLeanDirectWords : s_cap * S::W;
     if (2 * S::C > i.parts_floats) i.parts_floats = 2 * S::C;
-    const int attn_n = S::G * S::HD + 2 * S::HD + kLeanWarps * S::W;
+    const int attn_n = S::G * S::HD + 2 * S::HD + kLeanWarps * S::W + ((S::G * S::W + 31) / 32) * 2 * kLeanWarps;
     const int dn_n = 2 * S::H * S::DK + ((S::RAD + 3) & ~3) + 2 * S::H + 8;
     i.mix_floats = attn_n > dn_n ? attn_n : dn_n;
     if (i.mix_floats < 64) i.mix_floats = 64;

@@ -149,13 +149,24 @@ enum { LM_STORE = 0, LM_RESID = 1, LM_SWIGLU = 2, LM_LOGITS = 3 };
 // (`ocnt` counts them) publishes the whole slot with ONE store instruction: a line that all CTAs
 // poll must change once. (Measured on B200: with the rows of a slot stored one by one by their warps,
 // a few dozen cycles apart, an exchange costs 3-4 us instead of 1.2 us.)
-template <int K, int ROWS, int MODE, bool PAIR>
+template <int K, int ROWS, int MODE, bool PAIR, int ROPE_N = 0, int ROPE_HD = 64>
 __device__ __forceinline__ void lean_rows(Ring& r, int rows, int row0, const float* xs, float rn, unsigned long long* dst, uint32_t e,
                                           const float* resid, const float* pacc, float* logits, float* obuf, int* ocnt, int warp, int lane, float& bv, int& bi,
-                                          long long* tm = nullptr) {
+                                          long long* tm = nullptr, const float* rope_row = nullptr) {
     constexpr int RPS = kLeanStage / (K * 2);        // rows per stage
     static_assert(RPS >= 1, "a row must fit a ring stage");
     constexpr int NCH = (ROWS + RPS - 1) / RPS;
+    // RoPE factors of the row this lane would publish (whichever warp finishes last publishes): asked for now
+    float rope_cs = 1.f, rope_sn = 0.f;
+    if (ROPE_N > 0) {
+        static_assert(ROPE_N == 0 || (ROWS % 2 == 0 && ROWS <= 32), "a RoPE pair must not straddle two CTAs");
+        const int row = row0 + lane;
+        if (lane < rows && row < ROPE_N) {
+            const float2 t = *reinterpret_cast<const float2*>(rope_row + ((row & (ROPE_HD - 1)) & ~1));
+            rope_cs = t.x;
+            rope_sn = t.y;
+        }
+    }
 #pragma unroll 1
     for (int ch = 0; ch < NCH; ++ch) {
         const int c0 = ch * RPS;
@@ -204,8 +215,18 @@ __device__ __forceinline__ void lean_rows(Ring& r, int rows, int row0, const flo
                 if (last) {
                     __threadfence_block();
 #pragma unroll
-                    for (int j0 = 0; j0 < ROWS; j0 += 32)
-                        if (j0 + lane < rows) ll_store(dst + j0 + lane, obuf[j0 + lane], e);
+                    for (int j0 = 0; j0 < ROWS; j0 += 32) {
+                        if (j0 + lane < rows) {
+                            float o = obuf[j0 + lane];
+                            if (ROPE_N > 0) {
+                                // RoPE on adjacent pairs of the q and k rows (inference.cu:113-134), applied where the
+                                // slot is published: both rows of a pair stand in this slot (identity factors elsewhere)
+                                const float other = obuf[(j0 + lane) ^ 1];
+                                o = (lane & 1) ? rope_sn * other + rope_cs * o : rope_cs * o - rope_sn * other;
+                            }
+                            ll_store(dst + j0 + lane, o, e);
+                        }
+                    }
                     if (lane == 0) *ocnt = 0;
                 }
             }
@@ -241,14 +262,15 @@ __device__ __forceinline__ void lean_issue(Ring& r, const unsigned char* a, cons
 }
 
 // Flash-decode of this CTA's item out of shared memory (grid_attention with compile-time shapes,
-// no QK-norm): 16/G warps per query head. Publishes G partials in the item's slot.
+// no QK-norm): 16/G warps per query head. Publishes G partials in the item's slot. The q and k
+// rows arrive with RoPE applied (the QKV phase rotates them when it publishes its slot).
 template <typename S, typename KVT, typename Mark>
 __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLayer& L, const GridPlan& it, Ring& ring, float* mix, int rank,
                                                int pos, uint32_t e_proj, uint32_t e_out, int tid, volatile int* dead, int* err, Mark&& mark) {
     constexpr int HD = S::HD, G = S::G, W = S::W;
     constexpr int EPL = 16 / (int)sizeof(KVT), LPR = HD / EPL, PPI = 32 / LPR;
     constexpr int WPH = kLeanWarps / G;               // warps per query head
-    static_assert(WPH >= 1 && WPH * G == kLeanWarps, "query heads per kv head must divide the warp count");
+    static_assert(WPH >= 1 && WPH * G == kLeanWarps && G * W <= kLeanConsumers, "query heads per kv head must divide the warp count");
     constexpr int PAGE = kKvBlock * HD * (int)sizeof(KVT);
     constexpr int PPC = kLeanStage / PAGE < 32 ? kLeanStage / PAGE : 32;      // pages per stage
     const int lane = tid & 31, warp = tid >> 5;
@@ -258,8 +280,6 @@ __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLa
     float* tk = tq + G * HD;                          // [HD]
     float* tv = tk + HD;                              // [HD]
     float* wpart = tv + HD;                           // [16][W]
-    KVT* kpool = reinterpret_cast<KVT*>(L.kpool);
-    KVT* vpool = reinterpret_cast<KVT*>(L.vpool);
     const int g = warp / WPH, sub = warp - g * WPH;
 
     lean_gather_rows<S::RQA>(p.pj, h0 * HD, G * HD, e_proj, tq, tid, dead, err);
@@ -269,40 +289,6 @@ __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLa
     }
     consumer_sync<kLeanWarps>();
     mark(20);
-    // RoPE on adjacent pairs (inference.cu:113-134): one warp per vector; the new K/V row goes to the pool
-    {
-        const int nvecs = G + (it.cur_here ? 1 : 0);
-        const size_t row_off = it.cur_here ? (((size_t)p.page_table[pos / kKvBlock] * S::KVH + kvh) * kKvBlock + (pos % kKvBlock)) * HD : 0;
-        if (warp < nvecs) {
-            const bool is_k = warp >= G;
-            float* vec = is_k ? tk : tq + warp * HD;
-#pragma unroll
-            for (int i = 0; i < HD / 64; ++i) {
-                const int r = 2 * (lane + 32 * i);
-                const float a = vec[r], cc = vec[r + 1];
-                const float2 cssn = *reinterpret_cast<const float2*>(p.rope + (size_t)pos * HD + r);
-                float ra = cssn.x * a - cssn.y * cc, rc = cssn.y * a + cssn.x * cc;
-                if (is_k) {
-                    Elem<KVT>::put(kpool, row_off + r, ra);
-                    Elem<KVT>::put(kpool, row_off + r + 1, rc);
-                    ra = round_kv<KVT>(ra);
-                    rc = round_kv<KVT>(rc);
-                }
-                vec[r] = ra;
-                vec[r + 1] = rc;
-            }
-        } else if (it.cur_here && warp == nvecs) {
-#pragma unroll
-            for (int i = 0; i < HD / 32; ++i) {
-                const int r = lane + 32 * i;
-                const float v = tv[r];
-                Elem<KVT>::put(vpool, row_off + r, v);
-                tv[r] = round_kv<KVT>(v);
-            }
-        }
-    }
-    consumer_sync<kLeanWarps>();
-    mark(21);
     const float inv_div = rsqrtf((float)HD);          // scores are divided by sqrt(hd), inference.cu:154
     float q[EPL], acc[EPL], m = kNegBig, l = 0.f;
 #pragma unroll
@@ -350,10 +336,30 @@ __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLa
     }
     mark(22);
     if (it.cur_here && sub == 0) {
-        // the current position, from shared memory
+        // the current position: its K/V row, rounded the way the cache stores it; the first warp also appends it to the pool
+        float kc[EPL], vc[EPL];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) {
+            kc[e] = tk[lr * EPL + e];
+            vc[e] = tv[lr * EPL + e];
+        }
+        if (warp == 0 && grp == 0) {
+            KVT* kpool = reinterpret_cast<KVT*>(L.kpool);
+            KVT* vpool = reinterpret_cast<KVT*>(L.vpool);
+            const size_t row_off = (((size_t)p.page_table[pos / kKvBlock] * S::KVH + kvh) * kKvBlock + (pos % kKvBlock)) * HD + lr * EPL;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                Elem<KVT>::put(kpool, row_off + e, kc[e]);
+                Elem<KVT>::put(vpool, row_off + e, vc[e]);
+            }
+        }
         float s = 0.f;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) s = fmaf(q[e], tk[lr * EPL + e], s);
+        for (int e = 0; e < EPL; ++e) {
+            kc[e] = round_kv<KVT>(kc[e]);
+            vc[e] = round_kv<KVT>(vc[e]);
+            s = fmaf(q[e], kc[e], s);
+        }
 #pragma unroll
         for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (grp == 0) {
@@ -361,7 +367,7 @@ __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLa
             const float sc = __expf(m - mn), pe = __expf(s - mn);
             l = l * sc + pe;
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) acc[e] = acc[e] * sc + pe * tv[lr * EPL + e];
+            for (int e = 0; e < EPL; ++e) acc[e] = acc[e] * sc + pe * vc[e];
             m = mn;
         }
     }
@@ -388,22 +394,32 @@ __device__ __forceinline__ void lean_attention(const LeanParams& p, const StepLa
     }
     consumer_sync<kLeanWarps>();
     mark(23);
-    // merge the warps of each head; one thread per element of the item's partials
-    unsigned long long* dst = p.parts + (size_t)rank * lean_slot(G * W);
-#pragma unroll 1
-    for (int idx = tid; idx < G * W; idx += kLeanConsumers) {
-        const int gg = idx / W, e = idx - gg * W;
-        const float* w0 = wpart + gg * WPH * W;
-        float mn = kNegBig;
+    // merge the warps of each head: every publishing warp works out the 16 warps' factors to their heads' common
+    // maxima (its own copy in shared memory), then one thread per element of the item's partials
+    constexpr int NSTORE = (G * W + 31) / 32;          // warps that publish
+    if (warp < NSTORE) {
+        float* wsc = wpart + kLeanWarps * W + warp * 2 * kLeanWarps;      // [16] factors, [16] maxima
+        const int w16 = lane & (kLeanWarps - 1);
+        const float mw = wpart[w16 * W + HD];
+        float mx = mw;
 #pragma unroll
-        for (int w = 0; w < WPH; ++w) mn = fmaxf(mn, w0[w * W + HD]);
-        float val = mn;
-        if (e != HD) {
-            val = 0.f;
-#pragma unroll
-            for (int w = 0; w < WPH; ++w) val = fmaf(w0[w * W + e], __expf(w0[w * W + HD] - mn), val);
+        for (int o = WPH / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if (lane < kLeanWarps) {
+            wsc[lane] = __expf(mw - mx);
+            wsc[kLeanWarps + lane] = mx;
         }
-        ll_store(dst + idx, val, e_out);
+        __syncwarp();
+        const int idx = tid;
+        if (idx < G * W) {
+            const int gg = idx / W, e = idx - gg * W;
+            float val = wsc[kLeanWarps + gg * WPH];
+            if (e != HD) {
+                val = 0.f;
+#pragma unroll
+                for (int w = 0; w < WPH; ++w) val = fmaf(wpart[(gg * WPH + w) * W + e], wsc[gg * WPH + w], val);
+            }
+            ll_store(p.parts + (size_t)rank * lean_slot(G * W) + idx, val, e_out);
+        }
     }
 }
 
@@ -636,6 +652,8 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
     extern __shared__ __align__(128) float lean_smem[];
     float* smem = lean_smem;
     const int rank = (int)blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    unsigned long long g_entry = 0;
+    if (p.trace != nullptr && tid == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_entry));
     const int tok = p.tok_arg >= 0 ? p.tok_arg : c.tok[0];
     const int pos = c.pos[0];
     uint32_t e = *p.epoch;
@@ -694,6 +712,7 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
         tstart = tmark = clock64();
     }
     int n_trace = 0;
+    if (p.trace != nullptr && tid == 0) p.trace[(size_t)rank * kLeanTraceLen + n_trace++] = (long long)((g_entry << 8) | 30ull);
     auto mark = [&](int i) {
         if (tm != nullptr && tid == 0) {
             const long long n = clock64();
@@ -710,20 +729,35 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
     int bi = 0x7fffffff;
     const int xr0 = rank * RX;
 
-    // per-layer embeddings: pacc[l][j] = P_l[xr0 + j] . T_l[tok], one warp per (layer, row), all layers at once
+    // per-layer embeddings: pacc[l][j] = P_l[xr0 + j] . T_l[tok]; 8 lanes per (layer, row), 16-byte loads, all
+    // layers in one round of loads
     if (S::PLE > 0) {
+        static_assert(S::PLE % 8 == 0, "per-layer embedding rows are read as 16-byte vectors");
         const int n = p.n_layers * RX;
+        const int sub = lane & 7;
 #pragma unroll 1
-        for (int i = warp; i < n; i += kLeanWarps) {
-            const int l = i / RX, j = i - l * RX;
-            const bf16_t* Pm = reinterpret_cast<const bf16_t*>(layers[l].pleP) + (size_t)(xr0 + j) * S::PLE;
-            const bf16_t* Tb = reinterpret_cast<const bf16_t*>(layers[l].pleT) + (size_t)tok * S::PLE;
+        for (int i = warp * 4 + (lane >> 3); i < (n + 3) / 4 * 4; i += kLeanWarps * 4) {
             float a = 0.f;
+            if (i < n) {
+                const int l = i / RX, j = i - l * RX;
+                const bf16_t* Pm = reinterpret_cast<const bf16_t*>(layers[l].pleP) + (size_t)(xr0 + j) * S::PLE;
+                const bf16_t* Tb = reinterpret_cast<const bf16_t*>(layers[l].pleT) + (size_t)tok * S::PLE;
 #pragma unroll
-            for (int q = 0; q < (S::PLE + 31) / 32; ++q)
-                if (lane + 32 * q < S::PLE) a = fmaf(__bfloat162float(Pm[lane + 32 * q]), __bfloat162float(Tb[lane + 32 * q]), a);
-            a = warp_sum(a);
-            if (lane == 0) pacc[l * RX + j] = a;
+                for (int q = 0; q < (S::PLE + 63) / 64; ++q) {
+                    const int o = (sub + 8 * q) * 8;
+                    if (S::PLE % 64 == 0 || o < S::PLE) {
+                        float pw[8], tw[8];
+                        Elem<bf16_t>::load_vec(Pm + o, pw);
+                        Elem<bf16_t>::load_vec(Tb + o, tw);
+#pragma unroll
+                        for (int x = 0; x < 8; ++x) a = fmaf(pw[x], tw[x], a);
+                    }
+                }
+            }
+            a += __shfl_xor_sync(0xffffffffu, a, 1);
+            a += __shfl_xor_sync(0xffffffffu, a, 2);
+            a += __shfl_xor_sync(0xffffffffu, a, 4);
+            if (sub == 0 && i < n) pacc[i] = a;
         }
         consumer_sync<kLeanWarps>();
     }
@@ -755,8 +789,9 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
             e_proj = ++e;
             if (attn) {
                 const int r0 = min(rank * S::RQA, S::NQ_A), rows = min(S::RQA, S::NQ_A - r0);
-                lean_rows<D, S::RQA, LM_STORE, false>(ring, rows, r0, xs, rn, p.pj + (size_t)rank * lean_slot(S::RQA), e_proj,
-                                                      nullptr, nullptr, nullptr, obuf, ocnt, warp, lane, bv, bi, tm);
+                lean_rows<D, S::RQA, LM_STORE, false, S::H * S::HD + S::KVH * S::HD, S::HD>(
+                    ring, rows, r0, xs, rn, p.pj + (size_t)rank * lean_slot(S::RQA), e_proj, nullptr, nullptr, nullptr, obuf, ocnt, warp, lane, bv, bi, tm,
+                    p.rope + (size_t)pos * S::HD);
             } else {
                 const int r0 = min(rank * S::RQD, S::NQ_D), rows = min(S::RQD, S::NQ_D - r0);
                 lean_rows<D, S::RQD, LM_STORE, false>(ring, rows, r0, xs, rn, p.pj + (size_t)rank * lean_slot(S::RQD), e_proj,
@@ -858,20 +893,28 @@ __global__ void __launch_bounds__(kLeanThreads, 1) lean_decode_kernel(const __gr
         if (p.with_lm_head) {
             lean_gather_rows<2>(p.lm, 0, 2 * S::C, e, parts, tid, dead, p.err);
             consumer_sync<kLeanWarps>();
-            if (tid == 0 && p.do_pick) {
-                float best = parts[0];
-                int at = __float_as_int(parts[1]);
-                for (int r = 1; r < S::C; ++r) {
+            if (warp == 0 && p.do_pick) {
+                // lowest index among the largest values (the host loop of inference_orchestrator.cu:77-84 keeps the first)
+                float best = -INFINITY;
+                int at = 0x7fffffff;
+                for (int r = lane; r < S::C; r += 32) {
                     const float v = parts[2 * r];
                     const int ix = __float_as_int(parts[2 * r + 1]);
                     if (v > best || (v == best && ix < at)) { best = v; at = ix; }
                 }
-                advance_seq(c, 0, at);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float vo = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int io = __shfl_xor_sync(0xffffffffu, at, o);
+                    if (vo > best || (vo == best && io < at)) { best = vo; at = io; }
+                }
+                if (lane == 0) advance_seq(c, 0, at);
             }
         } else if (tid == 0) {
             advance_seq(c, 0, -1);
         }
         if (tid == 0) *p.epoch = e;
+        mark(31);
     }
 }
 
