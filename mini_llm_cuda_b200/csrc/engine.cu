@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <chrono>
 #include <cstring>
 #include <string>
 #include <type_traits>
@@ -447,6 +448,7 @@ struct mlb_session {
     int tg_topk[2] = {-1, -1}; float tg_temp[2] = {0.f, 0.f};
     int* pinned_out = nullptr;
     int ctl_host_io = 0;                    // while the one-token graph is captured: 1 = ids and error word to the host, 2 = + ids from the host
+    int tok_arg = -1;                       // single-kernel step: the pending id travels with the launch (>= 0), else it is read from `tok`
     float4* flush_buf = nullptr; size_t flush_n = 0;
     int* pinned_tok = nullptr;
     bool use_pdl = true;
@@ -718,11 +720,13 @@ struct Chain {
         }
         if (s->use_lean) {
             LeanParams lp = s->lean;
+            lp.tok_arg = s->tok_arg;
             lp.with_lm_head = kind == CHAIN_PREFILL ? 0 : 1;
             lp.do_pick = kind == CHAIN_GREEDY ? 1 : 0;
             CU(lean_kernel_launch(s->lean_idx, s->m->cfg.kv_dtype, s->lean_smem, s->stream, c, lp));
         } else {
             GridParams gp = s->grid;
+            gp.tok_arg = s->tok_arg;
             gp.with_lm_head = kind == CHAIN_PREFILL ? 0 : 1;
             gp.do_pick = kind == CHAIN_GREEDY ? 1 : 0;
             CU(grid_kernel_launch(s->m->cfg.weight_dtype, s->m->cfg.kv_dtype, s->grid_ctas, s->grid_smem, s->stream, c, gp));
@@ -1846,6 +1850,30 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
         CU(cudaStreamSynchronize(s->stream));
         for (int b = 0; b < B; ++b) out_tokens[b] = s->h_pos[b] < s->max_ctx ? s->pinned_out[b] : -1;
         for (int b = 0; b < B; ++b) s->h_pos[b] = std::min(s->h_pos[b] + 1, s->max_ctx);
+        s->have_logits = true;
+        return check_err_readback(s);
+    }
+    if (n == 1 && !step_ms && B == 1 && (s->use_grid || s->use_lean) && s->h_pos[0] < s->max_ctx) {
+        // The one-token call of the single-kernel step: the pending id travels as a launch argument, the
+        // kernel that advances the sequence writes the picked id and the error word to pinned host memory,
+        // and the host polls that word instead of synchronising the stream (which costs 5-10 us more).
+        if ((rc = ensure_graph(s, kind))) return rc;
+        volatile int* word = s->pinned_out;
+        *word = -2;
+        s->ctl_host_io = 1;
+        s->tok_arg = in_tokens ? in_tokens[0] : -1;
+        rc = chain_run(s, kind, nullptr, nullptr);
+        s->ctl_host_io = 0;
+        s->tok_arg = -1;
+        if (rc) return rc;
+        const auto t0 = std::chrono::steady_clock::now();
+        for (unsigned spins = 0; *word == -2; ++spins) {
+            if ((spins & 0xffffu) == 0xffffu && std::chrono::steady_clock::now() - t0 > std::chrono::seconds(5)) break;
+        }
+        if (*word == -2) CU(cudaStreamSynchronize(s->stream));       // a wait ran out on the device, or the launch failed late
+        if (*word == -2) return fail(MLB_E_CUDA, "the decode step ended without a token");
+        out_tokens[0] = *word;
+        s->h_pos[0] = std::min(s->h_pos[0] + 1, s->max_ctx);
         s->have_logits = true;
         return check_err_readback(s);
     }

@@ -147,8 +147,12 @@ __device__ __forceinline__ void advance_seq(const StepCtl& c, int b, int sampled
         if (oi < c.out_cap) c.out_ring[(size_t)b * c.out_cap + oi] = sampled;
         c.out_idx[b] = oi + 1;
         c.tok[b] = sampled;
+        // the host may be polling host_out: the error word goes first
+        if (c.host_err != nullptr && b == 0) {
+            *c.host_err = *c.dev_err;
+            __threadfence_system();
+        }
         if (c.host_out != nullptr) c.host_out[b] = sampled;
-        if (c.host_err != nullptr && b == 0) *c.host_err = *c.dev_err;
     }
     c.pos[b] = p + 1;
 }
