@@ -187,12 +187,16 @@ void mlb_kv_alloc_free(mlb_kv_alloc* a);
  *   0..positions[b], which must already be in the cache), q [batch][heads*head_dim] fp32
  *   (normalised and rotated), gate (nullable) [batch][heads*head_dim] sigmoid gates,
  *   out [batch][heads*head_dim] fp32. `stream` is a cudaStream_t (NULL = default stream).
+ * num_pages is the number of pages the pools hold. The page table is the caller's, so the kernel
+ * checks it: a sequence whose position needs more than pt_stride pages is skipped, a page id
+ * outside [0, num_pages) is replaced by page 0, and the call returns MLB_E_INVALID (nothing
+ * outside the caller's buffers is read).
  * Allocates its split-combine scratch with cudaMalloc for the call and returns after the
  * stream has finished. */
 int mlb_op_attn_decode(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table,
-                       int pt_stride, const int32_t* positions, const float* q, const float* gate_or_null,
-                       float* out, int batch, int heads, int kv_heads, int head_dim, int splits,
-                       void* stream);
+                       int pt_stride, int num_pages, const int32_t* positions, const float* q,
+                       const float* gate_or_null, float* out, int batch, int heads, int kv_heads, int head_dim,
+                       int splits, void* stream);
 
 /* Stand-alone batched projection on the tensor cores (tcgen05 + TMEM, TMA-fed), DEVICE pointers:
  * the kernel that replaces the reference's cublasGemmEx projections (inference.cu:401-465,
@@ -214,13 +218,19 @@ int mlb_op_gemm_bf16(const void* W, const void* W_up_or_null, const void* X, con
  * `stream` reaches this point. Shapes whose scratch (about batch*heads*splits*(head_dim+2)*4
  * bytes) exceeds mlb_op_attn_decode_static_capacity() are refused with MLB_E_UNSUPPORTED.
  * The FIRST call on each device resolves the array's address (a one-time runtime query): make
- * that call with the device current and before any stream capture starts. All calls on a
- * device share the array, so calls whose kernels could overlap on the GPU (two streams, two
- * threads) race; keep them ordered. */
+ * that call with the device current and before any stream capture starts. With CUDA's lazy
+ * module loading that query is also what places the array in device memory, so make it before
+ * the host claims all the memory (or set CUDA_MODULE_LOADING=EAGER); MLB_E_NOMEM otherwise.
+ * All calls on a device share the array, so calls whose kernels could overlap on the GPU (two
+ * streams, two threads) race; keep them ordered.
+ * Because the call does not wait, a page table that does not fit (see mlb_op_attn_decode) is
+ * reported by mlb_op_attn_decode_static_status, which waits for `stream` and returns
+ * MLB_E_INVALID if the last call on the current device met one (it allocates nothing either). */
 int mlb_op_attn_decode_static(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table,
-                              int pt_stride, const int32_t* positions, const float* q,
+                              int pt_stride, int num_pages, const int32_t* positions, const float* q,
                               const float* gate_or_null, float* out, int batch, int heads, int kv_heads,
                               int head_dim, int splits, void* stream);
+int mlb_op_attn_decode_static_status(void* stream);
 size_t mlb_op_attn_decode_static_capacity(void);
 
 /* No counterpart in the reference. Exercises the bounded wait that every streaming kernel of the

@@ -95,11 +95,12 @@ def lib() -> C.CDLL:
         "mlb_kv_alloc_release": (None, [vp, C.c_int]),
         "mlb_kv_alloc_free": (None, [vp]),
         "mlb_rope_table": (None, [f32p, C.c_int, C.c_int, C.c_float]),
-        "mlb_op_attn_decode": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int,
+        "mlb_op_attn_decode": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int,
                                          C.c_int, C.c_int, vp]),
         "mlb_op_gemm_bf16": (C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]),
-        "mlb_op_attn_decode_static": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int,
+        "mlb_op_attn_decode_static": (C.c_int, [vp, vp, C.c_int, vp, C.c_int, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int,
                                                 C.c_int, C.c_int, C.c_int, vp]),
+        "mlb_op_attn_decode_static_status": (C.c_int, [vp]),
         "mlb_op_attn_decode_static_capacity": (C.c_size_t, []),
         "mlb_last_error": (C.c_char_p, []),
         "mlb_version": (C.c_char_p, []),

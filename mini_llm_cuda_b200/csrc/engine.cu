@@ -846,7 +846,7 @@ struct Chain {
                 a.page_table = s->page_table; a.pt_stride = s->max_pages;
                 a.qbuf = s->qbuf; a.gbuf = L.ng ? s->gbuf : nullptr; a.abuf = s->abuf; a.abuf16 = s->a16;
                 a.part = s->part; a.ticket = s->attn_ticket;
-                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads;
+                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads; a.num_pages = 0; a.err = nullptr;
                 if (rec) {
                     uint64_t kvb = 0, fl = 0;
                     for (int b = 0; b < B; ++b) {
@@ -960,7 +960,7 @@ struct Chain {
                 a.page_table = s->page_table; a.pt_stride = s->max_pages;
                 a.qbuf = s->qbuf; a.gbuf = L.ng ? s->gbuf : nullptr; a.abuf = s->abuf; a.abuf16 = nullptr;
                 a.part = s->part; a.ticket = s->attn_ticket;
-                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads;
+                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads; a.num_pages = 0; a.err = nullptr;
                 if (rec) {
                     uint64_t kvb = 0, fl = 0;
                     for (int b = 0; b < B; ++b) {

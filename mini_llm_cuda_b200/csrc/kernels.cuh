@@ -650,6 +650,12 @@ struct AttnParams {
     int* ticket;            // [B * gridDim.y]
     int heads, kv_heads;
     int hg;                 // CTAs per kv head along grid.y: each takes G of the kv head's query heads
+    // A caller-owned page table (the operator entry points) is not trusted: with num_pages > 0 a sequence
+    // whose position needs more than pt_stride pages is skipped (code 4 in *err) and a page id outside
+    // [0, num_pages) is replaced by page 0 (code 5), so that nothing outside the caller's buffers is read.
+    // The session passes 0: its own allocator filled the table.
+    int num_pages;
+    int* err;
 };
 
 template <typename KVT, int HD, int G>
@@ -675,6 +681,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
     // The grid is sized for the longest context; a split needs at least one page, and the CTAs
     // beyond the page count leave at once (fewer partials for the combine to read). Every CTA of a
     // (sequence, kv head) computes the same S.
+    if (p.num_pages > 0 && npages > p.pt_stride) {   // uniform for all CTAs of this sequence
+        if (threadIdx.x == 0) atomicExch(p.err, 4);
+        return;
+    }
     const int S = min((int)gridDim.x, npages);
     const int SG = (int)gridDim.x;                 // stride of the partial buffer: fixed by the grid, not by S
     if (split >= S) return;
@@ -723,6 +733,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(StepCtl c, AttnParams 
         if (c0 == 0 && (i & 31) == 0) {
             const int ii = i + lane;
             pidx = ii < npw ? pt[pg_begin + warp + NW * ii] : 0;
+            if (p.num_pages > 0 && (unsigned)pidx >= (unsigned)p.num_pages) {
+                atomicExch(p.err, 5);
+                pidx = 0;
+            }
         }
         const int pg = pg_begin + warp + NW * i;
         const int page = __shfl_sync(0xffffffffu, pidx, i & 31);

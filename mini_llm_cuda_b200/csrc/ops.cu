@@ -1,5 +1,6 @@
 // Stand-alone operator entry points over DEVICE pointers: single kernels of the decode step
 // exposed for callers that own their buffers (and for kernel-level parity tests).
+#include <atomic>
 #include <cstdint>
 
 #include "../../include/mlb.h"
@@ -20,31 +21,34 @@ using namespace mlb;
 namespace {
 
 // Scratch of one flash-decode launch, carved from one byte range:
-//   tickets [B*kv_heads] int (zero before the launch) | limits [B] int (never reached) |
-//   partials [B][heads][splits][hd+2] float
+//   error word (zero before the launch) | tickets [B*kv_heads] int (zero before the launch) |
+//   limits [B] int (never reached) | partials [B][heads][splits][hd+2] float
 struct AttnScratch {
+    int* err;
     int* ticket;
     int* limit;
     float* part;
 };
 
+size_t attn_scratch_ints(int B, int kv_heads) { return (1 + (size_t)B * kv_heads + (size_t)B + 63) / 64 * 64; }     // keeps the floats 256-byte aligned
+
 size_t attn_scratch_bytes(int B, int heads, int kv_heads, int hd, int splits) {
-    size_t ints = ((size_t)B * kv_heads + (size_t)B + 63) / 64 * 64;     // keep the floats 256-byte aligned
-    return ints * 4 + (size_t)B * heads * splits * (hd + 2) * 4;
+    return attn_scratch_ints(B, kv_heads) * 4 + (size_t)B * heads * splits * (hd + 2) * 4;
 }
 
 AttnScratch carve(void* base, int B, int kv_heads) {
     AttnScratch s;
-    s.ticket = static_cast<int*>(base);
+    s.err = static_cast<int*>(base);
+    s.ticket = s.err + 1;
     s.limit = s.ticket + (size_t)B * kv_heads;
-    size_t ints = ((size_t)B * kv_heads + (size_t)B + 63) / 64 * 64;
-    s.part = reinterpret_cast<float*>(static_cast<int*>(base) + ints);
+    s.part = reinterpret_cast<float*>(static_cast<int*>(base) + attn_scratch_ints(B, kv_heads));
     return s;
 }
 
-int check_attn_args(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table, const int32_t* positions,
-                    const float* q, float* out, int batch, int heads, int kv_heads, int head_dim, int splits) {
+int check_attn_args(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table, int pt_stride, int num_pages,
+                    const int32_t* positions, const float* q, float* out, int batch, int heads, int kv_heads, int head_dim, int splits) {
     if (!kpool || !vpool || !page_table || !positions || !q || !out) return fail(MLB_E_INVALID, "attention op: null pointer");
+    if (pt_stride < 1 || num_pages < 1) return fail(MLB_E_INVALID, "attention op: pt_stride and num_pages must be >= 1");
     if (kv_dtype != MLB_DT_F32 && kv_dtype != MLB_DT_BF16) return fail(MLB_E_INVALID, "attention op: kv_dtype must be float32 or bfloat16");
     if (batch < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads) return fail(MLB_E_INVALID, "attention op: bad batch / head counts");
     const int g = heads / kv_heads;
@@ -67,11 +71,11 @@ cudaError_t launch_attn(const StepCtl& c, const AttnParams& p, int G, int splits
 }
 
 // Clears the part of the scratch that must start at zero, then launches. No allocation.
-int run_attn(void* scratch, const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table, int pt_stride,
+int run_attn(void* scratch, const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table, int pt_stride, int num_pages,
              const int32_t* positions, const float* q, const float* gate, float* out, int batch, int heads, int kv_heads,
              int head_dim, int splits, cudaStream_t st) {
     AttnScratch sc = carve(scratch, batch, kv_heads);
-    CU(cudaMemsetAsync(sc.ticket, 0, (size_t)batch * kv_heads * 4, st));
+    CU(cudaMemsetAsync(sc.err, 0, (1 + (size_t)batch * kv_heads) * 4, st));          // the error word and the tickets
     CU(cudaMemsetAsync(sc.limit, 0x7f, (size_t)batch * 4, st));          // 0x7f7f7f7f: every sequence takes part
     StepCtl c;
     c.B = batch; c.vocab = 0;
@@ -82,6 +86,7 @@ int run_attn(void* scratch, const void* kpool, const void* vpool, int kv_dtype, 
     p.kpool = kpool; p.vpool = vpool; p.page_table = page_table; p.pt_stride = pt_stride;
     p.qbuf = q; p.gbuf = gate; p.abuf = out; p.abuf16 = nullptr; p.part = sc.part; p.ticket = sc.ticket;
     p.heads = heads; p.kv_heads = kv_heads; p.hg = 1;
+    p.num_pages = num_pages; p.err = sc.err;
     const int G = heads / kv_heads;
     cudaError_t e;
     if (kv_dtype == MLB_DT_F32)
@@ -94,21 +99,30 @@ int run_attn(void* scratch, const void* kpool, const void* vpool, int kv_dtype, 
 
 }  // namespace
 
+static const char* attn_err_text(int code) {
+    return code == 4 ? "a position needs more pages than pt_stride (that sequence was skipped)"
+                     : "the page table names a page outside [0, num_pages) (page 0 was read instead)";
+}
+
 extern "C" int mlb_op_attn_decode(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table, int pt_stride,
-                                  const int32_t* positions, const float* q, const float* gate_or_null, float* out, int batch,
-                                  int heads, int kv_heads, int head_dim, int splits, void* stream) {
-    int rc = check_attn_args(kpool, vpool, kv_dtype, page_table, positions, q, out, batch, heads, kv_heads, head_dim, splits);
+                                  int num_pages, const int32_t* positions, const float* q, const float* gate_or_null, float* out,
+                                  int batch, int heads, int kv_heads, int head_dim, int splits, void* stream) {
+    int rc = check_attn_args(kpool, vpool, kv_dtype, page_table, pt_stride, num_pages, positions, q, out, batch, heads, kv_heads, head_dim,
+                             splits);
     if (rc) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     void* scratch = nullptr;
     cudaError_t e = cudaMalloc(&scratch, attn_scratch_bytes(batch, heads, kv_heads, head_dim, splits));
     if (e != cudaSuccess) return fail(MLB_E_NOMEM, "attention op: cudaMalloc of the scratch failed: %s", cudaGetErrorString(e));
-    rc = run_attn(scratch, kpool, vpool, kv_dtype, page_table, pt_stride, positions, q, gate_or_null, out, batch, heads, kv_heads,
-                  head_dim, splits, st);
+    rc = run_attn(scratch, kpool, vpool, kv_dtype, page_table, pt_stride, num_pages, positions, q, gate_or_null, out, batch, heads,
+                  kv_heads, head_dim, splits, st);
     cudaError_t se = cudaStreamSynchronize(st);       // the scratch must outlive the kernel
+    int code = 0;
+    if (rc == MLB_OK && se == cudaSuccess) se = cudaMemcpy(&code, scratch, 4, cudaMemcpyDeviceToHost);
     cudaFree(scratch);
     if (rc) return rc;
     if (se != cudaSuccess) return fail(MLB_E_CUDA, "attention op failed: %s", cudaGetErrorString(se));
+    if (code) return fail(MLB_E_INVALID, "attention op: %s; the output is invalid", attn_err_text(code));
     return MLB_OK;
 }
 
@@ -186,21 +200,28 @@ constexpr size_t kAttnStaticBytes = 4u << 20;      // 4 MiB per device
 static __device__ __align__(256) unsigned char g_attn_static_scratch[kAttnStaticBytes];
 
 constexpr int kMaxDevices = 64;
-void* g_attn_static_ptr[kMaxDevices] = {nullptr};  // per device, filled on the first call there
+// per device, filled on the first call there. Atomic: two host threads may make their first call at once
+// (both resolve the same address; either store wins).
+std::atomic<void*> g_attn_static_ptr[kMaxDevices];
 
 // One-time set-up for the CURRENT device: resolve the array's device address.
 int attn_static_address(void** out) {
     int dev = -1;
     CU(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return fail(MLB_E_UNSUPPORTED, "static attention op: device index %d not supported", dev);
-    if (g_attn_static_ptr[dev] == nullptr) {
-        void* p = nullptr;
+    void* p = g_attn_static_ptr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        // With CUDA's lazy module loading this query is also what places the array on the device: a host
+        // that has already given all device memory away gets an out-of-memory error here.
         cudaError_t e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+        if (e == cudaErrorMemoryAllocation)
+            return fail(MLB_E_NOMEM, "static attention op: no device memory left for the library's %zu-byte array; make the first call on a "
+                                     "device before the host claims all its memory, or set CUDA_MODULE_LOADING=EAGER", kAttnStaticBytes);
         if (e != cudaSuccess || p == nullptr)
             return fail(MLB_E_CUDA, "static attention op: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
-        g_attn_static_ptr[dev] = p;
+        g_attn_static_ptr[dev].store(p, std::memory_order_release);
     }
-    *out = g_attn_static_ptr[dev];
+    *out = p;
     return MLB_OK;
 }
 
@@ -209,10 +230,11 @@ int attn_static_address(void** out) {
 extern "C" size_t mlb_op_attn_decode_static_capacity(void) { return kAttnStaticBytes; }
 
 extern "C" int mlb_op_attn_decode_static(const void* kpool, const void* vpool, int kv_dtype, const int32_t* page_table,
-                                         int pt_stride, const int32_t* positions, const float* q, const float* gate_or_null,
-                                         float* out, int batch, int heads, int kv_heads, int head_dim, int splits,
-                                         void* stream) {
-    int rc = check_attn_args(kpool, vpool, kv_dtype, page_table, positions, q, out, batch, heads, kv_heads, head_dim, splits);
+                                         int pt_stride, int num_pages, const int32_t* positions, const float* q,
+                                         const float* gate_or_null, float* out, int batch, int heads, int kv_heads, int head_dim,
+                                         int splits, void* stream) {
+    int rc = check_attn_args(kpool, vpool, kv_dtype, page_table, pt_stride, num_pages, positions, q, out, batch, heads, kv_heads, head_dim,
+                             splits);
     if (rc) return rc;
     const size_t need = attn_scratch_bytes(batch, heads, kv_heads, head_dim, splits);
     if (need > kAttnStaticBytes)
@@ -222,10 +244,24 @@ extern "C" int mlb_op_attn_decode_static(const void* kpool, const void* vpool, i
                     batch, heads, splits, head_dim, need, kAttnStaticBytes);
     void* scratch = nullptr;
     if ((rc = attn_static_address(&scratch))) return rc;
-    // The array keeps whatever the previous call left: run_attn clears the arrival counters and
-    // rewrites the limits; the partials are fully overwritten before they are read.
-    return run_attn(scratch, kpool, vpool, kv_dtype, page_table, pt_stride, positions, q, gate_or_null, out, batch, heads,
+    // The array keeps whatever the previous call left: run_attn clears the error word and the arrival
+    // counters and rewrites the limits; the partials are fully overwritten before they are read.
+    return run_attn(scratch, kpool, vpool, kv_dtype, page_table, pt_stride, num_pages, positions, q, gate_or_null, out, batch, heads,
                     kv_heads, head_dim, splits, static_cast<cudaStream_t>(stream));
+}
+
+// The call above returns before its kernel has run, so a page table that does not fit (see AttnParams)
+// cannot be reported by it. This one waits for `stream` and reads the error word of the last call on the
+// current device (a 4-byte copy out of the array: still no allocation).
+extern "C" int mlb_op_attn_decode_static_status(void* stream) {
+    void* scratch = nullptr;
+    int rc = attn_static_address(&scratch);
+    if (rc) return rc;
+    CU(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    int code = 0;
+    CU(cudaMemcpy(&code, scratch, 4, cudaMemcpyDeviceToHost));
+    if (code) return fail(MLB_E_INVALID, "static attention op: %s; the output of that call is invalid", attn_err_text(code));
+    return MLB_OK;
 }
 
 // ---- bounded-wait probe ------------------------------------------------------------------------

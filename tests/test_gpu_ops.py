@@ -47,7 +47,7 @@ def make_attention_case(torch, batch, heads, kv_heads, hd, ctx_list, dtype, seed
     dev = "cuda:0"
     pos = torch.tensor([c - 1 for c in ctx_list], dtype=torch.int32)
     return dict(kpool=kpool.to(dev), vpool=vpool.to(dev), table=table.to(dev), pos=pos.to(dev), q=q.to(dev),
-                gate=gate.to(dev) if with_gate else None, want=want, pt_stride=pt_stride)
+                gate=gate.to(dev) if with_gate else None, want=want, pt_stride=pt_stride, n_pages=n_pages)
 
 
 def call_attention(api, torch, fn_name, case, batch, heads, kv_heads, hd, splits, dtype):
@@ -55,7 +55,7 @@ def call_attention(api, torch, fn_name, case, batch, heads, kv_heads, hd, splits
     kv_dt = api.DT_BF16 if dtype == torch.bfloat16 else api.DT_F32
     fn = getattr(api.lib(), fn_name)
     rc = fn(case["kpool"].data_ptr(), case["vpool"].data_ptr(), kv_dt, case["table"].data_ptr(), case["pt_stride"],
-            case["pos"].data_ptr(), case["q"].data_ptr(), case["gate"].data_ptr() if case["gate"] is not None else None,
+            case["n_pages"], case["pos"].data_ptr(), case["q"].data_ptr(), case["gate"].data_ptr() if case["gate"] is not None else None,
             out.data_ptr(), batch, heads, kv_heads, hd, splits, None)
     torch.cuda.synchronize()
     return rc, out
@@ -86,16 +86,58 @@ def test_attention_op_rejects_bad_arguments(api):
     args = lambda **kw: None
     out = torch.zeros(1, 256, device="cuda:0")
     base = [case["kpool"].data_ptr(), case["vpool"].data_ptr(), api.DT_F32, case["table"].data_ptr(), case["pt_stride"],
-            case["pos"].data_ptr(), case["q"].data_ptr(), None, out.data_ptr(), 1, 4, 4, 64, 4, None]
-    bad = list(base); bad[12] = 96
+            case["n_pages"], case["pos"].data_ptr(), case["q"].data_ptr(), None, out.data_ptr(), 1, 4, 4, 64, 4, None]
+    bad = list(base); bad[13] = 96
     assert L.mlb_op_attn_decode(*bad) == api.MLB_E_UNSUPPORTED
-    bad = list(base); bad[11] = 3
+    bad = list(base); bad[12] = 3
     assert L.mlb_op_attn_decode(*bad) == api.MLB_E_INVALID
-    bad = list(base); bad[6] = None
+    bad = list(base); bad[7] = None
     assert L.mlb_op_attn_decode(*bad) == api.MLB_E_INVALID
     bad = list(base); bad[2] = api.DT_FP8
     assert L.mlb_op_attn_decode(*bad) == api.MLB_E_INVALID
+    bad = list(base); bad[4] = 0
+    assert L.mlb_op_attn_decode(*bad) == api.MLB_E_INVALID
     assert L.mlb_op_attn_decode(*base) == 0
+
+
+def test_attention_op_skips_what_the_page_table_does_not_cover(api):
+    """A caller-owned page table is checked on the device. A position that needs more pages than
+    pt_stride: that sequence is skipped (its output row keeps what it held), the others are
+    computed. A page id outside the pool: page 0 is read instead. Either way the call returns
+    MLB_E_INVALID and nothing outside the caller's buffers is touched."""
+    import torch
+    L = api.lib()
+    B, H, hd = 3, 4, 64
+    case = make_attention_case(torch, B, H, H, hd, [40, 20, 33], torch.float32, 7, False)
+    # (a) sequence 1 claims a position far beyond its page-table row
+    pos = case["pos"].clone()
+    pos[1] = 16 * case["pt_stride"] + 5
+    out = torch.full((B, H * hd), 123.0, device="cuda:0")
+    rc = L.mlb_op_attn_decode(case["kpool"].data_ptr(), case["vpool"].data_ptr(), api.DT_F32, case["table"].data_ptr(),
+                              case["pt_stride"], case["n_pages"], pos.data_ptr(), case["q"].data_ptr(), None, out.data_ptr(),
+                              B, H, H, hd, 2, None)
+    assert rc == api.MLB_E_INVALID and b"more pages than pt_stride" in L.mlb_last_error()
+    assert (out[1] == 123.0).all()                                      # skipped, not dereferenced
+    for b in (0, 2):
+        assert (out[b].cpu().double() - case["want"][b]).abs().max().item() < 2e-5
+    # (b) a stale page id in the table
+    table = case["table"].clone()
+    table[2, 1] = case["n_pages"] + 1000
+    rc = L.mlb_op_attn_decode(case["kpool"].data_ptr(), case["vpool"].data_ptr(), api.DT_F32, table.data_ptr(),
+                              case["pt_stride"], case["n_pages"], case["pos"].data_ptr(), case["q"].data_ptr(), None,
+                              out.data_ptr(), B, H, H, hd, 2, None)
+    assert rc == api.MLB_E_INVALID and b"outside [0, num_pages)" in L.mlb_last_error()
+    # the allocation-free entry point reports the same through its status call
+    rc = L.mlb_op_attn_decode_static(case["kpool"].data_ptr(), case["vpool"].data_ptr(), api.DT_F32, table.data_ptr(),
+                                     case["pt_stride"], case["n_pages"], case["pos"].data_ptr(), case["q"].data_ptr(), None,
+                                     out.data_ptr(), B, H, H, hd, 2, None)
+    assert rc == 0
+    assert L.mlb_op_attn_decode_static_status(None) == api.MLB_E_INVALID
+    rc = L.mlb_op_attn_decode_static(case["kpool"].data_ptr(), case["vpool"].data_ptr(), api.DT_F32, case["table"].data_ptr(),
+                                     case["pt_stride"], case["n_pages"], case["pos"].data_ptr(), case["q"].data_ptr(), None,
+                                     out.data_ptr(), B, H, H, hd, 2, None)
+    assert rc == 0 and L.mlb_op_attn_decode_static_status(None) == 0
+    assert (out.cpu().double() - case["want"]).abs().max().item() < 2e-5
 
 
 @pytest.mark.parametrize("N,K,batch", [(128, 64, 16), (256, 512, 32), (1408, 512, 256), (512, 1408, 100), (1552, 512, 20),

@@ -36,6 +36,19 @@ def test_static_scratch_attention_matches_allocating_entry_point_twice(api):
         # same kernel, same inputs: equal to the tolerance the operator test uses
         assert (got.double() - want.double()).abs().max().item() < 2e-5
         assert (got.cpu().double() - case["want"]).abs().max().item() < 2e-5
+        assert api.lib().mlb_op_attn_decode_static_status(None) == 0
+    # the call allocates nothing: free device memory is the same before and after it (the first call above
+    # placed the library's array)
+    out = torch.empty(B, H * hd, device="cuda:0")
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    rc_s = api.lib().mlb_op_attn_decode_static(
+        case["kpool"].data_ptr(), case["vpool"].data_ptr(), api.DT_BF16 if dt == torch.bfloat16 else api.DT_F32,
+        case["table"].data_ptr(), case["pt_stride"], case["n_pages"], case["pos"].data_ptr(), case["q"].data_ptr(),
+        case["gate"].data_ptr(), out.data_ptr(), B, H, Hkv, hd, S, None)
+    torch.cuda.synchronize()
+    assert rc_s == 0 and torch.cuda.mem_get_info()[0] == free_before
+    assert torch.equal(out, got)
     # same shape again right away: stale partials / counters from the call before must not leak
     rc_s, again = call_attention(api, torch, "mlb_op_attn_decode_static", case, B, H, Hkv, hd, S, dt)
     assert rc_s == 0 and torch.equal(again, got)
