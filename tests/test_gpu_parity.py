@@ -215,6 +215,70 @@ def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name,
     model.close()
 
 
+BASELINE_BATCHED = {
+    # the batched configuration: the 1-GPU latency model at 256 sequences, temperature 1.0 / top-k 50
+    "cfg2": (dict(dim=512, layers=8, heads=8, head_dim=64, ffn_dim=1408, vocab=8192, max_context=128, rms_eps=1e-5, ple_dim=64,
+                  layer_types=periodic_layer_types(8, 4), weight_dtype="bfloat16", kv_dtype="bfloat16"), 256, True),
+    # the gated-delta-net stress widths (d=1024, 8 heads, key/value dim 128, ffn 2816) at batch 64, 3 of its 12 layers
+    "cfg3": (dict(dim=1024, layers=3, heads=8, head_dim=128, ffn_dim=2816, vocab=2048, max_context=128, rms_eps=1e-5,
+                  layer_types=periodic_layer_types(3, 1), weight_dtype="bfloat16", kv_dtype="bfloat16"), 64, False),
+    # the quantised larger model's widths (d=2048, 16 query / 4 kv heads of 128, ffn 5632, PLE 128, FP8) at batch 64, 2 layers
+    "cfg4": (dict(dim=2048, layers=2, heads=16, kv_heads=4, head_dim=128, ffn_dim=5632, vocab=4096, max_context=128, rms_eps=1e-5,
+                  ple_dim=128, layer_types=periodic_layer_types(2, 2), weight_dtype="float8_e4m3", kv_dtype="bfloat16"), 64, False),
+}
+
+
+@pytest.mark.parametrize("name", list(BASELINE_BATCHED))
+def test_baseline_batched_shapes_match_oracle(api, tmp_path, name):
+    """The batched BASELINE configurations at their real batch and widths on the tensor-core step (the tile
+    chooser picks other tiles at 64 / 256 sequences than at the small batches of the other tests). A few of
+    the sequences are followed by the oracle, teacher-forced on its tokens: logits within 2e-2 at every
+    step, greedy picks equal wherever the oracle's margin exceeds that bound; with sampling (the 256-sequence
+    configuration) every draw equals the oracle's top-k / Philox draw on the device's own logits."""
+    kw, batch, sampled = BASELINE_BATCHED[name]
+    spec = ModelSpec(**kw)
+    path = write_model(tmp_path, spec, seed=21, random_gains=(name != "cfg4"))
+    oracle = load_oracle(path)
+    lens = [3 + (11 * i) % 29 for i in range(batch)]
+    prompts = random_prompts(spec.vocab, lens, seed=22)
+    watch = [0, batch // 3, batch - 1]
+    steps = 6
+    rolls = {b: oracle_rollout(oracle, prompts[b], steps) for b in watch}
+    seeds = [1000 + b for b in range(batch)]
+    samp = {"mode": "top_k", "top_k": 50, "temperature": 1.0, "seeds": seeds} if sampled else None
+    model = api.Model(path)
+    sess = api.Session(model, batch)
+    sess.prefill(prompts)
+    assert sess.launches_per_step() > 1          # the tensor-core chain, not a batch-1 kernel
+    worst, checked, close_calls = 0.0, 0, 0
+    prev = None
+    for i in range(steps):
+        forced = None
+        if i > 0:
+            forced = [int(rolls[b][0][i - 1]) if b in rolls else int(prev[b]) for b in range(batch)]
+        picks = sess.decode_step(samp, in_tokens=forced)
+        lg = sess.logits()
+        for b in watch:
+            want = rolls[b][1][i]
+            worst = max(worst, logits_error(lg[b], want))
+            if sampled:
+                draw, margin = sample_top_k(lg[b], 1.0, 50, seeds[b], lens[b] + i, return_margin=True)
+                if int(picks[b]) != draw:
+                    assert margin < 1e-5, (i, b, margin)
+                    close_calls += 1
+                checked += 1
+            else:
+                top2 = np.sort(want)[-2:]
+                if (top2[1] - top2[0]) > 2 * TOL_LOWP * np.abs(want).max():
+                    assert int(picks[b]) == int(rolls[b][0][i]), (i, b)
+                    checked += 1
+        prev = picks
+    assert worst < TOL_LOWP, worst
+    assert checked >= len(watch) and close_calls <= 1
+    sess.close()
+    model.close()
+
+
 @pytest.mark.parametrize("name,lens,decode_path", [("bf16", [131], "chain"), ("bf16", [1, 2, 130, 60, 201, 17], "auto"),
                                                    ("bf16_w_f32_kv", [300, 5, 129], "chain"), ("bf16", [257], "grid"),
                                                    ("fp8", [280, 3, 70], "auto")])
