@@ -470,10 +470,12 @@ struct mlb_session {
     mlb::LeanParams lean;
     // tensor-core projections (bf16 weights, batch >= 16)
     bool use_tc = false;
-    int tc_nb = 0, tc_stages = 0, tc_stages_swiglu = 0;
+    int tc_nb = 0, tc_nb_resid = 16, tc_stages = 0, tc_stages_swiglu = 0;
     mlb::bf16_t *xn16 = nullptr, *a16 = nullptr, *h16 = nullptr;
     float* rawq = nullptr;
-    struct alignas(64) TcLayerMaps { CUtensorMap qkv, o, w1a, w1b, w2; };
+    struct alignas(64) TcLayerMaps { CUtensorMap qkv, o, w1a, w1b, w2, pleP, pleT; };   // pleP / pleT: [d][ple] projection, gathered [B][ple] rows
+    float* tc_ssq = nullptr;                 // [B][ceil(d / 128)] partial sums of squares of the residual stream
+    mlb::bf16_t* tple16 = nullptr;           // [layers][B][ple] per-layer embedding rows of the step's tokens
     std::vector<TcLayerMaps> tc_maps;
     // activation operand maps per batch tile 16, 32, 64, 128, 256 (index log2(Nb/16))
     struct alignas(64) TcGlobalMaps { CUtensorMap E, xn[5], a_attn[5], a_dn[5], h[5]; } tc_g;
@@ -571,6 +573,28 @@ static cudaError_t launch_chain(bool pdl, void (*kernel)(KArgs...), dim3 grid, d
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+
+// Batch tile (UMMA N) of one GEMM: the largest of 256..16 that still yields enough CTAs to
+// spread the weight stream and the MMAs over the SMs (the projections of a decode step have few
+// 128-row tiles; the activations are re-read per batch tile from L2, which is cheap).
+// One CTA per SM fits (the ring takes ~200 KB), so a grid runs in ceil(CTAs / SMs) waves and a CTA's
+// time follows the bytes it streams: `na` weight tiles of 128 rows plus the batch tile, per k-block.
+// Pick the tile with the least waves x bytes: 176 CTAs of 16 columns are two waves, 88 CTAs of 32
+// columns one.
+static int tc_pick_nb(const mlb_session* s, int N, int na) {
+    const int tiles_m = (N + kTcM - 1) / kTcM;
+    const int cap = std::min(256, (s->B + 15) / 16 * 16);
+    int best = 16;
+    long best_cost = -1;
+    for (int nb = 16; nb <= cap; nb <<= 1) {
+        const long ctas = (long)tiles_m * ((s->B + nb - 1) / nb);
+        const long waves = (ctas + s->sm_count - 1) / s->sm_count;
+        const long cost = waves * (na * kTcM + nb);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = nb; }
+    }
+    return best;
+}
+static int nb_index(int nb) { return nb == 16 ? 0 : nb == 32 ? 1 : nb == 64 ? 2 : nb == 128 ? 3 : 4; }
 
 template <typename T, typename T2, typename KVT>
 struct Chain {
@@ -745,101 +769,69 @@ struct Chain {
         return MLB_OK;
     }
 
-    // Batch tile (UMMA N) of one GEMM: the largest of 256..16 that still yields enough CTAs to
-    // spread the weight stream and the MMAs over the SMs (the projections of a decode step have few
-    // 128-row tiles; the activations are re-read per batch tile from L2, which is cheap).
-    // One CTA per SM fits (the ring takes ~200 KB), so a grid runs in ceil(CTAs / SMs) waves and a CTA's
-    // time follows the bytes it streams: `na` weight tiles of 128 rows plus the batch tile, per k-block.
-    // Pick the tile with the least waves x bytes: 176 CTAs of 16 columns are two waves, 88 CTAs of 32
-    // columns one.
-    static int tc_pick_nb(const mlb_session* s, int N, int na) {
-        const int tiles_m = (N + kTcM - 1) / kTcM;
-        const int cap = std::min(256, (s->B + 15) / 16 * 16);
-        int best = 16;
-        long best_cost = -1;
-        for (int nb = 16; nb <= cap; nb <<= 1) {
-            const long ctas = (long)tiles_m * ((s->B + nb - 1) / nb);
-            const long waves = (ctas + s->sm_count - 1) / s->sm_count;
-            const long cost = waves * (na * kTcM + nb);
-            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = nb; }
-        }
-        return best;
-    }
-    static int nb_index(int nb) { return nb == 16 ? 0 : nb == 32 ? 1 : nb == 64 ? 2 : nb == 128 ? 3 : 4; }
-
+    // One tensor-core projection. `normed`: the activation operand is bf16(x * gain) and the accumulator
+    // columns are scaled by 1 / rms(x) from the partial sums its producer left. `next_gain` (RESID): also
+    // write the operand and the partial sums for the next norm. `ext`: the per-layer embedding pair whose
+    // k-blocks follow the main operands' (RESID of the down projection).
     template <int MODE>
-    static int gemm_tc(mlb_session* s, const CUtensorMap& A, const CUtensorMap& A2, const CUtensorMap* Bmaps, int N, int K, float* y,
-                       const float* resid, bf16_t* h16, Recorder* rec, const char* name) {
+    static int gemm_tc(mlb_session* s, const StepCtl& c, const CUtensorMap& A, const CUtensorMap& A2, const CUtensorMap* Bmaps, int N, int K,
+                       float* y, bf16_t* h16, bool normed, const float* next_gain, const mlb_session::TcLayerMaps* ext,
+                       const QkvPostParams* q, Recorder* rec, const char* name) {
         GemmTcParams p;
-        const int nb = tc_pick_nb(s, N, MODE == TC_SWIGLU ? 2 : 1);
+        const int nb = MODE == TC_RESID ? s->tc_nb_resid : tc_pick_nb(s, N, MODE == TC_SWIGLU ? 2 : 1);
         p.N = N; p.K = K; p.B = s->B; p.Nb = nb;
+        const int ple = s->m->cfg.ple_dim;
+        p.nkb_x = ext ? (ple + kTcKB - 1) / kTcKB : 0;
         const size_t stage_bytes = (size_t)(MODE == TC_SWIGLU ? 2 : 1) * kTcM * 128 + (size_t)nb * 128;
         p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, (200 * 1024) / stage_bytes));
         uint32_t cols = 32;
         while (cols < (uint32_t)(MODE == TC_SWIGLU ? 2 : 1) * (uint32_t)nb) cols <<= 1;
         p.tmem_cols = cols;
-        p.y = y; p.resid = resid; p.h16 = h16; p.err = s->dev_err;
-        const size_t smem = (size_t)p.stages * stage_bytes + (2 * (size_t)p.stages + 1) * 8 + 16 + 1024;
+        p.y = y; p.resid = MODE == TC_RESID ? y : nullptr; p.h16 = h16; p.err = s->dev_err;
+        p.ssq_in = normed ? s->tc_ssq : nullptr; p.ssq_parts = (s->m->cfg.dim + kTcM - 1) / kTcM; p.eps = s->m->cfg.rms_eps;
+        p.xg16 = next_gain ? s->xn16 : nullptr; p.gain_next = next_gain; p.ssq_out = next_gain ? s->tc_ssq : nullptr;
+        const size_t smem = (size_t)p.stages * stage_bytes + (2 * (size_t)p.stages + 1) * 8 + 16 + kTcEpiFloats * 4 + 1024;
         dim3 grid((N + kTcM - 1) / kTcM, (s->B + nb - 1) / nb);
         int rc;
-        if (rec && (rc = rec->begin(name, (uint64_t)N * K * 2 * (MODE == TC_SWIGLU ? 2 : 1) + (uint64_t)s->B * K * 2 + (uint64_t)s->B * N * 4,
-                                    2ull * N * K * s->B * (MODE == TC_SWIGLU ? 2 : 1))))
+        if (rec && (rc = rec->begin(name, (uint64_t)N * (K + (ext ? ple : 0)) * 2 * (MODE == TC_SWIGLU ? 2 : 1) + (uint64_t)s->B * K * 2 + (uint64_t)s->B * N * 4,
+                                    2ull * N * (K + (ext ? ple : 0)) * s->B * (MODE == TC_SWIGLU ? 2 : 1))))
             return rc;
-        cudaError_t e = launch_chain(s->use_pdl, gemm_tc_kernel<MODE>, grid, dim3(128), smem, s->stream, A, A2, Bmaps[nb_index(nb)], p);
+        QkvPostParams q0{};
+        const CUtensorMap& Ax = ext ? ext->pleP : A;
+        const CUtensorMap& Bx = ext ? ext->pleT : A;
+        cudaError_t e = launch_chain(s->use_pdl, gemm_tc_kernel<MODE, KVT>, grid, dim3(128), smem, s->stream, A, A2, Bmaps[nb_index(nb)], Ax, Bx, p, c,
+                                     q ? *q : q0);
         if (e != cudaSuccess) return fail(MLB_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
         if (rec) return rec->end();
         return MLB_OK;
     }
 
-    // Large-batch step: projections as tcgen05 GEMMs on bf16 operands, small kernels in between.
+    // Large-batch step: projections as tcgen05 GEMMs on bf16 operands with the element-wise work in their
+    // epilogues; per layer: projection, attention / delta-net, o-projection, gate-up, down.
     static int run_tc(mlb_session* s, int kind, const StepCtl& c, Recorder* rec, int* n_launches) {
         if (!std::is_same<T, bf16_t>::value) return fail(MLB_E_UNSUPPORTED, "tensor-core projections need bf16 weights");
         const mlb_model* m = s->m;
         const mlb_config& cfg = m->cfg;
         const int d = cfg.dim, F = cfg.ffn_dim, B = s->B, ple = cfg.ple_dim;
         int launches = 0, rc;
-        auto prep = [&](const float* gain, const void* pleT, const void* pleP, int p_dim) -> int {
-            int r2;
-            if (p_dim > 0 && (size_t)d * p_dim >= 131072) {
-                // large per-layer embedding: its own launch over many CTAs, then the plain norm
-                if (rec && (r2 = rec->begin("ple_add", (uint64_t)B * d * 8 + (uint64_t)p_dim * d * 2, 0))) return r2;
-                cudaError_t e0 = launch_chain(s->use_pdl, ple_add_kernel<T2>, dim3(B, (d + 63) / 64), dim3(64), (size_t)p_dim * 4, s->stream, c,
-                                              s->x, d, static_cast<const T2*>(pleT), static_cast<const T2*>(pleP), p_dim);
-                if (e0 != cudaSuccess) return fail(MLB_E_CUDA, "per-layer embedding launch failed: %s", cudaGetErrorString(e0));
-                if (rec && (r2 = rec->end())) return r2;
-                ++launches;
-                pleT = nullptr; pleP = nullptr; p_dim = 0;
-            }
-            if (rec && (r2 = rec->begin("prep_norm_bf16", (uint64_t)B * d * 6 + (uint64_t)p_dim * d * 2, 0))) return r2;
-            cudaError_t e = launch_chain(s->use_pdl, prep_bf16_kernel<T2>, dim3(B), dim3(256), (size_t)(d + p_dim) * 4, s->stream, c, s->x,
-                                         d, gain, cfg.rms_eps, static_cast<const T2*>(pleT), static_cast<const T2*>(pleP), p_dim, s->xn16);
-            if (e != cudaSuccess) return fail(MLB_E_CUDA, "prep launch failed: %s", cudaGetErrorString(e));
-            if (rec && (r2 = rec->end())) return r2;
-            ++launches;
-            return MLB_OK;
-        };
-        if (rec && (rc = rec->begin("embed_ple_gather", (uint64_t)B * d * 6, 0))) return rc;
-        CU(launch_chain(s->use_pdl, embed_kernel<T, T2>, embed_grid(B, d, ple), embed_block(B, d, ple), (size_t)ple * 4, s->stream, c, static_cast<const T*>(m->E),
-                        static_cast<const float*>(m->Es), d, static_cast<const T2*>(m->layers[0].pleT),
-                        static_cast<const T2*>(m->layers[0].pleP), ple, s->x));
+        if (rec && (rc = rec->begin("embed_ple_gather_norm", (uint64_t)B * d * 8 + (uint64_t)B * ple * 2 * cfg.layers, 0))) return rc;
+        CU(launch_chain(s->use_pdl, embed_tc_kernel, dim3(B, (d + kTcM - 1) / kTcM), dim3(128), (size_t)ple * 4, s->stream, c,
+                        static_cast<const bf16_t*>(m->E), d, static_cast<const StepLayer*>(s->step_layers), cfg.layers, ple,
+                        static_cast<const float*>(m->layers[0].g1), s->x, s->xn16, s->tc_ssq, s->tple16));
         if (rec && (rc = rec->end())) return rc;
         ++launches;
         for (int i = 0; i < cfg.layers; ++i) {
             const DevLayer& L = m->layers[i];
             const mlb_session::TcLayerMaps& M = s->tc_maps[i];
-            const bool ple_here = ple > 0 && i > 0;
-            if ((rc = prep(L.g1, ple_here ? L.pleT : nullptr, ple_here ? L.pleP : nullptr, ple_here ? ple : 0))) return rc;
             if (L.type == MLB_LAYER_ATTENTION) {
-                if ((rc = gemm_tc<TC_RAW>(s, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, s->rawq, nullptr, nullptr, rec, "qkv_gemm_tcgen05"))) return rc;
-                ++launches;
                 QkvPostParams q;
-                q.raw = s->rawq; q.n_qkv = L.n_qkv; q.nq = L.nq; q.nk = L.nk; q.nv = L.nv; q.ng = L.ng; q.hd = cfg.head_dim;
+                q.nq = L.nq; q.nk = L.nk; q.nv = L.nv; q.ng = L.ng; q.hd = cfg.head_dim;
                 q.kv_heads = cfg.kv_heads; q.qk_norm = cfg.qk_norm; q.eps = cfg.rms_eps; q.gq = L.gq; q.gk = L.gk; q.rope = m->rope;
                 q.kpool = s->kpool[i]; q.vpool = s->vpool[i]; q.page_table = s->page_table; q.pt_stride = s->max_pages;
                 q.qbuf = s->qbuf; q.gbuf = s->gbuf;
-                if (rec && (rc = rec->begin("qkv_post_norm_rope_kvappend", (uint64_t)B * L.n_qkv * 8, 0))) return rc;
-                CU(launch_chain(s->use_pdl, qkv_post_kernel<KVT>, dim3(L.n_qkv / cfg.head_dim, B), dim3(cfg.head_dim / 2), 0, s->stream, c, q));
-                if (rec && (rc = rec->end())) return rc;
+                if ((rc = gemm_tc<TC_QKV>(s, c, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, nullptr, nullptr, true, nullptr, nullptr, &q, rec,
+                                          "qkv_gemm_tcgen05_norm_rope_kvappend")))
+                    return rc;
                 ++launches;
                 AttnParams a;
                 a.kpool = s->kpool[i]; a.vpool = s->vpool[i];
@@ -862,7 +854,9 @@ struct Chain {
                 if (rec && (rc = rec->end())) return rc;
                 ++launches;
             } else {
-                if ((rc = gemm_tc<TC_RAW>(s, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, s->raw, nullptr, nullptr, rec, "deltanet_proj_gemm_tcgen05"))) return rc;
+                if ((rc = gemm_tc<TC_RAW>(s, c, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, s->raw, nullptr, true, nullptr, nullptr, nullptr, rec,
+                                          "deltanet_proj_gemm_tcgen05")))
+                    return rc;
                 ++launches;
                 const int dk = cfg.dn_key_dim, dv = cfg.dn_value_dim, H = cfg.heads;
                 if (rec && (rc = rec->begin("deltanet_state_update", (uint64_t)B * 2ull * H * dk * dv * 4, (uint64_t)B * 6ull * H * dk * dv))) return rc;
@@ -886,12 +880,19 @@ struct Chain {
                 ++launches;
             }
             const CUtensorMap* amap = L.type == MLB_LAYER_ATTENTION ? s->tc_g.a_attn : s->tc_g.a_dn;
-            if ((rc = gemm_tc<TC_RESID>(s, M.o, M.o, amap, d, L.o_in, s->x, s->x, nullptr, rec, "oproj_gemm_tcgen05_residual"))) return rc;
+            if ((rc = gemm_tc<TC_RESID>(s, c, M.o, M.o, amap, d, L.o_in, s->x, nullptr, false, L.g2, nullptr, nullptr, rec,
+                                        "oproj_gemm_tcgen05_residual_norm")))
+                return rc;
             ++launches;
-            if ((rc = prep(L.g2, nullptr, nullptr, 0))) return rc;
-            if ((rc = gemm_tc<TC_SWIGLU>(s, M.w1a, M.w1b, s->tc_g.xn, F, d, nullptr, nullptr, s->h16, rec, "ffn_gateup_gemm_tcgen05_swiglu"))) return rc;
+            if ((rc = gemm_tc<TC_SWIGLU>(s, c, M.w1a, M.w1b, s->tc_g.xn, F, d, nullptr, s->h16, true, nullptr, nullptr, nullptr, rec,
+                                         "ffn_gateup_gemm_tcgen05_swiglu")))
+                return rc;
             ++launches;
-            if ((rc = gemm_tc<TC_RESID>(s, M.w2, M.w2, s->tc_g.h, d, F, s->x, s->x, nullptr, rec, "ffn_down_gemm_tcgen05_residual"))) return rc;
+            const bool last = i + 1 == cfg.layers;
+            const float* g_next = last ? m->g_final : m->layers[i + 1].g1;
+            if ((rc = gemm_tc<TC_RESID>(s, c, M.w2, M.w2, s->tc_g.h, d, F, s->x, nullptr, false, g_next,
+                                        (!last && ple > 0) ? &s->tc_maps[i + 1] : nullptr, nullptr, rec, "ffn_down_gemm_tcgen05_residual_ple_norm")))
+                return rc;
             ++launches;
         }
         if (kind == CHAIN_PREFILL && s->parent) {
@@ -902,8 +903,9 @@ struct Chain {
             if (rec && (rc = rec->end())) return rc;
             ++launches;
         } else {
-            if ((rc = prep(m->g_final, nullptr, nullptr, 0))) return rc;
-            if ((rc = gemm_tc<TC_RAW>(s, s->tc_g.E, s->tc_g.E, s->tc_g.xn, cfg.vocab, d, s->logits, nullptr, nullptr, rec, "lmhead_gemm_tcgen05"))) return rc;
+            if ((rc = gemm_tc<TC_RAW>(s, c, s->tc_g.E, s->tc_g.E, s->tc_g.xn, cfg.vocab, d, s->logits, nullptr, true, nullptr, nullptr, nullptr, rec,
+                                      "lmhead_gemm_tcgen05")))
+                return rc;
             ++launches;
             if (kind == CHAIN_GREEDY) {
                 if (rec && (rc = rec->begin("argmax_pick", (uint64_t)B * cfg.vocab * 4, 0))) return rc;
@@ -1343,13 +1345,16 @@ static int setup_tc_path(mlb_session* s) {
     s->tc_stages = (int)std::max<size_t>(2, std::min<size_t>(6, budget / ((size_t)kTcM * 128 + (size_t)s->tc_nb * 128)));
     s->tc_stages_swiglu = (int)std::max<size_t>(2, std::min<size_t>(6, budget / ((size_t)2 * kTcM * 128 + (size_t)s->tc_nb * 128)));
     const int nq = c.heads * c.head_dim, a_dn = c.heads * c.dn_value_dim;
-    int n_proj = 16;
-    for (const DevLayer& L : s->m->layers) n_proj = std::max(n_proj, L.n_qkv);
     int rc;
+    if (c.ple_dim > 0 && ple_dtype(c.weight_dtype) != MLB_DT_BF16) return MLB_OK;
+    if ((rc = build_step_layers(s))) return rc;
+    s->tc_nb_resid = tc_pick_nb(s, c.dim, 1);
+    const int parts = (c.dim + kTcM - 1) / kTcM;
     if ((rc = sess_alloc(s, (void**)&s->xn16, (size_t)B * c.dim * 2, true))) return rc;
     if ((rc = sess_alloc(s, (void**)&s->a16, (size_t)B * std::max(nq, a_dn) * 2, true))) return rc;
     if ((rc = sess_alloc(s, (void**)&s->h16, (size_t)B * c.ffn_dim * 2, true))) return rc;
-    if ((rc = sess_alloc(s, (void**)&s->rawq, (size_t)B * n_proj * 4, true))) return rc;
+    if ((rc = sess_alloc(s, (void**)&s->tc_ssq, (size_t)B * parts * 4, true))) return rc;
+    if (c.ple_dim > 0 && (rc = sess_alloc(s, (void**)&s->tple16, (size_t)c.layers * B * c.ple_dim * 2, true))) return rc;
     s->tc_maps.resize(c.layers);
     for (int i = 0; i < c.layers; ++i) {
         const DevLayer& L = s->m->layers[i];
@@ -1359,6 +1364,11 @@ static int setup_tc_path(mlb_session* s) {
         if ((rc = make_bf16_map(enc, &M.w1a, L.W1a, c.ffn_dim, c.dim, kTcM))) return rc;
         if ((rc = make_bf16_map(enc, &M.w1b, L.W1b, c.ffn_dim, c.dim, kTcM))) return rc;
         if ((rc = make_bf16_map(enc, &M.w2, L.W2, c.dim, c.ffn_dim, kTcM))) return rc;
+        if (c.ple_dim > 0) {
+            // operands of the per-layer embedding folded into the previous layer's down projection
+            if ((rc = make_bf16_map(enc, &M.pleP, L.pleP, c.dim, c.ple_dim, kTcM))) return rc;
+            if ((rc = make_bf16_map(enc, &M.pleT, s->tple16 + (size_t)i * B * c.ple_dim, B, c.ple_dim, s->tc_nb_resid))) return rc;
+        }
     }
     if ((rc = make_bf16_map(enc, &s->tc_g.E, s->m->E, c.vocab, c.dim, kTcM))) return rc;
     for (int i = 0; i < 5; ++i) {
@@ -1369,9 +1379,17 @@ static int setup_tc_path(mlb_session* s) {
         if ((rc = make_bf16_map(enc, &s->tc_g.h[i], s->h16, B, c.ffn_dim, nb))) return rc;
     }
     const int big = 227 * 1024;
-    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    if (c.kv_dtype == MLB_DT_BF16) {
+        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_QKV, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    } else {
+        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_QKV, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    }
     s->use_tc = true;
     return MLB_OK;
 }

@@ -9,10 +9,19 @@
 //   * one thread issues tcgen05.mma (kind::f16, M128 x N=Nb x K16, four per stage) into TMEM and
 //     tcgen05.commit's the stage back to the loader;
 //   * all four warps read the accumulator with tcgen05.ld (warp w owns TMEM lanes 32w..32w+31 =
-//     output features) and run the epilogue: plain store, residual add in place, or SwiGLU of
-//     the two accumulators written as the bf16 input of the down projection.
+//     output features) and run the epilogue.
+// Nothing but these kernels, the attention / delta-net kernels and the pick runs between two steps'
+// embeddings; what the reference does in element-wise kernels lives in the epilogues:
+//   * RMS norm is deferred. The kernel that produces the residual stream x (embedding, o-projection,
+//     down projection) also writes bf16(x * gain) - the next projection's activation operand - and,
+//     per sequence and 128-feature tile, the sum of x^2. The consuming GEMM scales its accumulator
+//     column b by 1 / sqrt(sum x_b^2 / K + eps): the same (x / rms) * gain . w up to rounding order.
+//   * QKV mode: per-head QK norm, RoPE, KV-cache append and the sigmoid gate on the accumulator.
+//   * SWIGLU mode: silu(gate) * up of two accumulators, written as the bf16 operand of the down projection.
+//   * RESID mode: residual add in place; the per-layer embedding P . T[tok] of the next layer rides along
+//     as extra k-blocks from a second operand pair ([W2 | P] . [h | T[tok]]).
 // Reference ops replaced: the cublasGemmEx calls of inference.cu:401-465, :581-602, :623-695,
-// :720-743 and the element-wise kernels fused behind them (inference.cu:252-291).
+// :720-743 and the element-wise kernels around them (inference.cu:24-134, :248-291).
 // Every mbarrier wait is bounded; a wait that runs out records an error code, the kernel still
 // frees its tensor memory and returns.
 #pragma once
@@ -26,17 +35,67 @@ constexpr int kTcM = 128;          // output features per CTA (UMMA M)
 constexpr int kTcKB = 64;          // bf16 elements per k-block = one 128-byte swizzle row
 constexpr uint32_t kTcSpin = 1u << 22;
 
-enum GemmTcMode : int { TC_RAW = 0, TC_RESID = 1, TC_SWIGLU = 2 };
+enum GemmTcMode : int { TC_RAW = 0, TC_RESID = 1, TC_SWIGLU = 2, TC_QKV = 3 };
+
+// Per-head QK RMS norm, RoPE, KV-cache append, sigmoid gate (inference.cu:52-134, :248) on the rows of a
+// fused q|k|v|gate projection.
+struct QkvPostParams {
+    int nq, nk, nv, ng, hd, kv_heads, qk_norm;
+    float eps;
+    const float* gq; const float* gk; const float* rope;
+    void* kpool; void* vpool;
+    const int* page_table; int pt_stride;
+    float* qbuf; float* gbuf;
+};
 
 struct GemmTcParams {
     int N, K, B, Nb;               // Nb = batch tile = UMMA N (multiple of 16, <= 256)
     int stages;
+    int nkb_x;                     // k-blocks taken from the second operand pair after the K / 64 of the first
     uint32_t tmem_cols;            // power of two >= 32 covering the accumulators
     float* y;                      // RAW / RESID: fp32 [B][N]
     const float* resid;            // RESID: fp32 [B][N] (may alias y)
     bf16_t* h16;                   // SWIGLU: bf16 [B][N]
+    // deferred RMS norm of the activation operand: partial sums of squares [B][ssq_parts]; null = operand is used as is
+    const float* ssq_in; int ssq_parts; float eps;
+    // RESID: operand and partial sums for the next norm (null = not wanted)
+    bf16_t* xg16; const float* gain_next; float* ssq_out;
     int* err;
 };
+
+// vals[16] per lane -> the sum over the warp's 32 lanes of column (lane >> 1) & 15, in 16 shuffles
+__device__ __forceinline__ float warp_colsum16(float (&v)[16], int lane) {
+    {
+        const bool hi = (lane & 16) != 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float send = hi ? v[j] : v[j + 8], keep = hi ? v[j + 8] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
+    }
+    {
+        const bool hi = (lane & 8) != 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float send = hi ? v[j] : v[j + 4], keep = hi ? v[j + 4] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+        }
+    }
+    {
+        const bool hi = (lane & 4) != 0;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float send = hi ? v[j] : v[j + 2], keep = hi ? v[j + 2] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+        }
+    }
+    {
+        const bool hi = (lane & 2) != 0;
+        const float send = hi ? v[0] : v[1], keep = hi ? v[1] : v[0];
+        v[0] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    }
+    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
+}
 
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, int* err, int code) {
     for (uint32_t i = 0; i < kTcSpin; ++i)
@@ -97,10 +156,15 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-template <int MODE>
+constexpr int kTcEpiFloats = 256 + 4 * 256 + 4 * 16;   // column scales, per-warp column sums, per-warp head sums
+
+template <int MODE, typename KVT>
 __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
                                                           const __grid_constant__ CUtensorMap tmA2,
-                                                          const __grid_constant__ CUtensorMap tmB, GemmTcParams p) {
+                                                          const __grid_constant__ CUtensorMap tmB,
+                                                          const __grid_constant__ CUtensorMap tmAx,
+                                                          const __grid_constant__ CUtensorMap tmBx, GemmTcParams p,
+                                                          StepCtl c, QkvPostParams q) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr int NA = MODE == TC_SWIGLU ? 2 : 1;
@@ -110,13 +174,17 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m0 = blockIdx.x * kTcM;
     const int b0 = blockIdx.y * p.Nb;
-    const int nkb = (p.K + kTcKB - 1) / kTcKB;
+    const int nkb1 = (p.K + kTcKB - 1) / kTcKB;
+    const int nkb = nkb1 + p.nkb_x;
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)p.stages * stage_bytes);
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = full0 + 8u * p.stages;
     const uint32_t accum = empty0 + 8u * p.stages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * p.stages + 1);
+    float* rinv_s = reinterpret_cast<float*>(tmem_slot + 4);      // [256] scale of column b
+    float* colsum_s = rinv_s + 256;                               // [4][256] per-warp sums of x^2 (RESID)
+    float* head_s = colsum_s + 4 * 256;                           // [4][16] per-warp sums of a chunk (QK norm)
 
     if (tid == 0) {
         for (int i = 0; i < p.stages; ++i) {
@@ -142,25 +210,33 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
         // The weight tiles of the first stages depend on nothing: they are on their way before this
         // kernel waits for its predecessor, whose results only the activation tiles need.
         const uint32_t tx = (uint32_t)stage_bytes;
+        auto load_a = [&](int kb, uint32_t base, uint32_t bar) {
+            if (kb < nkb1) {
+                tma_load_2d(base, &tmA, kb * kTcKB, m0, bar);
+                if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes, &tmA2, kb * kTcKB, m0, bar);
+            } else {
+                tma_load_2d(base, &tmAx, (kb - nkb1) * kTcKB, m0, bar);
+            }
+        };
+        auto load_b = [&](int kb, uint32_t base, uint32_t bar) {
+            if (kb < nkb1) tma_load_2d(base + NA * a_bytes, &tmB, kb * kTcKB, b0, bar);
+            else tma_load_2d(base + NA * a_bytes, &tmBx, (kb - nkb1) * kTcKB, b0, bar);
+        };
         const int pre = min(p.stages, nkb);
         for (int kb = 0; kb < pre; ++kb) {
             mbar_expect_tx(full0 + 8u * kb, tx);
-            const uint32_t base = smem_u32(smem + (size_t)kb * stage_bytes);
-            tma_load_2d(base, &tmA, kb * kTcKB, m0, full0 + 8u * kb);
-            if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes, &tmA2, kb * kTcKB, m0, full0 + 8u * kb);
+            load_a(kb, smem_u32(smem + (size_t)kb * stage_bytes), full0 + 8u * kb);
         }
         pdl_wait();                  // the activation operand comes from the predecessor kernel
-        for (int kb = 0; kb < pre; ++kb)
-            tma_load_2d(smem_u32(smem + (size_t)kb * stage_bytes) + NA * a_bytes, &tmB, kb * kTcKB, b0, full0 + 8u * kb);
+        for (int kb = 0; kb < pre; ++kb) load_b(kb, smem_u32(smem + (size_t)kb * stage_bytes), full0 + 8u * kb);
         for (int kb = pre; kb < nkb; ++kb) {
             const int s = kb % p.stages;
             const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
             if (!tc_wait(empty0 + 8u * s, ph ^ 1u, p.err, 11)) break;
             mbar_expect_tx(full0 + 8u * s, tx);
             const uint32_t base = smem_u32(smem + (size_t)s * stage_bytes);
-            tma_load_2d(base, &tmA, kb * kTcKB, m0, full0 + 8u * s);
-            if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes, &tmA2, kb * kTcKB, m0, full0 + 8u * s);
-            tma_load_2d(base + NA * a_bytes, &tmB, kb * kTcKB, b0, full0 + 8u * s);
+            load_a(kb, base, full0 + 8u * s);
+            load_b(kb, base, full0 + 8u * s);
         }
     } else {
         pdl_wait();
@@ -188,7 +264,20 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
         }
         umma_commit(accum);                        // the accumulators are complete
     }
-    __syncwarp();
+    if (warp >= 2) {
+        // scale of column b from the partial sums of squares its producer left (inference.cu:24-50)
+        for (int j = tid - 64; j < p.Nb; j += 64) {
+            float r = 1.0f;
+            const int b = b0 + j;
+            if (p.ssq_in != nullptr && b < p.B) {
+                float tot = 0.f;
+                for (int t = 0; t < p.ssq_parts; ++t) tot += __ldcg(p.ssq_in + (size_t)b * p.ssq_parts + t);
+                r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+            }
+            rinv_s[j] = r;
+        }
+    }
+    __syncthreads();
 
     // ---- epilogue: all four warps ------------------------------------------------------------------
     tc_wait(accum, 0, p.err, 13);
@@ -199,12 +288,27 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
     // residual values of the first chunk (RESID): fetched one chunk ahead of the stores, because
     // the output may alias the residual and the compiler must keep loads behind earlier stores
     float rnext[16];
+    float gain = 0.f;
     if (MODE == TC_RESID) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const int b = b0 + j;
             rnext[j] = (row_ok && b < p.B) ? __ldcg(p.resid + (size_t)b * p.N + row) : 0.f;
         }
+        if (p.xg16 != nullptr && row_ok) gain = p.gain_next[row];
+    }
+    // QKV: which of q | k | v | gate this warp's 32 rows belong to (the parts are whole heads of 64 or 128 rows)
+    const int seg_q = q.nq, seg_k = q.nq + q.nk, seg_v = seg_k + q.nv;
+    int seg = 0, rloc = 0, kvh = 0, head_w0 = 0, head_wn = 1;
+    float gn = 1.0f;
+    if (MODE == TC_QKV) {
+        const int wrow = m0 + warp * 32;
+        seg = wrow < seg_q ? 0 : (wrow < seg_k ? 1 : (wrow < seg_v ? 2 : 3));
+        rloc = row % q.hd;
+        kvh = seg == 1 ? (row - seg_q) / q.hd : (seg == 2 ? (row - seg_k) / q.hd : 0);
+        head_wn = q.hd / 32;
+        head_w0 = warp / head_wn * head_wn;
+        if (q.qk_norm && seg < 2 && row_ok) gn = seg == 0 ? q.gq[row] : q.gk[row - seg_q];
     }
     for (int c0 = 0; c0 < p.Nb; c0 += 16) {
         uint32_t v[16], u[16];
@@ -223,178 +327,151 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
             }
         }
         tmem_ld_wait();
-        if (row_ok) {
+        if (MODE == TC_QKV) {
+            float vv[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) vv[j] = __uint_as_float(v[j]) * rinv_s[c0 + j];
+            if (q.qk_norm) {
+                float sq[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) sq[j] = (seg < 2 && row_ok) ? vv[j] * vv[j] : 0.f;
+                const float tot = warp_colsum16(sq, lane);
+                if (!(lane & 1)) head_s[warp * 16 + ((lane >> 1) & 15)] = tot;
+                __syncthreads();
+                if (seg < 2) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float t = 0.f;
+                        for (int w = 0; w < head_wn; ++w) t += head_s[(head_w0 + w) * 16 + j];
+                        vv[j] = (vv[j] / sqrtf(t / (float)q.hd + q.eps)) * gn;
+                    }
+                }
+                __syncthreads();
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const int b = b0 + c0 + j;
-                if (b < p.B) {
+                const float other = __shfl_xor_sync(0xffffffffu, vv[j], 1);
+                if (!row_ok || !seq_active(c, b)) continue;
+                const int pos = c.pos[b];
+                if (seg < 2) {
+                    const float cs = q.rope[(size_t)pos * q.hd + (rloc & ~1)], sn = q.rope[(size_t)pos * q.hd + (rloc | 1)];
+                    const float rot = (rloc & 1) ? fmaf(sn, other, cs * vv[j]) : fmaf(cs, vv[j], -(sn * other));
+                    if (seg == 0) {
+                        q.qbuf[(size_t)b * q.nq + row] = rot;
+                    } else {
+                        const int page = q.page_table[(size_t)b * q.pt_stride + pos / kKvBlock];
+                        const size_t off = (((size_t)page * q.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * q.hd + rloc;
+                        Elem<KVT>::put(reinterpret_cast<KVT*>(q.kpool), off, rot);
+                    }
+                } else if (seg == 2) {
+                    const int page = q.page_table[(size_t)b * q.pt_stride + pos / kKvBlock];
+                    const size_t off = (((size_t)page * q.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * q.hd + rloc;
+                    Elem<KVT>::put(reinterpret_cast<KVT*>(q.vpool), off, vv[j]);
+                } else {
+                    q.gbuf[(size_t)b * q.ng + (row - seg_v)] = 1.0f / (1.0f + expf(-vv[j]));
+                }
+            }
+        } else {
+            float sq[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int b = b0 + c0 + j;
+                sq[j] = 0.f;
+                if (row_ok && b < p.B) {
                     const size_t o = (size_t)b * p.N + row;
                     const float acc = __uint_as_float(v[j]);
                     if (MODE == TC_RAW) {
-                        p.y[o] = acc;
+                        p.y[o] = acc * rinv_s[c0 + j];
                     } else if (MODE == TC_RESID) {
-                        p.y[o] = acc + rcur[j];            // inference.cu:252-260, :283-291
+                        const float xn = acc + rcur[j];    // inference.cu:252-260, :283-291
+                        p.y[o] = xn;
+                        if (p.xg16 != nullptr) {
+                            p.xg16[o] = __float2bfloat16_rn(xn * gain);
+                            sq[j] = xn * xn;
+                        }
                     } else {
-                        const float up = __uint_as_float(u[j]);
-                        p.h16[o] = __float2bfloat16_rn((acc / (1.0f + expf(-acc))) * up);   // inference.cu:262-281
+                        const float ri = rinv_s[c0 + j];
+                        const float g = acc * ri, up = __uint_as_float(u[j]) * ri;
+                        p.h16[o] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);   // inference.cu:262-281
                     }
                 }
+            }
+            if (MODE == TC_RESID && p.xg16 != nullptr) {
+                const float tot = warp_colsum16(sq, lane);
+                if (!(lane & 1)) colsum_s[warp * 256 + c0 + ((lane >> 1) & 15)] = tot;
             }
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (MODE == TC_RESID && p.ssq_out != nullptr) {
+        for (int j = tid; j < p.Nb; j += 128) {
+            const int b = b0 + j;
+            if (b < p.B)
+                p.ssq_out[(size_t)b * gridDim.x + blockIdx.x] =
+                    (colsum_s[j] + colsum_s[256 + j]) + (colsum_s[512 + j] + colsum_s[768 + j]);
+        }
+    }
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
     }
 }
 
 // ---- small kernels around the GEMMs ---------------------------------------------------------------
-// RMS norm (+ the layer's per-layer embedding added to the residual stream first) and conversion to
-// the bf16 activation operand. One CTA per sequence. (inference.cu:24-50, :83-95)
-// x[b] += P . T[tok_b]: the per-layer embedding of a large model as a launch of its own, one
-// projection row per thread and the rows of a sequence spread over grid.y CTAs. Inside
-// prep_bf16_kernel one CTA per sequence walks all d rows (25 us at d = 2048, ple = 128).
-// grid = (B, ceil(d / 64)), block = 64, dynamic shared memory = ple floats.
-template <typename T2>
-__global__ void __launch_bounds__(64) ple_add_kernel(StepCtl c, float* __restrict__ x, int K, const T2* __restrict__ pleT,
-                                                     const T2* __restrict__ pleP, int ple) {
+// Start of a step: token embedding plus the first layer's per-layer embedding into the fp32 residual
+// stream (inference.cu:137-170), its bf16(x * gain) operand and partial sums of squares for the first
+// projection, and the per-layer embedding rows T_l[tok] of the later layers gathered as bf16 operands of
+// the down projections. grid = (B, ceil(d / 128)), block = 128: one feature per thread.
+static __global__ void __launch_bounds__(128) embed_tc_kernel(StepCtl c, const bf16_t* __restrict__ E, int d,
+                                                              const StepLayer* __restrict__ layers, int n_layers, int ple,
+                                                              const float* __restrict__ gain, float* __restrict__ x,
+                                                              bf16_t* __restrict__ xg16, float* __restrict__ ssq,
+                                                              bf16_t* __restrict__ tple16) {
     pdl_launch_dependents();
-    pdl_wait();
+    pdl_wait();                      // pos / tok come from the last kernel of the previous step
     const int b = blockIdx.x;
     if (!seq_active(c, b)) return;
-    extern __shared__ __align__(16) float trow[];
-    const int t = c.tok[b];
-    for (int j = threadIdx.x; j < ple; j += blockDim.x) trow[j] = Elem<T2>::get(pleT, (size_t)t * ple + j);
-    __syncthreads();
-    constexpr int EPV2 = Elem<T2>::EPV;
-    const int i = blockIdx.y * blockDim.x + threadIdx.x;
-    if (i >= K) return;
-    float a = 0.f;
-    const T2* prow = pleP + (size_t)i * ple;
-#pragma unroll 4
-    for (int j = 0; j < ple; j += EPV2) {
-        float w[EPV2];
-        Elem<T2>::load_vec(prow + j, w);
-#pragma unroll
-        for (int e = 0; e < EPV2; ++e) a = fmaf(w[e], trow[j + e], a);
+    int t = c.tok[b];
+    if (c.tok_src != nullptr) {
+        t = c.tok_src[b];
+        if (blockIdx.y == 0 && threadIdx.x == 0) c.tok[b] = t;
     }
-    x[(size_t)b * K + i] += a;
-}
-
-template <typename T2>
-__global__ void __launch_bounds__(256) prep_bf16_kernel(StepCtl c, float* __restrict__ x, int K, const float* __restrict__ gain,
-                                                        float eps, const T2* __restrict__ pleT, const T2* __restrict__ pleP, int ple,
-                                                        bf16_t* __restrict__ out) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int b = blockIdx.x;
-    if (!seq_active(c, b)) return;
-    extern __shared__ __align__(16) float sm[];
-    float* xs = sm;                 // [K]
-    float* trow = sm + K;           // [ple]
-    __shared__ float red[8];
+    extern __shared__ __align__(16) float trow[];
+    __shared__ float red[4];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float* xr = x + (size_t)b * K;
     if (ple > 0) {
-        const int t = c.tok[b];
-        for (int j = tid; j < ple; j += blockDim.x) trow[j] = Elem<T2>::get(pleT, (size_t)t * ple + j);
+        const bf16_t* T0 = static_cast<const bf16_t*>(layers[0].pleT);
+        for (int j = tid; j < ple; j += 128) trow[j] = __bfloat162float(T0[(size_t)t * ple + j]);
+        for (int l = 1 + blockIdx.y; l < n_layers; l += gridDim.y) {
+            const bf16_t* Tl = static_cast<const bf16_t*>(layers[l].pleT);
+            for (int j = tid; j < ple; j += 128) tple16[((size_t)l * c.B + b) * ple + j] = Tl[(size_t)t * ple + j];
+        }
         __syncthreads();
     }
-    float ss = 0.f;
-    constexpr int EPV2 = Elem<T2>::EPV;
-    for (int i = tid; i < K; i += blockDim.x) {
-        float v = xr[i];
+    const int i = blockIdx.y * 128 + tid;
+    float v = 0.f;
+    if (i < d) {
+        v = __bfloat162float(E[(size_t)t * d + i]);
         if (ple > 0) {
             float a = 0.f;
-            const T2* prow = pleP + (size_t)i * ple;
-            for (int j = 0; j < ple; j += EPV2) {
-                float w[EPV2];
-                Elem<T2>::load_vec(prow + j, w);
+            const bf16_t* prow = static_cast<const bf16_t*>(layers[0].pleP) + (size_t)i * ple;
+#pragma unroll 4
+            for (int j = 0; j < ple; j += 8) {
+                float w[8];
+                Elem<bf16_t>::load_vec(prow + j, w);
 #pragma unroll
-                for (int e = 0; e < EPV2; ++e) a = fmaf(w[e], trow[j + e], a);
+                for (int e = 0; e < 8; ++e) a = fmaf(w[e], trow[j + e], a);
             }
             v += a;
-            xr[i] = v;              // the residual stream carries the per-layer embedding on
         }
-        xs[i] = v;
-        ss = fmaf(v, v, ss);
+        x[(size_t)b * d + i] = v;
+        xg16[(size_t)b * d + i] = __float2bfloat16_rn(v * gain[i]);
     }
-    if (gain != nullptr) {
-        ss = warp_sum(ss);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
-        const float r = sqrtf(tot / (float)K + eps);
-        for (int i = tid; i < K; i += blockDim.x) out[(size_t)b * K + i] = __float2bfloat16_rn((xs[i] / r) * gain[i]);
-    } else {
-        for (int i = tid; i < K; i += blockDim.x) out[(size_t)b * K + i] = __float2bfloat16_rn(xs[i]);
-    }
-}
-
-// Per-head QK RMS norm, RoPE, KV-cache append, sigmoid gate on the raw fp32 projections of a
-// batched GEMM (inference.cu:52-134, :248). grid = (heads of q|k|v|gate, B), block = hd/2 threads.
-struct QkvPostParams {
-    const float* raw; int n_qkv;
-    int nq, nk, nv, ng, hd, kv_heads, qk_norm;
-    float eps;
-    const float* gq; const float* gk; const float* rope;
-    void* kpool; void* vpool;
-    const int* page_table; int pt_stride;
-    float* qbuf; float* gbuf;
-};
-
-template <typename KVT>
-__global__ void __launch_bounds__(64) qkv_post_kernel(StepCtl c, QkvPostParams p) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int b = blockIdx.y;
-    if (!seq_active(c, b)) return;
-    const int hd = p.hd, row0 = blockIdx.x * hd;
-    const int pr = threadIdx.x, lane = pr & 31, warp = pr >> 5;
-    const int seg_q = p.nq, seg_k = p.nq + p.nk, seg_v = seg_k + p.nv;
-    const int seg = row0 < seg_q ? 0 : (row0 < seg_k ? 1 : (row0 < seg_v ? 2 : 3));
-    const float* src = p.raw + (size_t)b * p.n_qkv + row0;
-    const int r = 2 * pr;
-    float a = src[r], cc = src[r + 1];
-    const int pos = c.pos[b];
-    __shared__ float red[2];
-    if (p.qk_norm && seg < 2) {
-        float ss = warp_sum(a * a + cc * cc);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        float tot = red[0];
-        if (blockDim.x > 32) tot += red[1];
-        const float rs = sqrtf(tot / (float)hd + p.eps);
-        const int srow = seg == 0 ? row0 + r : row0 + r - seg_q;
-        const float* g = seg == 0 ? p.gq : p.gk;
-        a = (a / rs) * g[srow];
-        cc = (cc / rs) * g[srow + 1];
-    }
-    if (seg < 2) {
-        const float cs = p.rope[(size_t)pos * hd + r], sn = p.rope[(size_t)pos * hd + r + 1];
-        const float ra = cs * a - sn * cc, rc = sn * a + cs * cc;
-        if (seg == 0) {
-            p.qbuf[(size_t)b * p.nq + row0 + r] = ra;
-            p.qbuf[(size_t)b * p.nq + row0 + r + 1] = rc;
-        } else {
-            const int kvh = (row0 - seg_q) / hd;
-            const int page = p.page_table[(size_t)b * p.pt_stride + pos / kKvBlock];
-            const size_t off = (((size_t)page * p.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * hd + r;
-            Elem<KVT>::put(reinterpret_cast<KVT*>(p.kpool), off, ra);
-            Elem<KVT>::put(reinterpret_cast<KVT*>(p.kpool), off + 1, rc);
-        }
-    } else if (seg == 2) {
-        const int kvh = (row0 - seg_k) / hd;
-        const int page = p.page_table[(size_t)b * p.pt_stride + pos / kKvBlock];
-        const size_t off = (((size_t)page * p.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * hd + r;
-        Elem<KVT>::put(reinterpret_cast<KVT*>(p.vpool), off, a);
-        Elem<KVT>::put(reinterpret_cast<KVT*>(p.vpool), off + 1, cc);
-    } else {
-        p.gbuf[(size_t)b * p.ng + (row0 - seg_v) + r] = 1.0f / (1.0f + expf(-a));
-        p.gbuf[(size_t)b * p.ng + (row0 - seg_v) + r + 1] = 1.0f / (1.0f + expf(-cc));
-    }
+    const float ss = warp_sum(v * v);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (tid == 0) ssq[(size_t)b * gridDim.y + blockIdx.y] = (red[0] + red[1]) + (red[2] + red[3]);
 }
 
 // Greedy pick over the fp32 logits of a batched LM-head GEMM: argmax, lowest index on ties
