@@ -418,6 +418,8 @@ struct Recorder {
 };
 }  // namespace mlb
 
+struct TcShape { int nb, split, stages, group; size_t smem; uint32_t tmem_cols; };
+
 struct mlb_session {
     mlb_model* m = nullptr;
     int B = 0, max_ctx = 0, max_pages = 0, kv_pages = 0;
@@ -470,7 +472,12 @@ struct mlb_session {
     mlb::LeanParams lean;
     // tensor-core projections (bf16 weights, batch >= 16)
     bool use_tc = false;
-    int tc_nb = 0, tc_nb_resid = 16, tc_stages = 0, tc_stages_swiglu = 0;
+    int tc_nb = 0, tc_stages = 0, tc_stages_swiglu = 0;
+    int tc_max_split = 2;                     // MLB_TC_SPLIT: largest cluster that may split a GEMM's k-blocks
+    int tc_cluster_cap[4] = {0, 0, 0, 0};     // clusters of 1, 2, 4, 8 GEMM CTAs that can be resident at once
+    unsigned long long* tc_trace = nullptr;   // MLB_TC_TRACE=1: [64][8] timer stamps of the step's GEMM launches
+    int tc_trace_n = 0;
+    TcShape tc_shape_down{};                  // launch shape of the down projection (its per-layer embedding map has this batch tile)
     mlb::bf16_t *xn16 = nullptr, *a16 = nullptr, *h16 = nullptr;
     float* rawq = nullptr;
     struct alignas(64) TcLayerMaps { CUtensorMap qkv, o, w1a, w1b, w2, pleP, pleT; };   // pleP / pleT: [d][ple] projection, gathered [B][ple] rows
@@ -574,23 +581,74 @@ static cudaError_t launch_chain(bool pdl, void (*kernel)(KArgs...), dim3 grid, d
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
-// Batch tile (UMMA N) of one GEMM: the largest of 256..16 that still yields enough CTAs to
-// spread the weight stream and the MMAs over the SMs (the projections of a decode step have few
-// 128-row tiles; the activations are re-read per batch tile from L2, which is cheap).
-// One CTA per SM fits (the ring takes ~200 KB), so a grid runs in ceil(CTAs / SMs) waves and a CTA's
-// time follows the bytes it streams: `na` weight tiles of 128 rows plus the batch tile, per k-block.
-// Pick the tile with the least waves x bytes: 176 CTAs of 16 columns are two waves, 88 CTAs of 32
-// columns one.
-static int tc_pick_nb(const mlb_session* s, int N, int na) {
+// launch_chain for a grid whose z extent is one thread-block cluster (cluster_z CTAs share an output tile).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_cluster(bool pdl, int cluster_z, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args... args) {
+    cudaLaunchConfig_t cfg;
+    std::memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// Shape of one tensor-core GEMM launch: batch tile (UMMA N), how many CTAs of a cluster split the k-blocks of
+// an output tile, and the ring. Measured on B200: a tcgen05.mma of M = 128 costs about 0.1 us whatever its N
+// (16..128), so a CTA's k-loop takes 0.4 us per 64-wide k-block (0.8 with two weight tiles) whatever the ring
+// depth, and is the time of the kernel unless the k-blocks are spread over CTAs. Exchanging partial
+// accumulators through distributed shared memory costs 2-3 us per launch with clusters of 4 and 8, more than
+// it saves at these sizes; pairs pay off at small batches (cfg1 step at 32 sequences: 452 -> 424 us) and are
+// neutral at 256, so MLB_TC_SPLIT defaults to 2. One wave of CTAs per launch where possible.
+static TcShape tc_pick_shape(const mlb_session* s, int N, int nkb_all, int na) {
     const int tiles_m = (N + kTcM - 1) / kTcM;
     const int cap = std::min(256, (s->B + 15) / 16 * 16);
-    int best = 16;
-    long best_cost = -1;
-    for (int nb = 16; nb <= cap; nb <<= 1) {
-        const long ctas = (long)tiles_m * ((s->B + nb - 1) / nb);
-        const long waves = (ctas + s->sm_count - 1) / s->sm_count;
-        const long cost = waves * (na * kTcM + nb);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = nb; }
+    TcShape best{};
+    double best_cost = -1.0;
+    for (int nb = 16; nb <= cap && na * nb <= 512; nb <<= 1) {
+        for (int li = 0; li < 4; ++li) {
+            const int S = 1 << li;
+            if (S > s->tc_max_split || S > nkb_all) break;
+            if (S > 1 && (nb % S != 0 || s->tc_cluster_cap[li] <= 0)) continue;
+            const size_t stage_bytes = (size_t)na * kTcM * 128 + (size_t)nb * 128;
+            const int kpc = (nkb_all + S - 1) / S;
+            int st = (int)std::max<size_t>(1, std::min<size_t>(std::min(kpc, 12), kTcRingBytes / stage_bytes));
+            const int g = st >= kpc ? 1 : (st >= 8 ? 4 : (st >= 4 ? 2 : 1));
+            st -= st % g;
+            const size_t body = std::max((size_t)st * stage_bytes, S > 1 ? (size_t)na * nb * kTcM * 4 : (size_t)0);
+            const size_t smem = 1024 + kTcHeadBytes + kTcStageBytes + body;
+            if (smem > 227 * 1024) continue;
+            const long ctas = (long)tiles_m * ((s->B + nb - 1) / nb) * S;
+            const long resident = S == 1 ? s->sm_count : (long)s->tc_cluster_cap[li] * S;
+            const long waves = (ctas + resident - 1) / resident;
+            const double t_loop = 0.4 * na * kpc;
+            const double t_red = S > 1 ? 0.5 + (double)na * nb * 512.0 / 65536.0 : 0.0;
+            const double t_epi = 0.25 * ((nb / S + 15) / 16);
+            const double cost = (double)waves * (t_loop + t_red + t_epi + 0.5);
+            if (best_cost < 0 || cost < best_cost) {
+                best_cost = cost;
+                uint32_t cols = 32;
+                while (cols < (uint32_t)(na * nb)) cols <<= 1;
+                best = TcShape{nb, S, st, g, smem, cols};
+            }
+        }
     }
     return best;
 }
@@ -778,29 +836,29 @@ struct Chain {
                        float* y, bf16_t* h16, bool normed, const float* next_gain, const mlb_session::TcLayerMaps* ext,
                        const QkvPostParams* q, Recorder* rec, const char* name) {
         GemmTcParams p;
-        const int nb = MODE == TC_RESID ? s->tc_nb_resid : tc_pick_nb(s, N, MODE == TC_SWIGLU ? 2 : 1);
-        p.N = N; p.K = K; p.B = s->B; p.Nb = nb;
         const int ple = s->m->cfg.ple_dim;
+        const int na = MODE == TC_SWIGLU ? 2 : 1;
         p.nkb_x = ext ? (ple + kTcKB - 1) / kTcKB : 0;
-        const size_t stage_bytes = (size_t)(MODE == TC_SWIGLU ? 2 : 1) * kTcM * 128 + (size_t)nb * 128;
-        p.stages = (int)std::max<size_t>(2, std::min<size_t>(8, (200 * 1024) / stage_bytes));
-        uint32_t cols = 32;
-        while (cols < (uint32_t)(MODE == TC_SWIGLU ? 2 : 1) * (uint32_t)nb) cols <<= 1;
-        p.tmem_cols = cols;
+        const TcShape sh = ext ? s->tc_shape_down : tc_pick_shape(s, N, (K + kTcKB - 1) / kTcKB, na);
+        if (sh.nb == 0) return fail(MLB_E_UNSUPPORTED, "%s: no launch shape fits", name);
+        const int nb = sh.nb;
+        p.N = N; p.K = K; p.B = s->B; p.Nb = nb;
+        p.stages = sh.stages; p.group = sh.group; p.tmem_cols = sh.tmem_cols;
         p.y = y; p.resid = MODE == TC_RESID ? y : nullptr; p.h16 = h16; p.err = s->dev_err;
+        p.trace = s->tc_trace ? s->tc_trace + 8 * (size_t)(s->tc_trace_n++ % 64) : nullptr;
         p.ssq_in = normed ? s->tc_ssq : nullptr; p.ssq_parts = (s->m->cfg.dim + kTcM - 1) / kTcM; p.eps = s->m->cfg.rms_eps;
         p.xg16 = next_gain ? s->xn16 : nullptr; p.gain_next = next_gain; p.ssq_out = next_gain ? s->tc_ssq : nullptr;
-        const size_t smem = (size_t)p.stages * stage_bytes + (2 * (size_t)p.stages + 1) * 8 + 16 + kTcEpiFloats * 4 + 1024;
-        dim3 grid((N + kTcM - 1) / kTcM, (s->B + nb - 1) / nb);
+        const size_t smem = sh.smem;
+        dim3 grid((N + kTcM - 1) / kTcM, (s->B + nb - 1) / nb, sh.split);
         int rc;
-        if (rec && (rc = rec->begin(name, (uint64_t)N * (K + (ext ? ple : 0)) * 2 * (MODE == TC_SWIGLU ? 2 : 1) + (uint64_t)s->B * K * 2 + (uint64_t)s->B * N * 4,
-                                    2ull * N * (K + (ext ? ple : 0)) * s->B * (MODE == TC_SWIGLU ? 2 : 1))))
+        if (rec && (rc = rec->begin(name, (uint64_t)N * (K + (ext ? ple : 0)) * 2 * na + (uint64_t)s->B * K * 2 + (uint64_t)s->B * N * 4,
+                                    2ull * N * (K + (ext ? ple : 0)) * s->B * na)))
             return rc;
         QkvPostParams q0{};
         const CUtensorMap& Ax = ext ? ext->pleP : A;
         const CUtensorMap& Bx = ext ? ext->pleT : A;
-        cudaError_t e = launch_chain(s->use_pdl, gemm_tc_kernel<MODE, KVT>, grid, dim3(128), smem, s->stream, A, A2, Bmaps[nb_index(nb)], Ax, Bx, p, c,
-                                     q ? *q : q0);
+        cudaError_t e = launch_cluster(s->use_pdl, sh.split, gemm_tc_kernel<MODE, KVT>, grid, dim3(kTcThreads), smem, s->stream, A, A2, Bmaps[nb_index(nb)], Ax, Bx, p,
+                                       c, q ? *q : q0);
         if (e != cudaSuccess) return fail(MLB_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
         if (rec) return rec->end();
         return MLB_OK;
@@ -1348,7 +1406,34 @@ static int setup_tc_path(mlb_session* s) {
     int rc;
     if (c.ple_dim > 0 && ple_dtype(c.weight_dtype) != MLB_DT_BF16) return MLB_OK;
     if ((rc = build_step_layers(s))) return rc;
-    s->tc_nb_resid = tc_pick_nb(s, c.dim, 1);
+    if (const char* v = std::getenv("MLB_TC_TRACE"))
+        if (v[0] == '1' && (rc = sess_alloc(s, (void**)&s->tc_trace, 64 * 8 * 8, true))) return rc;
+    s->tc_max_split = 2;
+    if (const char* v = std::getenv("MLB_TC_SPLIT")) s->tc_max_split = std::max(1, std::min(8, std::atoi(v)));
+    {
+        // how many clusters of GEMM CTAs fit on the GPU at once (a 100 KB CTA, typical of a split launch)
+        const int big = 227 * 1024;
+        void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, GemmTcParams, StepCtl, QkvPostParams) =
+            gemm_tc_kernel<TC_RESID, float>;
+        CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        s->tc_cluster_cap[0] = s->sm_count;
+        for (int li = 1; li < 4; ++li) {
+            cudaLaunchConfig_t cfg;
+            std::memset(&cfg, 0, sizeof cfg);
+            cfg.gridDim = dim3(1, 1, 1u << li);
+            cfg.blockDim = dim3(kTcThreads);
+            cfg.dynamicSmemBytes = 100 * 1024;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1u << li;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+            s->tc_cluster_cap[li] = n;
+        }
+    }
+    s->tc_shape_down = tc_pick_shape(s, c.dim, (c.ffn_dim + kTcKB - 1) / kTcKB + (c.ple_dim + kTcKB - 1) / kTcKB, 1);
     const int parts = (c.dim + kTcM - 1) / kTcM;
     if ((rc = sess_alloc(s, (void**)&s->xn16, (size_t)B * c.dim * 2, true))) return rc;
     if ((rc = sess_alloc(s, (void**)&s->a16, (size_t)B * std::max(nq, a_dn) * 2, true))) return rc;
@@ -1367,7 +1452,7 @@ static int setup_tc_path(mlb_session* s) {
         if (c.ple_dim > 0) {
             // operands of the per-layer embedding folded into the previous layer's down projection
             if ((rc = make_bf16_map(enc, &M.pleP, L.pleP, c.dim, c.ple_dim, kTcM))) return rc;
-            if ((rc = make_bf16_map(enc, &M.pleT, s->tple16 + (size_t)i * B * c.ple_dim, B, c.ple_dim, s->tc_nb_resid))) return rc;
+            if ((rc = make_bf16_map(enc, &M.pleT, s->tple16 + (size_t)i * B * c.ple_dim, B, c.ple_dim, s->tc_shape_down.nb))) return rc;
         }
     }
     if ((rc = make_bf16_map(enc, &s->tc_g.E, s->m->E, c.vocab, c.dim, kTcM))) return rc;
@@ -2064,6 +2149,15 @@ extern "C" int mlb_session_grid_timers(mlb_session* s, long long* out, int cap) 
 
 extern "C" int mlb_session_grid_trace(mlb_session* s, long long* out, int cap) {
     if (!s || !out) return fail(MLB_E_INVALID, "null argument");
+    if (s->tc_trace) {
+        // tensor-core step: 8 words per GEMM launch of the last step (entry, set up, predecessor complete,
+        // accumulators complete, epilogue done), 64 launches at most
+        if (cap < 512) return fail(MLB_E_INVALID, "room for 512 words needed, %d given", cap);
+        CU(cudaSetDevice(s->m->device));
+        CU(cudaStreamSynchronize(s->stream));
+        CU(cudaMemcpy(out, s->tc_trace, 512 * 8, cudaMemcpyDeviceToHost));
+        return 64;
+    }
     if (!s->use_lean || !s->lean.trace) return 0;
     CU(cudaSetDevice(s->m->device));
     const int n = s->grid_ctas * kLeanTraceLen;

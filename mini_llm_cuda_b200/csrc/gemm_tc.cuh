@@ -50,7 +50,8 @@ struct QkvPostParams {
 
 struct GemmTcParams {
     int N, K, B, Nb;               // Nb = batch tile = UMMA N (multiple of 16, <= 256)
-    int stages;
+    int stages;                    // ring depth, a multiple of `group`
+    int group;                     // k-blocks per refill of the ring: one tcgen05.commit frees `group` stages
     int nkb_x;                     // k-blocks taken from the second operand pair after the K / 64 of the first
     uint32_t tmem_cols;            // power of two >= 32 covering the accumulators
     float* y;                      // RAW / RESID: fp32 [B][N]
@@ -61,6 +62,7 @@ struct GemmTcParams {
     // RESID: operand and partial sums for the next norm (null = not wanted)
     bf16_t* xg16; const float* gain_next; float* ssq_out;
     int* err;
+    unsigned long long* trace;     // diagnostics: five %globaltimer stamps of CTA (0, 0, 0), or null
 };
 
 // vals[16] per lane -> the sum over the warp's 32 lanes of column (lane >> 1) & 15, in 16 shuffles
@@ -97,6 +99,23 @@ __device__ __forceinline__ float warp_colsum16(float (&v)[16], int lane) {
     return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 1);
 }
 
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Loads the compiler must issue where they are written (it otherwise sinks a prefetch to its first use, past
+// the wait for the accumulator, and the epilogue pays one L2 latency per column: 0.5 us each, measured).
+__device__ __forceinline__ float2 ld_nc_f2_now(const float2* p) {
+    float2 v;
+    asm volatile("ld.global.nc.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ld_cg_f32_now(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, int* err, int code) {
     for (uint32_t i = 0; i < kTcSpin; ++i)
         if (mbar_try_wait(bar, parity)) return true;
@@ -156,17 +175,52 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-constexpr int kTcEpiFloats = 256 + 4 * 256 + 4 * 16;   // column scales, per-warp column sums, per-warp head sums
+constexpr int kTcThreads = 256;   // warp 0: TMA loader, warp 1: MMA issuer; all 8 warps run the epilogue (warps w and w + 4 share TMEM lanes)
+constexpr int kTcHeadBytes = 9216;     // epilogue words (7680 B) and barriers
+constexpr int kTcStageBytes = 32768;   // staging of the QKV epilogue
+constexpr size_t kTcRingBytes = 184 * 1024;   // what is left of 227 KB for the ring of stages
+constexpr int kTcEpiFloats = 256 + 4 * 256 + 8 * 16 + 2 * 256;   // column scales, per-warp column sums, per-warp head sums, positions, pages
 
+// ---- thread-block cluster: the CTAs that share one output tile and split its k-blocks -----------------
+// barrier over the four warps of one epilogue group (hardware barriers 1 and 2; 0 is __syncthreads)
+__device__ __forceinline__ void group_sync(int grp) { asm volatile("bar.sync %0, 128;" ::"r"(grp + 1) : "memory"); }
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Hardware barrier over the CTAs of the cluster; every CTA reaches every one of them (no early return in
+// the kernel), so it needs no bound.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float cluster_ld_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// grid = (ceil(N / 128), ceil(B / Nb), split) with clusters of (1, 1, split) when split > 1: the `split`
+// CTAs of a cluster take consecutive shares of the k-blocks of one output tile (a tcgen05.mma of these
+// shapes costs about 0.1 us whatever its N, so the k-loop of a lone CTA is the time of the kernel), leave
+// their partial accumulators in shared memory, and each finishes Nb / split columns of the tile from the
+// partials of all of them, read over distributed shared memory in a fixed order.
 template <int MODE, typename KVT>
-__global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                          const __grid_constant__ CUtensorMap tmA2,
-                                                          const __grid_constant__ CUtensorMap tmB,
-                                                          const __grid_constant__ CUtensorMap tmAx,
-                                                          const __grid_constant__ CUtensorMap tmBx, GemmTcParams p,
-                                                          StepCtl c, QkvPostParams q) {
+__global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                       const __grid_constant__ CUtensorMap tmA2,
+                                                       const __grid_constant__ CUtensorMap tmB,
+                                                       const __grid_constant__ CUtensorMap tmAx,
+                                                       const __grid_constant__ CUtensorMap tmBx, GemmTcParams p,
+                                                       StepCtl c, QkvPostParams q) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const bool tracing = p.trace != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    if (tracing) p.trace[0] = globaltimer_ns();          // entry
     constexpr int NA = MODE == TC_SWIGLU ? 2 : 1;
     const int a_bytes = kTcM * 128;
     const int b_bytes = p.Nb * 128;
@@ -175,16 +229,28 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
     const int m0 = blockIdx.x * kTcM;
     const int b0 = blockIdx.y * p.Nb;
     const int nkb1 = (p.K + kTcKB - 1) / kTcKB;
-    const int nkb = nkb1 + p.nkb_x;
+    const int split = (int)gridDim.z, rank = (int)blockIdx.z;      // cluster = the CTAs of one (x, y)
+    // this CTA's k-blocks [kb_lo, kb_lo + nkb) of the nkb1 + nkb_x of the tile
+    const int nkb_all = nkb1 + p.nkb_x;
+    const int kb_lo = (int)(((long)nkb_all * rank) / split);
+    const int nkb = (int)(((long)nkb_all * (rank + 1)) / split) - kb_lo;
 
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)p.stages * stage_bytes);
+    // shared memory: [epilogue words][barriers][ring stages | partial accumulators]; the offsets of the first
+    // two are the same in every CTA of a cluster
+    float* rinv_s = reinterpret_cast<float*>(smem);               // [256] scale of column b
+    float* colsum_s = rinv_s + 256;                               // [4][256] per-warp sums of x^2 (RESID)
+    float* head_s = colsum_s + 4 * 256;                           // [8][16] per-warp sums of a chunk (QK norm)
+    int* pos_s = reinterpret_cast<int*>(head_s + 8 * 16);         // [256] position of column b, -1 = takes no part (QKV)
+    int* page_s = pos_s + 256;                                    // [256] KV page its new row goes to (QKV)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTcEpiFloats * 4);
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = full0 + 8u * p.stages;
     const uint32_t accum = empty0 + 8u * p.stages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * p.stages + 1);
-    float* rinv_s = reinterpret_cast<float*>(tmem_slot + 4);      // [256] scale of column b
-    float* colsum_s = rinv_s + 256;                               // [4][256] per-warp sums of x^2 (RESID)
-    float* head_s = colsum_s + 4 * 256;                           // [4][16] per-warp sums of a chunk (QK norm)
+    float* stage_s = reinterpret_cast<float*>(smem + kTcHeadBytes);                  // [2 groups][16][128] a chunk of the tile (QKV)
+    float* rope_s = stage_s + 2 * 16 * kTcM;                                         // [2 groups][16][128] its RoPE factors (QKV)
+    unsigned char* ring = smem + kTcHeadBytes + kTcStageBytes;    // 1024-aligned
+    float* part = reinterpret_cast<float*>(ring);                 // [NA][Nb][128] partial accumulators (split > 1), over the ring
 
     if (tid == 0) {
         for (int i = 0; i < p.stages; ++i) {
@@ -203,6 +269,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (tracing) p.trace[1] = globaltimer_ns();          // barriers and tensor memory set up
 
     pdl_launch_dependents();
     if (warp == 0 && lane == 0) {
@@ -211,30 +278,34 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
         // kernel waits for its predecessor, whose results only the activation tiles need.
         const uint32_t tx = (uint32_t)stage_bytes;
         auto load_a = [&](int kb, uint32_t base, uint32_t bar) {
-            if (kb < nkb1) {
-                tma_load_2d(base, &tmA, kb * kTcKB, m0, bar);
-                if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes, &tmA2, kb * kTcKB, m0, bar);
+            const int k = kb_lo + kb;
+            if (k < nkb1) {
+                tma_load_2d(base, &tmA, k * kTcKB, m0, bar);
+                if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes, &tmA2, k * kTcKB, m0, bar);
             } else {
-                tma_load_2d(base, &tmAx, (kb - nkb1) * kTcKB, m0, bar);
+                tma_load_2d(base, &tmAx, (k - nkb1) * kTcKB, m0, bar);
             }
         };
         auto load_b = [&](int kb, uint32_t base, uint32_t bar) {
-            if (kb < nkb1) tma_load_2d(base + NA * a_bytes, &tmB, kb * kTcKB, b0, bar);
-            else tma_load_2d(base + NA * a_bytes, &tmBx, (kb - nkb1) * kTcKB, b0, bar);
+            const int k = kb_lo + kb;
+            if (k < nkb1) tma_load_2d(base + NA * a_bytes, &tmB, k * kTcKB, b0, bar);
+            else tma_load_2d(base + NA * a_bytes, &tmBx, (k - nkb1) * kTcKB, b0, bar);
         };
         const int pre = min(p.stages, nkb);
         for (int kb = 0; kb < pre; ++kb) {
             mbar_expect_tx(full0 + 8u * kb, tx);
-            load_a(kb, smem_u32(smem + (size_t)kb * stage_bytes), full0 + 8u * kb);
+            load_a(kb, smem_u32(ring + (size_t)kb * stage_bytes), full0 + 8u * kb);
         }
         pdl_wait();                  // the activation operand comes from the predecessor kernel
-        for (int kb = 0; kb < pre; ++kb) load_b(kb, smem_u32(smem + (size_t)kb * stage_bytes), full0 + 8u * kb);
+        if (tracing) p.trace[2] = globaltimer_ns();      // predecessor complete
+        for (int kb = 0; kb < pre; ++kb) load_b(kb, smem_u32(ring + (size_t)kb * stage_bytes), full0 + 8u * kb);
         for (int kb = pre; kb < nkb; ++kb) {
             const int s = kb % p.stages;
             const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
-            if (!tc_wait(empty0 + 8u * s, ph ^ 1u, p.err, 11)) break;
+            // the stages come back `group` at a time, on the barrier of the group's last stage
+            if (kb % p.group == 0 && !tc_wait(empty0 + 8u * (s + p.group - 1), ph ^ 1u, p.err, 11)) break;
             mbar_expect_tx(full0 + 8u * s, tx);
-            const uint32_t base = smem_u32(smem + (size_t)s * stage_bytes);
+            const uint32_t base = smem_u32(ring + (size_t)s * stage_bytes);
             load_a(kb, base, full0 + 8u * s);
             load_b(kb, base, full0 + 8u * s);
         }
@@ -249,7 +320,7 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
             const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
             if (!tc_wait(full0 + 8u * s, ph, p.err, 12)) break;
             tc_fence_after();
-            const uint32_t base = smem_u32(smem + (size_t)s * stage_bytes);
+            const uint32_t base = smem_u32(ring + (size_t)s * stage_bytes);
             const uint64_t adesc = umma_desc_sw128(base);
             const uint64_t a2desc = umma_desc_sw128(base + a_bytes);
             const uint64_t bdesc = umma_desc_sw128(base + NA * a_bytes);
@@ -260,13 +331,14 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
                 umma_bf16(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, acc);
                 if (MODE == TC_SWIGLU) umma_bf16(tmem_base + (uint32_t)p.Nb, a2desc + 2u * j, bdesc + 2u * j, idesc, acc);
             }
-            umma_commit(empty0 + 8u * s);          // the stage is free once these MMAs have read it
+            // hand stages back only where the loader will refill them, a group at a time
+            if (kb % p.group == p.group - 1 && kb - (p.group - 1) + p.stages < nkb) umma_commit(empty0 + 8u * s);
         }
-        umma_commit(accum);                        // the accumulators are complete
+        umma_commit(accum);                        // the accumulators are complete (at once, if there was no k-block)
     }
     if (warp >= 2) {
         // scale of column b from the partial sums of squares its producer left (inference.cu:24-50)
-        for (int j = tid - 64; j < p.Nb; j += 64) {
+        for (int j = tid - 64; j < p.Nb; j += kTcThreads - 64) {
             float r = 1.0f;
             const int b = b0 + j;
             if (p.ssq_in != nullptr && b < p.B) {
@@ -275,16 +347,30 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
                 r = 1.0f / sqrtf(tot / (float)p.K + p.eps);
             }
             rinv_s[j] = r;
+            if (MODE == TC_QKV) {
+                // position and KV page of the column: fetched here, off the epilogue's critical path
+                int pos = -1, page = 0;
+                if (seq_active(c, b)) {
+                    pos = c.pos[b];
+                    page = q.page_table[(size_t)b * q.pt_stride + pos / kKvBlock];
+                }
+                pos_s[j] = pos;
+                page_s[j] = page;
+            }
         }
     }
     __syncthreads();
 
     // ---- epilogue: all four warps ------------------------------------------------------------------
-    tc_wait(accum, 0, p.err, 13);
-    tc_fence_after();
-    const int row = m0 + warp * 32 + lane;            // output feature of this thread
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // Two groups of four warps: group g takes every other chunk of 16 columns. The epilogue is a chain of
+    // dependent instructions per thread, so its time follows the columns a thread owns.
+    const int wq = warp & 3, grp = warp >> 2;
+    const int row = m0 + wq * 32 + lane;              // output feature of this thread
+    const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
     const bool row_ok = row < p.N;
+    // the columns this CTA finishes: all of the tile, or its share of them
+    const int cb = split > 1 ? (p.Nb * rank) / split : 0;
+    const int ce = split > 1 ? (p.Nb * (rank + 1)) / split : p.Nb;
     // residual values of the first chunk (RESID): fetched one chunk ahead of the stores, because
     // the output may alias the residual and the compiler must keep loads behind earlier stores
     float rnext[16];
@@ -292,8 +378,8 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
     if (MODE == TC_RESID) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const int b = b0 + j;
-            rnext[j] = (row_ok && b < p.B) ? __ldcg(p.resid + (size_t)b * p.N + row) : 0.f;
+            const int b = b0 + cb + 16 * grp + j;
+            rnext[j] = (row_ok && cb + 16 * grp + j < ce && b < p.B) ? ld_cg_f32_now(p.resid + (size_t)b * p.N + row) : 0.f;
         }
         if (p.xg16 != nullptr && row_ok) gain = p.gain_next[row];
     }
@@ -302,85 +388,147 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
     int seg = 0, rloc = 0, kvh = 0, head_w0 = 0, head_wn = 1;
     float gn = 1.0f;
     if (MODE == TC_QKV) {
-        const int wrow = m0 + warp * 32;
+        const int wrow = m0 + wq * 32;
         seg = wrow < seg_q ? 0 : (wrow < seg_k ? 1 : (wrow < seg_v ? 2 : 3));
         rloc = row % q.hd;
         kvh = seg == 1 ? (row - seg_q) / q.hd : (seg == 2 ? (row - seg_k) / q.hd : 0);
         head_wn = q.hd / 32;
-        head_w0 = warp / head_wn * head_wn;
+        head_w0 = grp * 4 + wq / head_wn * head_wn;
         if (q.qk_norm && seg < 2 && row_ok) gn = seg == 0 ? q.gq[row] : q.gk[row - seg_q];
     }
-    for (int c0 = 0; c0 < p.Nb; c0 += 16) {
-        uint32_t v[16], u[16];
-        tmem_ld16_issue(tmem_base + lane_base + (uint32_t)c0, v);
-        if (MODE == TC_SWIGLU) tmem_ld16_issue(tmem_base + lane_base + (uint32_t)(p.Nb + c0), u);
+    // QKV: the chunk of 16 columns a group works on goes through shared memory, so that the per-column work is a
+    // rolled loop: unrolled over the 16 accumulator registers it was 25 KB of code that every CTA ran once, from
+    // a cold instruction cache (8 us per chunk, measured; 1 us this way). The RoPE factors of the chunk's
+    // positions are staged the same way, for the first chunk before the accumulator is waited for.
+    const int r128 = tid & 127;
+    float* st = stage_s + grp * 16 * kTcM;
+    float* rp = rope_s + grp * 16 * kTcM;
+    float gn_other = 1.0f;
+    if (MODE == TC_QKV && q.qk_norm && seg < 2 && (row ^ 1) < p.N) gn_other = seg == 0 ? q.gq[row ^ 1] : q.gk[(row ^ 1) - seg_q];
+    auto stage_rope = [&](int c0) {
+        float t[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int pos = c0 + j < ce ? pos_s[c0 + j] : -1;
+            t[j] = (pos >= 0 && row_ok && seg < 2) ? __ldg(q.rope + (size_t)pos * q.hd + rloc) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) rp[j * kTcM + r128] = t[j];
+    };
+    if (MODE == TC_QKV) stage_rope(cb + 16 * grp);
+    tc_wait(accum, 0, p.err, 13);
+    tc_fence_after();
+    if (tracing) p.trace[3] = globaltimer_ns();          // accumulators complete
+    if (split > 1) {
+        // partial accumulators of all Nb columns into shared memory (the ring is idle: every MMA that read it
+        // has completed), column-major so that a warp writes and later reads 128 consecutive bytes
+        for (int c0 = 16 * grp; c0 < NA * p.Nb; c0 += 32) {
+            uint32_t t[16];
+            tmem_ld16_issue(tmem_base + lane_base + (uint32_t)c0, t);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) part[(size_t)(c0 + j) * kTcM + (tid & 127)] = nkb > 0 ? __uint_as_float(t[j]) : 0.f;
+        }
+        cluster_sync_all();
+    }
+    const uint32_t part_addr = smem_u32(part);
+    // both groups run the same number of rounds; a round past the group's last chunk has all its columns masked
+    for (int c0 = cb + 16 * grp; c0 - 16 * grp < ce; c0 += 32) {
+        float v[16], u[16];
         float rcur[16];
         if (MODE == TC_RESID) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) rcur[j] = rnext[j];
-            if (c0 + 16 < p.Nb) {
+            if (c0 + 32 < ce) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const int b = b0 + c0 + 16 + j;
-                    rnext[j] = (row_ok && b < p.B) ? __ldcg(p.resid + (size_t)b * p.N + row) : 0.f;
+                    const int b = b0 + c0 + 32 + j;
+                    rnext[j] = (row_ok && c0 + 32 + j < ce && b < p.B) ? ld_cg_f32_now(p.resid + (size_t)b * p.N + row) : 0.f;
                 }
             }
         }
-        tmem_ld_wait();
+        if (split > 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { v[j] = 0.f; u[j] = 0.f; }
+            for (int r = 0; r < split; ++r) {
+                const uint32_t base = cluster_map(part_addr, (uint32_t)r) + (uint32_t)(tid & 127) * 4u;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (c0 + j < ce) {
+                        v[j] += cluster_ld_f32(base + (uint32_t)(c0 + j) * (kTcM * 4u));
+                        if (MODE == TC_SWIGLU) u[j] += cluster_ld_f32(base + (uint32_t)(p.Nb + c0 + j) * (kTcM * 4u));
+                    }
+                }
+            }
+        } else {
+            uint32_t t[16], t2[16];
+            const uint32_t cc = (uint32_t)(c0 < ce ? c0 : cb);       // a masked round reads a valid chunk and drops it
+            tmem_ld16_issue(tmem_base + lane_base + cc, t);
+            if (MODE == TC_SWIGLU) tmem_ld16_issue(tmem_base + lane_base + (uint32_t)p.Nb + cc, t2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                v[j] = __uint_as_float(t[j]);
+                if (MODE == TC_SWIGLU) u[j] = __uint_as_float(t2[j]);
+            }
+        }
         if (MODE == TC_QKV) {
             float vv[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) vv[j] = __uint_as_float(v[j]) * rinv_s[c0 + j];
+            for (int j = 0; j < 16; ++j) {
+                vv[j] = c0 + j < ce ? v[j] * rinv_s[c0 + j] : 0.f;
+                st[j * kTcM + r128] = vv[j];
+            }
             if (q.qk_norm) {
                 float sq[16];
 #pragma unroll
                 for (int j = 0; j < 16; ++j) sq[j] = (seg < 2 && row_ok) ? vv[j] * vv[j] : 0.f;
                 const float tot = warp_colsum16(sq, lane);
                 if (!(lane & 1)) head_s[warp * 16 + ((lane >> 1) & 15)] = tot;
-                __syncthreads();
+            }
+            group_sync(grp);
+            const float inv_hd = 1.0f / (float)q.hd;
+#pragma unroll 1
+            for (int j = 0; j < 16; ++j) {
+                const int pos = c0 + j < ce ? pos_s[c0 + j] : -1;
+                if (!row_ok || pos < 0) continue;
+                const int b = b0 + c0 + j;
+                float val = st[j * kTcM + r128];
                 if (seg < 2) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
+                    float oth = st[j * kTcM + (r128 ^ 1)];
+                    if (q.qk_norm) {
                         float t = 0.f;
                         for (int w = 0; w < head_wn; ++w) t += head_s[(head_w0 + w) * 16 + j];
-                        vv[j] = (vv[j] / sqrtf(t / (float)q.hd + q.eps)) * gn;
+                        const float sc = rsqrtf(t * inv_hd + q.eps);
+                        val *= sc * gn;
+                        oth *= sc * gn_other;
                     }
-                }
-                __syncthreads();
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int b = b0 + c0 + j;
-                const float other = __shfl_xor_sync(0xffffffffu, vv[j], 1);
-                if (!row_ok || !seq_active(c, b)) continue;
-                const int pos = c.pos[b];
-                if (seg < 2) {
-                    const float cs = q.rope[(size_t)pos * q.hd + (rloc & ~1)], sn = q.rope[(size_t)pos * q.hd + (rloc | 1)];
-                    const float rot = (rloc & 1) ? fmaf(sn, other, cs * vv[j]) : fmaf(cs, vv[j], -(sn * other));
+                    const float cs = rp[j * kTcM + (r128 & ~1)], sn = rp[j * kTcM + (r128 | 1)];
+                    const float rot = (rloc & 1) ? fmaf(sn, oth, cs * val) : fmaf(cs, val, -(sn * oth));
                     if (seg == 0) {
                         q.qbuf[(size_t)b * q.nq + row] = rot;
                     } else {
-                        const int page = q.page_table[(size_t)b * q.pt_stride + pos / kKvBlock];
-                        const size_t off = (((size_t)page * q.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * q.hd + rloc;
+                        const size_t off = (((size_t)page_s[c0 + j] * q.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * q.hd + rloc;
                         Elem<KVT>::put(reinterpret_cast<KVT*>(q.kpool), off, rot);
                     }
                 } else if (seg == 2) {
-                    const int page = q.page_table[(size_t)b * q.pt_stride + pos / kKvBlock];
-                    const size_t off = (((size_t)page * q.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * q.hd + rloc;
-                    Elem<KVT>::put(reinterpret_cast<KVT*>(q.vpool), off, vv[j]);
+                    const size_t off = (((size_t)page_s[c0 + j] * q.kv_heads + kvh) * kKvBlock + (pos % kKvBlock)) * q.hd + rloc;
+                    Elem<KVT>::put(reinterpret_cast<KVT*>(q.vpool), off, val);
                 } else {
-                    q.gbuf[(size_t)b * q.ng + (row - seg_v)] = 1.0f / (1.0f + expf(-vv[j]));
+                    q.gbuf[(size_t)b * q.ng + (row - seg_v)] = __fdividef(1.0f, 1.0f + __expf(-val));
                 }
             }
+            group_sync(grp);                         // the staging is reused by the next chunk
+            if (c0 + 32 < ce) stage_rope(c0 + 32);
         } else {
             float sq[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const int b = b0 + c0 + j;
                 sq[j] = 0.f;
-                if (row_ok && b < p.B) {
+                if (row_ok && c0 + j < ce && b < p.B) {
                     const size_t o = (size_t)b * p.N + row;
-                    const float acc = __uint_as_float(v[j]);
+                    const float acc = v[j];
                     if (MODE == TC_RAW) {
                         p.y[o] = acc * rinv_s[c0 + j];
                     } else if (MODE == TC_RESID) {
@@ -392,21 +540,22 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
                         }
                     } else {
                         const float ri = rinv_s[c0 + j];
-                        const float g = acc * ri, up = __uint_as_float(u[j]) * ri;
-                        p.h16[o] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);   // inference.cu:262-281
+                        const float g = acc * ri, up = u[j] * ri;
+                        p.h16[o] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * up);   // inference.cu:262-281
                     }
                 }
             }
             if (MODE == TC_RESID && p.xg16 != nullptr) {
                 const float tot = warp_colsum16(sq, lane);
-                if (!(lane & 1)) colsum_s[warp * 256 + c0 + ((lane >> 1) & 15)] = tot;
+                const int col = c0 + ((lane >> 1) & 15);
+                if (!(lane & 1) && col < ce) colsum_s[wq * 256 + col] = tot;
             }
         }
     }
     tc_fence_before();
     __syncthreads();
     if (MODE == TC_RESID && p.ssq_out != nullptr) {
-        for (int j = tid; j < p.Nb; j += 128) {
+        for (int j = cb + tid; j < ce; j += kTcThreads) {
             const int b = b0 + j;
             if (b < p.B)
                 p.ssq_out[(size_t)b * gridDim.x + blockIdx.x] =
@@ -416,6 +565,8 @@ __global__ void __launch_bounds__(128, 1) gemm_tc_kernel(const __grid_constant__
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
     }
+    if (tracing) p.trace[4] = globaltimer_ns();          // epilogue done
+    if (split > 1) cluster_sync_all();      // the partial accumulators stay until every CTA of the cluster has read them
 }
 
 // ---- small kernels around the GEMMs ---------------------------------------------------------------

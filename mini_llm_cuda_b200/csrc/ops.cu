@@ -146,8 +146,10 @@ extern "C" int mlb_op_gemm_bf16(const void* W, const void* W_up_or_null, const v
     GemmTcParams p;
     p.N = N; p.K = K; p.B = batch; p.Nb = Nb;
     const size_t stage_bytes = (size_t)na * kTcM * 128 + (size_t)Nb * 128;
-    p.stages = (int)((200 * 1024) / stage_bytes);
+    p.stages = (int)(kTcRingBytes / stage_bytes);
     if (p.stages > 6) p.stages = 6;
+    p.group = 1;
+    p.trace = nullptr;
     uint32_t cols = 32;
     while (cols < (uint32_t)na * (uint32_t)Nb) cols <<= 1;
     p.tmem_cols = cols;
@@ -156,19 +158,19 @@ extern "C" int mlb_op_gemm_bf16(const void* W, const void* W_up_or_null, const v
     p.nkb_x = 0; p.ssq_in = nullptr; p.ssq_parts = 0; p.eps = 0.f; p.xg16 = nullptr; p.gain_next = nullptr; p.ssq_out = nullptr;
     const StepCtl c0{};
     const QkvPostParams q0{};
-    const size_t smem = (size_t)p.stages * stage_bytes + (2 * (size_t)p.stages + 1) * 8 + 16 + kTcEpiFloats * 4 + 1024;
+    const size_t smem = 1024 + kTcHeadBytes + kTcStageBytes + (size_t)p.stages * stage_bytes;
     dim3 grid((N + kTcM - 1) / kTcM, (batch + Nb - 1) / Nb);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if (W_up_or_null) {
         e = cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e == cudaSuccess) gemm_tc_kernel<TC_SWIGLU, float><<<grid, 128, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
+        if (e == cudaSuccess) gemm_tc_kernel<TC_SWIGLU, float><<<grid, kTcThreads, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
     } else if (resid_or_null) {
         e = cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e == cudaSuccess) gemm_tc_kernel<TC_RESID, float><<<grid, 128, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
+        if (e == cudaSuccess) gemm_tc_kernel<TC_RESID, float><<<grid, kTcThreads, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
     } else {
         e = cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e == cudaSuccess) gemm_tc_kernel<TC_RAW, float><<<grid, 128, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
+        if (e == cudaSuccess) gemm_tc_kernel<TC_RAW, float><<<grid, kTcThreads, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
     }
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);

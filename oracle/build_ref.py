@@ -50,7 +50,16 @@ CONFIGS = {
 }
 
 
-def build(ref_root: str = "/root/reference", only=None) -> list:
+def default_ref_root() -> str:
+    """The reference checkout: $MLB_REFERENCE_ROOT, else a `reference` directory beside this repository."""
+    env = os.environ.get("MLB_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
+
+
+def build(ref_root: str = "", only=None) -> list:
+    ref_root = ref_root or default_ref_root()
     if not os.path.isdir(ref_root) or not os.path.exists(os.path.join(ref_root, "inference.cu")):
         print(f"build_ref: no reference checkout at {ref_root}; keeping prebuilt files in {OUT}")
         return []
@@ -84,4 +93,4 @@ def build(ref_root: str = "/root/reference", only=None) -> list:
 
 
 if __name__ == "__main__":
-    build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    build(sys.argv[1] if len(sys.argv) > 1 else "")

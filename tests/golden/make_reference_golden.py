@@ -85,4 +85,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    # the reference checkout: first argument, else $MLB_REFERENCE_ROOT, else a `reference` directory beside this repository
+    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+        "MLB_REFERENCE_ROOT", os.path.normpath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference"))))
