@@ -56,6 +56,12 @@ int mlb_compat_load_story_context(const char* storiesPath, int storyIndex, int p
 int mlb_compat_run_inference(int L);
 int mlb_compat_run_inference_loop(const char* storiesPath, int storyIndex, int contextPercent,
                                   int skipUserInput, int verboseOutput);
+/* Additions to the reference's loop, which ends only at maxL and prints the text once at the end
+ * (inference_orchestrator.cu:64, :168-183). Stop token: by vocabulary string (after loadVocab) or by id
+ * (token_or_null == NULL; -1 clears it); runInferenceLoop then also ends when that token is generated (it is
+ * kept in the sequence). Streaming: each generated token is printed as soon as it exists. Both default off. */
+int mlb_compat_set_stop_token(const char* token_or_null, int token_id);
+void mlb_compat_set_streaming(int on);
 int mlb_compat_max_context(void);
 int mlb_compat_vocab_size(void);
 int* mlb_compat_tokens(void);                 /* == seqTokenIndices */

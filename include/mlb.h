@@ -131,10 +131,18 @@ int mlb_score_tokens(mlb_session* s, const int32_t* tokens, int len, float* logi
  * (inference_orchestrator.cu:64-160): forward for the pending token of every sequence, pick
  * the next token on the device, append it. in_tokens (nullable) overrides the pending tokens
  * from the host first, as the reference's per-step upload does (:154). out_tokens receives
- * [batch] ids (-1 for a sequence that is at max_context). */
+ * [batch] ids (-1 for a sequence that is at max_context or has drawn the stop token). */
 int mlb_decode_step(mlb_session* s, const mlb_sampling* sampling, const int32_t* in_tokens,
                     int32_t* out_tokens);
-/* n steps back to back without host round trips; out_tokens is [batch][n]. */
+/* Stop token of the session (-1, the default: none). The reference's loop ends only at maxL
+ * (inference_orchestrator.cu:64); a serving loop also ends a sequence at an end-of-text id. The kernel that
+ * appends a picked id compares it with this one and, on a match, takes the sequence out of all later steps
+ * (the id itself is appended and returned); the other sequences of the batch go on. mlb_session_stopped
+ * writes [batch] flags: 1 = the sequence has drawn the stop token since the last reset / prefill. */
+int mlb_session_set_stop_token(mlb_session* s, int token_id);
+int mlb_session_stopped(mlb_session* s, int32_t* out_flags);
+/* n steps back to back without host round trips; out_tokens is [batch][n] (-1 behind the end of a sequence:
+ * max_context reached, or the stop token drawn). */
 int mlb_decode_n(mlb_session* s, const mlb_sampling* sampling, int n, int32_t* out_tokens);
 /* As mlb_decode_n, timing each step with CUDA events on the session's stream; flush_l2
  * writes a buffer larger than L2 before each step, outside the per-step bracket. total_ms

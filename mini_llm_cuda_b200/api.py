@@ -77,6 +77,8 @@ def lib() -> C.CDLL:
         "mlb_prefill": (C.c_int, [vp, i32p, i32p, C.c_int]),
         "mlb_decode_step": (C.c_int, [vp, samp, i32p, i32p]),
         "mlb_decode_n": (C.c_int, [vp, samp, C.c_int, i32p]),
+        "mlb_session_set_stop_token": (C.c_int, [vp, C.c_int]),
+        "mlb_session_stopped": (C.c_int, [vp, i32p]),
         "mlb_decode_timed": (C.c_int, [vp, samp, C.c_int, C.c_int, f32p, f32p, i32p]),
         "mlb_profile_decode": (C.c_int, [vp, samp, C.c_int, C.c_int, C.POINTER(KernelStat), C.c_int, C.POINTER(C.c_int)]),
         "mlb_get_logits": (C.c_int, [vp, f32p]),
@@ -113,6 +115,8 @@ def lib() -> C.CDLL:
         "mlb_compat_load_story_context": (C.c_int, [C.c_char_p, C.c_int, C.c_int]),
         "mlb_compat_run_inference": (C.c_int, [C.c_int]),
         "mlb_compat_run_inference_loop": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int]),
+        "mlb_compat_set_stop_token": (C.c_int, [C.c_char_p, C.c_int]),
+        "mlb_compat_set_streaming": (None, [C.c_int]),
         "mlb_compat_max_context": (C.c_int, []),
         "mlb_compat_vocab_size": (C.c_int, []),
         "mlb_compat_tokens": (i32p, []),
@@ -226,6 +230,15 @@ class Session:
 
     def reset(self):
         check(lib().mlb_session_reset(self._h))
+
+    def set_stop_token(self, token_id: int):
+        """A sequence that picks this id is appended it and takes no further step (-1: none)."""
+        check(lib().mlb_session_set_stop_token(self._h, int(token_id)))
+
+    def stopped(self) -> np.ndarray:
+        out = np.zeros(self.batch, dtype=np.int32)
+        check(lib().mlb_session_stopped(self._h, _ptr(out, C.c_int32)))
+        return out
 
     def prefill(self, prompts: Sequence[Sequence[int]]):
         assert len(prompts) == self.batch

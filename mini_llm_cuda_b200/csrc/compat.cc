@@ -33,6 +33,8 @@ struct CompatState {
     std::unordered_map<std::string, int> vocab_index;
     double last_loop_ms = 0.0;
     int pending_pick = -1;                   // device pick of the last runInference
+    int stop_token = -1;                     // generation also ends when this id is picked (-1: only at maxL)
+    bool streaming = false;                  // print each generated token as it arrives
 };
 
 CompatState& st() {
@@ -80,6 +82,7 @@ int load_model_path(const char* path) {
     }
     s.max_context = c.max_context;
     s.vocab = c.vocab;
+    if (s.stop_token >= c.vocab) s.stop_token = -1;
     s.cached.clear();
     s.probs.assign(static_cast<size_t>(c.vocab), 0.f);
     ensure_token_capacity(c.max_context + 1);
@@ -226,8 +229,8 @@ int runInference(int L) {
     size_t keep = 0;
     const size_t want = static_cast<size_t>(L - 1);
     while (keep < s.cached.size() && keep < want && s.cached[keep] == seqTokenIndices[keep]) ++keep;
-    if (keep != s.cached.size() || s.cached.size() > want) {
-        // the cached prefix diverged (or is longer): ingest the prompt again
+    if (keep != s.cached.size() || s.cached.size() > want || (s.cached.empty() && want >= 2)) {
+        // the cached prefix diverged (or is longer), or nothing is cached yet: ingest the prompt in one call
         int len = L;
         if (mlb_prefill(s.session, seqTokenIndices, &len, s.max_context + 1) != MLB_OK) return 1;
         s.cached.assign(seqTokenIndices, seqTokenIndices + (L - 1));
@@ -261,15 +264,35 @@ int runInferenceLoop(const char* storiesPath, int storyIndex, int contextPercent
         // No host decision between tokens: ingest the prompt, then let the device run the
         // whole loop (the reference's per-token D2H / qsort / H2D, inference_orchestrator.cu:68-154,
         // is replaced by an on-device argmax and a 4-byte id per token).
+        // the device ends the sequence at the stop token only inside this loop: runInference() feeds given tokens
+        if (s.stop_token >= 0) mlb_session_set_stop_token(s.session, s.stop_token);
         int len = L;
         if (mlb_prefill(s.session, seqTokenIndices, &len, maxL + 1) != MLB_OK) { std::printf("Error: %s\n", mlb_last_error()); return 1; }
         const int n = maxL - L;
-        std::vector<int> outv(static_cast<size_t>(n));
-        if (mlb_decode_n(s.session, nullptr, n, outv.data()) != MLB_OK) { std::printf("Error: %s\n", mlb_last_error()); return 1; }
-        for (int i = 0; i < n; ++i) seqTokenIndices[L + i] = outv[i];
-        s.cached.assign(seqTokenIndices, seqTokenIndices + (maxL - 1));
-        L = maxL;
-        generated = n;
+        // Without a stop token and without streaming the whole loop is one call. Otherwise the tokens come a
+        // chunk at a time (one per call when streaming, so that each is printed as soon as it exists), and the
+        // loop ends where the device took the sequence out of the batch.
+        const int chunk = s.streaming ? 1 : (s.stop_token >= 0 ? 64 : n);
+        std::vector<int> outv(static_cast<size_t>(chunk));
+        bool stopped = false;
+        while (L < maxL && !stopped) {
+            const int m = std::min(chunk, maxL - L);
+            const int rc = m == 1 ? mlb_decode_step(s.session, nullptr, nullptr, outv.data()) : mlb_decode_n(s.session, nullptr, m, outv.data());
+            if (rc != MLB_OK) { std::printf("Error: %s\n", mlb_last_error()); return 1; }
+            for (int i = 0; i < m; ++i) {
+                if (outv[i] < 0) { stopped = true; break; }
+                seqTokenIndices[L++] = outv[i];
+                ++generated;
+                if (s.streaming) { print_token(vocabGetToken(outv[i])); std::fflush(stdout); }
+                if (outv[i] == s.stop_token) { stopped = true; break; }
+            }
+        }
+        if (s.streaming) std::printf("\n");
+        s.cached.assign(seqTokenIndices, seqTokenIndices + (L - 1));
+        if (s.stop_token >= 0) {
+            mlb_session_set_stop_token(s.session, -1);
+            if (stopped) s.cached.clear();       // the session holds an ended sequence: the next call ingests again
+        }
     } else {
         while (L < maxL) {
             if (runInference(L) != 0) { std::printf("Error: %s\n", mlb_last_error()); return 1; }
@@ -303,6 +326,8 @@ int runInferenceLoop(const char* storiesPath, int storyIndex, int contextPercent
             seqTokenIndices[L] = next;
             ++L;
             ++generated;
+            if (s.streaming && !verboseOutput) { print_token(vocabGetToken(next)); std::fflush(stdout); }
+            if (next == s.stop_token) { std::printf("\nStop token reached.\n"); break; }
             if (verboseOutput) std::printf("\n[Token added. Total context: %d tokens, generated: %d]\n", L, generated);
         }
     }
@@ -329,6 +354,14 @@ int mlb_compat_run_inference(int L) { return runInference(L); }
 int mlb_compat_run_inference_loop(const char* p, int i, int pct, int skip, int verbose) {
     return runInferenceLoop(p, i, pct, skip != 0, verbose != 0);
 }
+int mlb_compat_set_stop_token(const char* token_or_null, int token_id) {
+    CompatState& s = st();
+    if (token_or_null) token_id = vocabLookup(token_or_null);
+    if (token_or_null && token_id < 0) return MLB_E_INVALID;
+    s.stop_token = token_id < 0 ? -1 : token_id;
+    return MLB_OK;
+}
+void mlb_compat_set_streaming(int on) { st().streaming = on != 0; }
 int mlb_compat_max_context(void) { return st().max_context; }
 int mlb_compat_vocab_size(void) { return st().vocab; }
 int* mlb_compat_tokens(void) { return seqTokenIndices; }

@@ -435,6 +435,8 @@ struct mlb_session {
     std::vector<void*> allocs;
     // host mirrors
     std::vector<int> h_pos;
+    std::vector<char> h_stopped;            // the sequence drew the stop token: it takes no further step
+    int stop_token = -1;
     std::vector<int> h_table;
     bool table_dirty = true;
     bool have_logits = false;
@@ -537,6 +539,23 @@ static void free_session(mlb_session* s) {
     delete s;
 }
 
+// Host mirror of seq_active for the decode chains.
+static bool seq_live(const mlb_session* s, int b) { return s->h_pos[b] < s->max_ctx && !s->h_stopped[b]; }
+// After a decode call returned `n` ids of sequence b (ring order): advance the mirror, stop at the stop token,
+// blank what lies behind it.
+static void note_outputs(mlb_session* s, int b, int32_t* out, int n) {
+    int room = seq_live(s, b) ? std::min(n, s->max_ctx - s->h_pos[b]) : 0;
+    for (int i = 0; i < room; ++i) {
+        if (s->stop_token >= 0 && out[i] == s->stop_token) {
+            room = i + 1;
+            s->h_stopped[b] = 1;
+            break;
+        }
+    }
+    for (int i = room; i < n; ++i) out[i] = -1;
+    s->h_pos[b] += room;
+}
+
 static StepCtl make_ctl(mlb_session* s, int kind) {
     StepCtl c;
     c.B = s->B;
@@ -544,6 +563,7 @@ static StepCtl make_ctl(mlb_session* s, int kind) {
     c.pos = s->pos;
     c.tok = s->tok;
     c.limit = kind == CHAIN_PREFILL ? s->limit_prefill : s->limit_decode;
+    c.stop_token = kind == CHAIN_PREFILL ? -1 : s->stop_token;
     c.prompt = kind == CHAIN_PREFILL ? s->prompt : nullptr;
     c.prompt_stride = s->max_ctx;
     c.out_ring = s->out_ring;
@@ -900,7 +920,7 @@ struct Chain {
                 if (rec) {
                     uint64_t kvb = 0, fl = 0;
                     for (int b = 0; b < B; ++b) {
-                        if (s->h_pos[b] >= s->max_ctx) continue;
+                        if (!seq_live(s, b)) continue;
                         kvb += 2ull * cfg.kv_heads * cfg.head_dim * sizeof(KVT) * (s->h_pos[b] + 1);
                         fl += 4ull * cfg.heads * cfg.head_dim * (s->h_pos[b] + 1);
                     }
@@ -1024,7 +1044,7 @@ struct Chain {
                 if (rec) {
                     uint64_t kvb = 0, fl = 0;
                     for (int b = 0; b < B; ++b) {
-                        if (s->h_pos[b] >= s->max_ctx) continue;
+                        if (!seq_live(s, b)) continue;
                         kvb += 2ull * cfg.kv_heads * cfg.head_dim * sizeof(KVT) * (s->h_pos[b] + 1);
                         fl += 4ull * cfg.heads * cfg.head_dim * (s->h_pos[b] + 1);
                     }
@@ -1561,7 +1581,7 @@ static int grow_pages(mlb_session* s, int extra_steps) {
     for (auto* p : s->kpool) if (p) has_attn = true;
     if (!has_attn) return MLB_OK;
     for (int b = 0; b < s->B; ++b) {
-        int want = std::min(s->h_pos[b] + extra_steps, s->max_ctx);
+        int want = s->h_stopped[b] ? s->h_pos[b] : std::min(s->h_pos[b] + extra_steps, s->max_ctx);
         size_t before = s->alloc.seq_pages[b].size();
         int rc = kv_ensure(&s->alloc, b, want, kKvBlock);
         if (s->alloc.seq_pages[b].size() != before) s->table_dirty = true;
@@ -1680,6 +1700,7 @@ static int session_create(mlb_model* m, int batch, int max_context, int kv_block
     s->alloc.seq_pages.assign(batch, {});
     for (int p = s->kv_pages - 1; p >= 0; --p) s->alloc.free_list.push_back(p);
     s->h_pos.assign(batch, 0);
+    s->h_stopped.assign(batch, 0);
     s->h_table.assign(B * s->max_pages, 0);
     std::vector<int> lim(batch, max_context);
     SCU(cudaMemcpy(s->limit_decode, lim.data(), B * 4, cudaMemcpyHostToDevice));
@@ -1734,6 +1755,12 @@ extern "C" int mlb_session_reset(mlb_session* s) {
     CU(cudaMemsetAsync(s->tok, 0, B * 4, s->stream));
     CU(cudaMemsetAsync(s->limit_prefill, 0, B * 4, s->stream));
     CU(cudaMemsetAsync(s->out_idx, 0, B * 4, s->stream));
+    {
+        // a sequence that stopped had its decode limit lowered on the device
+        const std::vector<int> lim(B, s->max_ctx);
+        CU(cudaMemcpyAsync(s->limit_decode, lim.data(), B * 4, cudaMemcpyHostToDevice, s->stream));
+        CU(cudaStreamSynchronize(s->stream));
+    }
     const mlb_config& c = s->m->cfg;
     for (int i = 0; i < c.layers; ++i)
         if (s->state[i]) CU(cudaMemsetAsync(s->state[i], 0, B * c.heads * c.dn_value_dim * c.dn_key_dim * 4, s->stream));
@@ -1742,6 +1769,7 @@ extern "C" int mlb_session_reset(mlb_session* s) {
         for (int pg : s->alloc.seq_pages[b]) s->alloc.free_list.push_back(pg);
         s->alloc.seq_pages[b].clear();
         s->h_pos[b] = 0;
+        s->h_stopped[b] = 0;
     }
     s->table_dirty = true;
     s->have_logits = false;
@@ -1924,6 +1952,26 @@ extern "C" int mlb_score_tokens(mlb_session* s, const int32_t* tokens, int len, 
     return rc2;
 }
 
+extern "C" int mlb_session_set_stop_token(mlb_session* s, int token_id) {
+    if (!s) return fail(MLB_E_INVALID, "null session");
+    if (token_id >= s->m->cfg.vocab) return fail(MLB_E_INVALID, "stop token %d is outside the vocabulary of %d", token_id, s->m->cfg.vocab);
+    if (token_id < 0) token_id = -1;
+    if (token_id == s->stop_token) return MLB_OK;
+    CU(cudaSetDevice(s->m->device));
+    CU(cudaStreamSynchronize(s->stream));
+    // the id is an argument of the captured launches: capture again on next use
+    for (auto& g : s->graphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
+    for (auto& g : s->tgraphs) if (g) { cudaGraphExecDestroy(g); g = nullptr; }
+    s->stop_token = token_id;
+    return MLB_OK;
+}
+
+extern "C" int mlb_session_stopped(mlb_session* s, int32_t* out_flags) {
+    if (!s || !out_flags) return fail(MLB_E_INVALID, "null argument");
+    for (int b = 0; b < s->B; ++b) out_flags[b] = s->h_stopped[b] ? 1 : 0;
+    return MLB_OK;
+}
+
 namespace mlb {
 // Shared body of the decode entry points. step_ms != null times each step.
 static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int32_t* in_tokens, int32_t* out_tokens,
@@ -1933,8 +1981,8 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
     CU(cudaSetDevice(s->m->device));
     const int B = s->B;
     bool any = false;
-    for (int b = 0; b < B; ++b) any = any || s->h_pos[b] < s->max_ctx;
-    if (!any) return fail(MLB_E_CONTEXT_FULL, "every sequence is at max_context %d", s->max_ctx);
+    for (int b = 0; b < B; ++b) any = any || seq_live(s, b);
+    if (!any) return fail(MLB_E_CONTEXT_FULL, "every sequence is at max_context %d or has drawn the stop token", s->max_ctx);
     if (n > s->max_ctx) n = std::min(n, s->max_ctx);
     int kind, rc;
     if ((rc = apply_sampling(s, sp, &kind))) return rc;
@@ -1951,12 +1999,14 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
         if ((rc = ensure_token_graph(s, kind, in_tokens != nullptr))) return rc;
         CU(cudaGraphLaunch(s->tgraphs[kind * 2 + (in_tokens ? 1 : 0)], s->stream));
         CU(cudaStreamSynchronize(s->stream));
-        for (int b = 0; b < B; ++b) out_tokens[b] = s->h_pos[b] < s->max_ctx ? s->pinned_out[b] : -1;
-        for (int b = 0; b < B; ++b) s->h_pos[b] = std::min(s->h_pos[b] + 1, s->max_ctx);
+        for (int b = 0; b < B; ++b) {
+            out_tokens[b] = s->pinned_out[b];
+            note_outputs(s, b, &out_tokens[b], 1);
+        }
         s->have_logits = true;
         return check_err_readback(s);
     }
-    if (n == 1 && !step_ms && B == 1 && (s->use_grid || s->use_lean) && s->h_pos[0] < s->max_ctx) {
+    if (n == 1 && !step_ms && B == 1 && (s->use_grid || s->use_lean) && seq_live(s, 0)) {
         // The one-token call of the single-kernel step: the pending id travels as a launch argument, the
         // kernel that advances the sequence writes the picked id and the error word to pinned host memory,
         // and the host polls that word instead of synchronising the stream (which costs 5-10 us more).
@@ -1976,7 +2026,7 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
         if (*word == -2) CU(cudaStreamSynchronize(s->stream));       // a wait ran out on the device, or the launch failed late
         if (*word == -2) return fail(MLB_E_CUDA, "the decode step ended without a token");
         out_tokens[0] = *word;
-        s->h_pos[0] = std::min(s->h_pos[0] + 1, s->max_ctx);
+        note_outputs(s, 0, &out_tokens[0], 1);
         s->have_logits = true;
         return check_err_readback(s);
     }
@@ -2005,22 +2055,19 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
         // one id per sequence: gather through the pinned buffer
         CU(cudaMemcpy2DAsync(s->pinned_tok, 4, s->out_ring, (size_t)s->max_ctx * 4, 4, B, cudaMemcpyDeviceToHost, s->stream));
         CU(cudaStreamSynchronize(s->stream));
-        for (int b = 0; b < B; ++b) out_tokens[b] = s->h_pos[b] < s->max_ctx ? s->pinned_tok[b] : -1;
+        for (int b = 0; b < B; ++b) out_tokens[b] = s->pinned_tok[b];
     } else {
         std::vector<int> ring((size_t)B * n);
         CU(cudaMemcpy2DAsync(ring.data(), (size_t)n * 4, s->out_ring, (size_t)s->max_ctx * 4, (size_t)n * 4, B, cudaMemcpyDeviceToHost, s->stream));
         CU(cudaStreamSynchronize(s->stream));
-        for (int b = 0; b < B; ++b) {
-            int room = std::max(0, s->max_ctx - s->h_pos[b]);
-            for (int i = 0; i < n; ++i) out_tokens[(size_t)b * n + i] = i < room ? ring[(size_t)b * n + i] : -1;
-        }
+        std::memcpy(out_tokens, ring.data(), ring.size() * 4);
     }
     if (step_ms) {
         for (int i = 0; i < n; ++i) CU(cudaEventElapsedTime(&step_ms[i], ev[2 * i], ev[2 * i + 1]));
         if (total_ms) CU(cudaEventElapsedTime(total_ms, ev[0], ev[2 * (size_t)n - 1]));
         for (auto& e : ev) cudaEventDestroy(e);
     }
-    for (int b = 0; b < B; ++b) s->h_pos[b] = std::min(s->h_pos[b] + n, s->max_ctx);
+    for (int b = 0; b < B; ++b) note_outputs(s, b, &out_tokens[(size_t)b * n], n);
     s->have_logits = true;
     return check_err_readback(s);
 }
@@ -2050,16 +2097,26 @@ extern "C" int mlb_profile_decode(mlb_session* s, const mlb_sampling* sp, int n,
     rec.st = s->stream;
     for (int i = 0; i < n; ++i) {
         bool any = false;
-        for (int b = 0; b < s->B; ++b) any = any || s->h_pos[b] < s->max_ctx;
+        for (int b = 0; b < s->B; ++b) any = any || seq_live(s, b);
         if (!any) break;
         if (flush_l2) {
             l2_flush_kernel<<<1184, 256, 0, s->stream>>>(s->flush_buf, s->flush_n, (float)i);
             CU(cudaGetLastError());
         }
         if ((rc = chain_run(s, kind, &rec, nullptr))) return rc;
-        for (int b = 0; b < s->B; ++b) s->h_pos[b] = std::min(s->h_pos[b] + 1, s->max_ctx);
+        for (int b = 0; b < s->B; ++b) if (seq_live(s, b)) s->h_pos[b] += 1;
     }
     CU(cudaStreamSynchronize(s->stream));
+    if (s->stop_token >= 0) {
+        // no ids came back: take positions and who stopped from the device
+        std::vector<int> dp(s->B), dl(s->B);
+        CU(cudaMemcpy(dp.data(), s->pos, (size_t)s->B * 4, cudaMemcpyDeviceToHost));
+        CU(cudaMemcpy(dl.data(), s->limit_decode, (size_t)s->B * 4, cudaMemcpyDeviceToHost));
+        for (int b = 0; b < s->B; ++b) {
+            s->h_pos[b] = std::min(dp[b], s->max_ctx);
+            s->h_stopped[b] = dl[b] < s->max_ctx;
+        }
+    }
     s->have_logits = true;
     int count = 0;
     for (auto& r : rec.recs) {
@@ -2120,7 +2177,7 @@ extern "C" int mlb_session_step_bytes(mlb_session* s, uint64_t* weights, uint64_
     uint64_t kvb = 0, st = 0, rw = 0;
     const uint64_t kv_elt = elt_size(c.kv_dtype), w_elt = elt_size(c.weight_dtype), p_elt = elt_size(ple_dtype(c.weight_dtype));
     for (int b = 0; b < s->B; ++b) {
-        if (s->h_pos[b] >= s->max_ctx) continue;
+        if (!seq_live(s, b)) continue;
         for (int i = 0; i < c.layers; ++i) {
             if (c.layer_types[i] == MLB_LAYER_ATTENTION) kvb += 2ull * c.kv_heads * c.head_dim * kv_elt * (s->h_pos[b] + 1);
             else st += 2ull * c.heads * c.dn_key_dim * c.dn_value_dim * 4;

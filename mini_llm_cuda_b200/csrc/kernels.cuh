@@ -116,7 +116,8 @@ struct StepCtl {
     int vocab;
     int* pos;            // [B] position of the pending token == tokens consumed so far
     int* tok;            // [B] pending token
-    const int* limit;    // [B] a sequence takes part in the step iff pos < limit
+    int* limit;          // [B] a sequence takes part in the step iff pos < limit
+    int stop_token;      // a sequence that picks this id leaves the batch after appending it (limit = pos); -1 = none
     // prompt forcing (prefill chain) and output ring (decode chain)
     const int* prompt;   // [B][prompt_stride] or null
     int prompt_stride;
@@ -153,6 +154,7 @@ __device__ __forceinline__ void advance_seq(const StepCtl& c, int b, int sampled
             __threadfence_system();
         }
         if (c.host_out != nullptr) c.host_out[b] = sampled;
+        if (sampled == c.stop_token) c.limit[b] = p + 1;          // end of this sequence: later steps skip it
     }
     c.pos[b] = p + 1;
 }

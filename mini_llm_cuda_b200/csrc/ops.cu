@@ -79,7 +79,7 @@ int run_attn(void* scratch, const void* kpool, const void* vpool, int kv_dtype, 
     CU(cudaMemsetAsync(sc.limit, 0x7f, (size_t)batch * 4, st));          // 0x7f7f7f7f: every sequence takes part
     StepCtl c;
     c.B = batch; c.vocab = 0;
-    c.pos = const_cast<int*>(positions); c.tok = nullptr; c.limit = sc.limit;
+    c.pos = const_cast<int*>(positions); c.tok = nullptr; c.limit = sc.limit; c.stop_token = -1;
     c.prompt = nullptr; c.prompt_stride = 0; c.out_ring = nullptr; c.out_idx = nullptr; c.out_cap = 0;
     c.tok_src = nullptr; c.host_out = nullptr; c.host_err = nullptr; c.dev_err = nullptr;
     AttnParams p;

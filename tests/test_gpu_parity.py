@@ -610,6 +610,58 @@ def test_cfg0_fp32_64_greedy(api, tmp_path):
     model.close()
 
 
+@pytest.mark.parametrize("weight_dtype,batch", [("float32", 1), ("float32", 2), ("bfloat16", 1), ("bfloat16", 4)])
+def test_stop_token_takes_a_sequence_out_of_the_batch(api, tmp_path, weight_dtype, batch):
+    """A sequence that picks the session's stop token keeps it and takes no further step; the other sequences
+    of the batch are not disturbed. Checked against the same session's free run (and, for fp32, the oracle)
+    on the single-kernel step (batch 1), the GEMV chain (batch 2) and the tensor-core step (batch 4)."""
+    spec = small(layers=4, layer_types=periodic_layer_types(4, 2), ple_dim=64 if weight_dtype == "bfloat16" else 32,
+                 weight_dtype=weight_dtype, kv_dtype="bfloat16" if weight_dtype == "bfloat16" else "float32")
+    path = write_model(tmp_path, spec, seed=31)
+    prompts = random_prompts(spec.vocab, [9 + 5 * b for b in range(batch)], seed=32)
+    n = 24
+    model = api.Model(path)
+    sess = api.Session(model, batch)
+    sess.prefill(prompts)
+    free = sess.decode(n)                                  # [batch][n], no stop token
+    if weight_dtype == "float32":
+        oracle = load_oracle(path)
+        for b in range(batch):
+            assert free[b].tolist() == oracle_rollout(oracle, prompts[b], n)[0].tolist()
+    stop = int(free[batch - 1][7])                         # the last sequence draws it at step 7 (or earlier)
+    first = [next((i for i, t in enumerate(free[b].tolist()) if t == stop), None) for b in range(batch)]
+    assert first[batch - 1] is not None and first[batch - 1] <= 7
+    sess.set_stop_token(stop)
+    sess.prefill(prompts)
+    assert not sess.stopped().any()
+    part = sess.decode(10)                                 # the stop survives a call boundary
+    if sess.stopped().all():
+        with pytest.raises(api.MlbError):
+            sess.decode(n - 10)
+        got = np.concatenate([part, np.full((batch, n - 10), -1, dtype=part.dtype)], axis=1)
+    else:
+        got = np.concatenate([part, sess.decode(n - 10)], axis=1)
+    for b in range(batch):
+        k = n if first[b] is None else first[b] + 1
+        assert got[b][:k].tolist() == free[b][:k].tolist(), b
+        assert (got[b][k:] == -1).all(), b
+        assert int(sess.stopped()[b]) == (0 if first[b] is None else 1)
+        assert int(sess.positions()[b]) == len(prompts[b]) - 1 + k
+    live = [b for b in range(batch) if first[b] is None]
+    if live:
+        nxt = sess.decode_step()                           # the one-token call skips the ended sequences too
+        assert all(int(nxt[b]) == -1 for b in range(batch) if b not in live) and all(int(nxt[b]) >= 0 for b in live)
+    else:
+        with pytest.raises(api.MlbError):
+            sess.decode_step()
+    # a new prompt starts every sequence again; without a stop token the free run comes back
+    sess.set_stop_token(-1)
+    sess.prefill(prompts)
+    assert np.array_equal(sess.decode(n), free)
+    sess.close()
+    model.close()
+
+
 def test_compat_entry_points(api, tmp_path, capfd):
     """The reference's entry points (loadModel / loadVocab / runInferenceLoop / runInference)
     through their C-linkage twins."""
@@ -647,6 +699,23 @@ def test_compat_entry_points(api, tmp_path, capfd):
         assert rc == 0
         toks2 = np.ctypeslib.as_array(L.mlb_compat_tokens(), shape=(64,)).copy()
         assert np.array_equal(toks, toks2)
+        # stop token by vocabulary string, streamed output: the loop ends with that token, printed as it goes
+        stop_at = 15 + 9
+        assert L.mlb_compat_set_stop_token(b"nope", 0) != 0
+        assert L.mlb_compat_set_stop_token(vocab[int(toks[stop_at])].encode(), 0) == 0
+        L.mlb_compat_set_streaming(1)
+        assert "Generation took" in capfd.readouterr().out
+        rc = L.mlb_compat_run_inference_loop(b"./stories.json", 1, 50, 1, 0)
+        assert rc == 0
+        first = 15 + toks[15:].tolist().index(int(toks[stop_at]))
+        toks3 = np.ctypeslib.as_array(L.mlb_compat_tokens(), shape=(64,)).copy()
+        assert toks3[:first + 1].tolist() == toks[:first + 1].tolist()
+        out = capfd.readouterr().out
+        assert f"Generated {first + 1 - 15} new tokens" in out and f"Final sequence length: {first + 1} tokens" in out
+        streamed = "".join("[\\n]" if vocab[t] == "\n" else vocab[t] for t in toks[15:first + 1].tolist())
+        assert streamed in out.split("Starting text generation")[1].split("Generation took")[0]
+        L.mlb_compat_set_stop_token(None, -1)
+        L.mlb_compat_set_streaming(0)
         # runInference(L): probabilities of column L-1
         assert L.mlb_compat_run_inference(15) == 0
         probs = np.ctypeslib.as_array(L.mlb_compat_last_probs(), shape=(600,)).copy()
@@ -659,4 +728,3 @@ def test_compat_entry_points(api, tmp_path, capfd):
     finally:
         os.chdir(cwd)
         L.mlb_compat_shutdown()
-    assert "Generation took" in capfd.readouterr().out
