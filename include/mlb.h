@@ -117,6 +117,26 @@ void mlb_session_free(mlb_session* s);
  * MLB_E_UNSUPPORTED where they cannot run. */
 int mlb_prefill(mlb_session* s, const int32_t* tokens, const int32_t* lens, int stride);
 
+/* ---- several GPUs of one box ---------------------------------------------------------------------
+ * The reference runs on device 0 only (memory_allocation.cu:329, no cudaSetDevice anywhere). A pool
+ * serves `batch` sequences from n_devices GPUs: every device holds a full replica of the weights and the
+ * KV pages / delta-net state of a contiguous block of the sequences (mlb_shard_range: the first
+ * batch % n_devices devices hold one more); calls run one host thread and one stream per device and
+ * return when all are done. No data crosses between the devices. A device index may repeat (two
+ * shards on one GPU). Arrays are laid out as for a session of `batch` sequences. */
+typedef struct mlb_pool mlb_pool;
+int mlb_shard_range(int n_items, int n_shards, int shard, int* begin, int* end);      /* host only */
+int mlb_pool_new(const char* model_path, const int* devices, int n_devices, int batch, int max_context,
+                 const mlb_config* override_or_null, mlb_pool** out);
+void mlb_pool_free(mlb_pool* p);
+/* Writes device and sequence range of up to `cap` shards; returns the number of shards. */
+int mlb_pool_shards(const mlb_pool* p, int* devices, int* begins, int* ends, int cap);
+int mlb_pool_set_stop_token(mlb_pool* p, int token_id);
+int mlb_pool_prefill(mlb_pool* p, const int32_t* tokens, const int32_t* lens, int stride);
+/* out_tokens [batch][n]; with top-k sampling and no seeds the Philox key of a sequence is its index in
+ * the pool, so the ids do not depend on the number of devices. */
+int mlb_pool_decode_n(mlb_pool* p, const mlb_sampling* sampling, int n, int32_t* out_tokens);
+
 /* Teacher-forced scoring forward: the full-sequence forward of runInference(L)
  * (inference.cu:376-752), whose [V x L] scores the reference's trainer consumes
  * (training_orchestrator.cu:308). logits_out [len][V] fp32 host, row t = prediction after

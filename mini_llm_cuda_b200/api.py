@@ -78,6 +78,13 @@ def lib() -> C.CDLL:
         "mlb_decode_step": (C.c_int, [vp, samp, i32p, i32p]),
         "mlb_decode_n": (C.c_int, [vp, samp, C.c_int, i32p]),
         "mlb_session_set_stop_token": (C.c_int, [vp, C.c_int]),
+        "mlb_shard_range": (C.c_int, [C.c_int, C.c_int, C.c_int, i32p, i32p]),
+        "mlb_pool_new": (C.c_int, [C.c_char_p, i32p, C.c_int, C.c_int, C.c_int, cfgp, C.POINTER(vp)]),
+        "mlb_pool_free": (None, [vp]),
+        "mlb_pool_shards": (C.c_int, [vp, i32p, i32p, i32p, C.c_int]),
+        "mlb_pool_set_stop_token": (C.c_int, [vp, C.c_int]),
+        "mlb_pool_prefill": (C.c_int, [vp, i32p, i32p, C.c_int]),
+        "mlb_pool_decode_n": (C.c_int, [vp, samp, C.c_int, i32p]),
         "mlb_session_stopped": (C.c_int, [vp, i32p]),
         "mlb_decode_timed": (C.c_int, [vp, samp, C.c_int, C.c_int, f32p, f32p, i32p]),
         "mlb_profile_decode": (C.c_int, [vp, samp, C.c_int, C.c_int, C.POINTER(KernelStat), C.c_int, C.POINTER(C.c_int)]),
@@ -335,6 +342,57 @@ class Session:
             self.close()
         except Exception:
             pass
+
+
+class Pool:
+    """`batch` independent sequences sharded over several GPUs of one box (mlb_pool_*)."""
+
+    def __init__(self, path: str, devices: Sequence[int], batch: int, max_context: int = 0, override: Optional[Config] = None):
+        self._h = C.c_void_p()
+        self.batch = batch
+        dev = _i32(list(devices))
+        check(lib().mlb_pool_new(path.encode(), _ptr(dev, C.c_int32), len(dev), batch, max_context,
+                                 C.byref(override) if override is not None else None, C.byref(self._h)))
+
+    def shards(self) -> List[tuple]:
+        d, b, e = (np.zeros(64, dtype=np.int32) for _ in range(3))
+        n = check(lib().mlb_pool_shards(self._h, _ptr(d, C.c_int32), _ptr(b, C.c_int32), _ptr(e, C.c_int32), 64))
+        return [(int(d[i]), int(b[i]), int(e[i])) for i in range(n)]
+
+    def set_stop_token(self, token_id: int):
+        check(lib().mlb_pool_set_stop_token(self._h, int(token_id)))
+
+    def prefill(self, prompts: Sequence[Sequence[int]]):
+        assert len(prompts) == self.batch
+        lens = _i32([len(p) for p in prompts])
+        stride = max(1, int(lens.max()))
+        toks = np.zeros((self.batch, stride), dtype=np.int32)
+        for i, p in enumerate(prompts):
+            toks[i, :len(p)] = p
+        check(lib().mlb_pool_prefill(self._h, _ptr(toks, C.c_int32), _ptr(lens, C.c_int32), stride))
+
+    def decode(self, n: int, sampling: Optional[dict] = None) -> np.ndarray:
+        out = np.empty((self.batch, n), dtype=np.int32)
+        sp, keep = _sampling(sampling, self.batch)
+        check(lib().mlb_pool_decode_n(self._h, C.byref(sp) if sp else None, n, _ptr(out, C.c_int32)))
+        return out
+
+    def close(self):
+        if self._h:
+            lib().mlb_pool_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def shard_range_c(n_items: int, n_shards: int, shard: int) -> tuple:
+    b, e = C.c_int32(), C.c_int32()
+    check(lib().mlb_shard_range(n_items, n_shards, shard, C.byref(b), C.byref(e)))
+    return b.value, e.value
 
 
 class KvAllocator:

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libmini_llm_b200.so")
-SOURCES = ["engine.cu", "grid.cu", "lean.cu", "ops.cu", "model_file.cc", "compat.cc"]
+SOURCES = ["engine.cu", "grid.cu", "lean.cu", "ops.cu", "model_file.cc", "compat.cc", "pool.cc"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

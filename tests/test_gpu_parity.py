@@ -662,6 +662,49 @@ def test_stop_token_takes_a_sequence_out_of_the_batch(api, tmp_path, weight_dtyp
     model.close()
 
 
+@pytest.mark.parametrize("devices", [[0, 0, 0], [0, 1]])
+def test_pool_shards_sequences_over_devices(api, tmp_path, devices):
+    """mlb_pool_*: the sequences of one batch served by several (model, session, host thread) triples give the
+    ids one session gives for the whole batch, greedy and sampled, and a stop token reaches every shard.
+    [0, 0, 0] runs three shards on one GPU (uneven: 7 sequences as 3 + 2 + 2); [0, 1] needs two GPUs."""
+    import torch
+    if max(devices) >= torch.cuda.device_count():
+        pytest.skip("needs %d GPUs" % (max(devices) + 1))
+    spec = small(layers=4, layer_types=periodic_layer_types(4, 2), ple_dim=32)
+    path = write_model(tmp_path, spec, seed=41)
+    batch, n = 7, 12
+    prompts = random_prompts(spec.vocab, [5 + 3 * b for b in range(batch)], seed=42)
+    model = api.Model(path)
+    sess = api.Session(model, batch)
+    sess.prefill(prompts)
+    want = sess.decode(n)
+    samp = {"mode": "top_k", "top_k": 8, "temperature": 0.9}
+    sess.prefill(prompts)
+    want_s = sess.decode(n, samp)
+    sess.close()
+    model.close()
+    pool = api.Pool(path, devices, batch)
+    sh = pool.shards()
+    assert [d for d, _, _ in sh] == devices and sh[0][1] == 0 and sh[-1][2] == batch
+    assert all(sh[i][2] == sh[i + 1][1] for i in range(len(sh) - 1))
+    pool.prefill(prompts)
+    assert np.array_equal(pool.decode(n), want)
+    pool.prefill(prompts)
+    assert np.array_equal(pool.decode(n, samp), want_s)          # default Philox keys are pool-wide sequence indices
+    stop = int(want[batch - 1][5])
+    pool.set_stop_token(stop)
+    pool.prefill(prompts)
+    got = pool.decode(n)
+    for b in range(batch):
+        row = want[b].tolist()
+        k = row.index(stop) + 1 if stop in row else n
+        assert got[b][:k].tolist() == row[:k] and (got[b][k:] == -1).all()
+    pool.close()
+    with pytest.raises(api.MlbError) as e:
+        api.Pool(os.path.join(str(tmp_path), "missing.bin"), devices, batch)
+    assert "device" in str(e.value)
+
+
 def test_compat_entry_points(api, tmp_path, capfd):
     """The reference's entry points (loadModel / loadVocab / runInferenceLoop / runInference)
     through their C-linkage twins."""

@@ -203,3 +203,32 @@ def test_rope_table_bitwise_equals_oracle(api):
     t = api.rope_table(4, 64, 10000.0)
     assert np.all(t[0, 0::2] == 1.0) and np.all(t[0, 1::2] == 0.0)      # position 0: cos 1, sin 0
     assert abs(t[1, 0] - np.cos(1.0)) < 1e-7 and abs(t[1, 1] - np.sin(1.0)) < 1e-7
+
+
+def test_pool_sharding_matches_the_python_sharding_and_refuses_bad_arguments(api):
+    """Host side of the multi-GPU pool without a GPU: the C shard ranges are those of the torchrun driver's
+    shard_range (contiguous, the first n % world shards one longer, together covering every sequence once),
+    and mlb_pool_new turns down argument errors before it touches a device."""
+    import ctypes as C
+    from mini_llm_cuda_b200.sharding import shard_range
+    for n in (0, 1, 7, 8, 64, 255, 256):
+        for world in (1, 2, 3, 4, 8):
+            cover = []
+            for r in range(world):
+                got = api.shard_range_c(n, world, r)
+                assert got == shard_range(n, world, r)
+                cover += list(range(*got))
+            assert cover == list(range(n))
+    with pytest.raises(api.MlbError):
+        api.shard_range_c(8, 4, 4)
+    with pytest.raises(api.MlbError):
+        api.shard_range_c(8, 0, 0)
+    L = api.lib()
+    h = C.c_void_p()
+    dev = np.array([0, -1], dtype=np.int32)
+    ptr = dev.ctypes.data_as(C.POINTER(C.c_int32))
+    assert L.mlb_pool_new(b"nowhere.bin", ptr, 0, 4, 0, None, C.byref(h)) == api.MLB_E_INVALID
+    assert L.mlb_pool_new(b"nowhere.bin", ptr, 2, 4, 0, None, C.byref(h)) == api.MLB_E_INVALID      # negative device
+    assert L.mlb_pool_new(b"nowhere.bin", ptr, 1, 0, 0, None, C.byref(h)) == api.MLB_E_INVALID      # empty batch
+    assert L.mlb_pool_new(None, ptr, 1, 4, 0, None, C.byref(h)) == api.MLB_E_INVALID
+    assert not h
