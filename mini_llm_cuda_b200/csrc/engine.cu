@@ -137,7 +137,7 @@ struct Uploader {
             hsrc = reinterpret_cast<const float*>(src);
         } else {
             hbuf.resize(n);
-            convert_to_f32(src, t.dtype, n, hbuf.data());
+            convert_to_f32(src, t.dtype, n, hbuf.data(), (uint64_t)t.cols);
             hsrc = hbuf.data();
         }
         CU(cudaMemcpy(dstage, hsrc, n * 4, cudaMemcpyHostToDevice));
@@ -179,8 +179,16 @@ struct Uploader {
         if (dt == MLB_DT_FP8_E4M3 && (rc = dev_alloc(reinterpret_cast<void**>(S), (size_t)rows * 4))) return rc;
         size_t off = 0;
         for (auto* t : parts) {
-            if ((rc = stage(*t))) return rc;
-            if ((rc = emit(*t, dt, *W, off, *S))) return rc;
+            if (t->dtype == FD_FP8 && dt == MLB_DT_FP8_E4M3) {
+                // quantised offline: the file's codes and per-row scales are the device's
+                const unsigned char* src = file->data() + t->offset;
+                const size_t n = (size_t)t->rows * t->cols;
+                CU(cudaMemcpy(static_cast<fp8_t*>(*W) + off * (size_t)cols, src, n, cudaMemcpyHostToDevice));
+                CU(cudaMemcpy(*S + off, src + n, (size_t)t->rows * 4, cudaMemcpyHostToDevice));
+            } else {
+                if ((rc = stage(*t))) return rc;
+                if ((rc = emit(*t, dt, *W, off, *S))) return rc;
+            }
             off += t->rows;
         }
         if (total_rows) *total_rows = rows;

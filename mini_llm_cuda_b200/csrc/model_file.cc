@@ -40,6 +40,14 @@ bool parse_meta(const JsonValue& v, TensorDesc* t, std::string* err) {
     if (dtype->str == "float32") { t->dtype = FD_F32; t->nbytes = 4 * n; }
     else if (dtype->str == "float64") { t->dtype = FD_F64; t->nbytes = 8 * n; }
     else if (dtype->str == "bfloat16") { t->dtype = FD_BF16; t->nbytes = 2 * n; }
+    else if (dtype->str == "float8_e4m3") {
+        if (t->ndim != 2) {
+            *err = "tensor '" + t->name + "': float8_e4m3 needs a matrix (codes with one scale per row)";
+            return false;
+        }
+        t->dtype = FD_FP8;
+        t->nbytes = n + 4 * static_cast<uint64_t>(t->rows);
+    }
     else {
         *err = "Unsupported dtype: " + dtype->str;     // load_model.cu:55-57
         return false;
@@ -92,7 +100,25 @@ int read_file(const char* path, std::vector<unsigned char>* out, std::string* er
     return MLB_OK;
 }
 
-void convert_to_f32(const unsigned char* src, FileDtype dt, uint64_t n, float* dst) {
+float e4m3_to_f32(unsigned char code) {
+    const int e = (code >> 3) & 15, m = code & 7;
+    float v;
+    if (e == 15 && m == 7) v = std::nanf("");
+    else if (e == 0) v = std::ldexp(static_cast<float>(m), -9);              // subnormal: m / 8 * 2^-6
+    else v = std::ldexp(1.0f + static_cast<float>(m) / 8.0f, e - 7);
+    return (code & 0x80) ? -v : v;
+}
+
+void convert_to_f32(const unsigned char* src, FileDtype dt, uint64_t n, float* dst, uint64_t cols) {
+    if (dt == FD_FP8) {
+        const uint64_t rows = cols ? n / cols : 0;
+        for (uint64_t r = 0; r < rows; ++r) {
+            float sc;
+            std::memcpy(&sc, src + n + 4 * r, 4);
+            for (uint64_t c = 0; c < cols; ++c) dst[r * cols + c] = e4m3_to_f32(src[r * cols + c]) * sc;
+        }
+        return;
+    }
     if (dt == FD_F32) {
         std::memcpy(dst, src, n * 4);
     } else if (dt == FD_F64) {

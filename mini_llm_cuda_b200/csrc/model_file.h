@@ -10,7 +10,10 @@
 
 namespace mlb {
 
-enum FileDtype { FD_F32 = 0, FD_F64 = 1, FD_BF16 = 2 };
+// FD_FP8: e4m3 codes [rows][cols] followed by one float32 scale per row (value = code * scale[row]); written
+// by the offline converter for the matrices a float8_e4m3 model keeps in that form on the device. The
+// reference's loader knows float32, float64 and bfloat16 only (load_model.cu:24-61).
+enum FileDtype { FD_F32 = 0, FD_F64 = 1, FD_BF16 = 2, FD_FP8 = 3 };
 
 struct TensorDesc {
     std::string name;      // JSON key, e.g. "queryWeights"
@@ -38,7 +41,10 @@ int parse_model_header(const unsigned char* data, uint64_t avail, uint64_t file_
 // Reads the whole file into memory. Returns an mlb_status.
 int read_file(const char* path, std::vector<unsigned char>* out, std::string* err);
 
-// Converts `n` elements at `src` of the given file dtype to float32.
-void convert_to_f32(const unsigned char* src, FileDtype dt, uint64_t n, float* dst);
+// Converts `n` elements at `src` of the given file dtype to float32 (FD_FP8: rows of `cols` codes, the scales
+// behind them).
+void convert_to_f32(const unsigned char* src, FileDtype dt, uint64_t n, float* dst, uint64_t cols = 0);
+// Value of one e4m3 code (no infinities; 0x7f / 0xff are NaN).
+float e4m3_to_f32(unsigned char code);
 
 }  // namespace mlb

@@ -191,7 +191,48 @@ def _to_bf16_bits(a: np.ndarray) -> np.ndarray:
     return (rounded >> np.uint32(16)).astype(np.uint16)
 
 
+def _to_e4m3_bits(x: np.ndarray) -> np.ndarray:
+    """float32 -> e4m3 codes (1 sign, 4 exponent bits with bias 7, 3 mantissa bits; largest finite value 448),
+    round to nearest even, saturating: what __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3) returns."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    sign = (np.signbit(x)).astype(np.uint8) << 7
+    ax = np.minimum(np.abs(x).astype(np.float64), 448.0)
+    mant, exp = np.frexp(ax)                      # ax = mant * 2^exp, mant in [0.5, 1)
+    e = exp - 1                                   # ax = (2 mant) * 2^e
+    normal = ax >= 2.0 ** -6
+    q_n = np.rint((2.0 * mant - 1.0) * 8.0)       # 0..8, ties to even
+    carry = q_n == 8
+    e_n = np.where(carry, e + 1, e)
+    q_n = np.where(carry, 0, q_n)
+    code_n = ((e_n + 7).astype(np.int64) << 3) | q_n.astype(np.int64)
+    code_s = np.rint(ax * 512.0).astype(np.int64)     # subnormals step 2^-9; 8 is the smallest normal
+    code = np.where(normal, code_n, code_s)
+    code = np.minimum(code, 0x7E)
+    return (code.astype(np.uint8) | sign).astype(np.uint8)
+
+
+def _e4m3_values() -> np.ndarray:
+    v = np.zeros(256, dtype=np.float32)
+    for c in range(256):
+        e, m = (c >> 3) & 15, c & 7
+        mag = np.nan if (e == 15 and m == 7) else (m * 2.0 ** -9 if e == 0 else (1.0 + m / 8.0) * 2.0 ** (e - 7))
+        v[c] = -mag if c & 0x80 else mag
+    return v
+
+
+def quantize_fp8_rows(a: np.ndarray):
+    """Per-row e4m3 as the loader's device kernel does it: scale = max|row| / 448 in float32 (1 for an all-zero
+    row), code = e4m3(row / scale). Returns (codes uint8 [rows][cols], scales float32 [rows])."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    amax = np.abs(a).max(axis=1)
+    scale = np.where(amax > 0, amax / np.float32(448.0), np.float32(1.0)).astype(np.float32)
+    return _to_e4m3_bits(a / scale[:, None]), scale
+
+
 def _encode(a: np.ndarray, dtype: str) -> bytes:
+    if dtype == "float8_e4m3":
+        codes, scale = quantize_fp8_rows(a)
+        return codes.tobytes() + scale.astype("<f4").tobytes()
     if dtype == "float32":
         return np.ascontiguousarray(a, dtype="<f4").tobytes()
     if dtype == "float64":
@@ -212,8 +253,12 @@ def write_model_bin(path: str, spec: ModelSpec, weights: dict, file_dtype: str =
     def meta(a, dt):
         return {"shape": [int(s) for s in a.shape], "dtype": dt}
 
-    def dt_of(a):
-        return "float32" if a.ndim == 1 else file_dtype
+    def dt_of(a, name=""):
+        if a.ndim == 1:
+            return "float32"
+        if file_dtype == "float8_e4m3" and name in ("pleTable", "pleProjection"):
+            return "bfloat16"        # the device keeps the per-layer embedding in bf16 under FP8 weights
+        return file_dtype
 
     header = {}
     chunks = []
@@ -237,8 +282,8 @@ def write_model_bin(path: str, spec: ModelSpec, weights: dict, file_dtype: str =
         for b, ext in enumerate(weights.get("ext", [])):
             for name in EXT_NAMES:
                 if name in ext:
-                    ext_list.append({"name": name, "block": b, **meta(ext[name], dt_of(ext[name]))})
-                    chunks.append(_encode(ext[name], dt_of(ext[name])))
+                    ext_list.append({"name": name, "block": b, **meta(ext[name], dt_of(ext[name], name))})
+                    chunks.append(_encode(ext[name], dt_of(ext[name], name)))
         header["ext"] = ext_list
     else:
         assert not any(weights.get("ext", [])), "ext tensors need with_config=True"
@@ -260,6 +305,11 @@ def _decode(buf: bytes, shape, dtype: str) -> np.ndarray:
         a = np.frombuffer(buf, dtype="<f8", count=n).astype(np.float32)     # narrowed as load_model.cu:81-85 does
     elif dtype == "bfloat16":
         a = (np.frombuffer(buf, dtype="<u2", count=n).astype(np.uint32) << 16).view(np.float32)
+    elif dtype == "float8_e4m3":
+        rows = int(shape[0])
+        codes = np.frombuffer(buf, dtype=np.uint8, count=n)
+        scale = np.frombuffer(buf, dtype="<f4", count=rows, offset=n).astype(np.float32)
+        a = (_e4m3_values()[codes].reshape(rows, -1) * scale[:, None]).astype(np.float32).reshape(-1)
     else:
         raise ValueError(f"Unsupported dtype: {dtype}")                      # load_model.cu:55-57
     return a.reshape(shape)
@@ -286,8 +336,11 @@ def read_model_bin(path: str):
     def take(meta):
         nonlocal off
         shape = [int(x) for x in meta["shape"]]
-        nbytes = int(np.prod(shape)) * _DT_SIZE.get(meta["dtype"], 0)
-        if meta["dtype"] not in _DT_SIZE:
+        if meta["dtype"] == "float8_e4m3":
+            nbytes = int(np.prod(shape)) + 4 * shape[0]
+        elif meta["dtype"] in _DT_SIZE:
+            nbytes = int(np.prod(shape)) * _DT_SIZE[meta["dtype"]]
+        else:
             raise ValueError(f"Unsupported dtype: {meta['dtype']}")
         if off + nbytes > len(raw):
             raise ValueError("tensor data exceeds the file")
@@ -307,9 +360,11 @@ def read_model_bin(path: str):
 
 
 def convert_model_bin(src: str, dst: str, heads: int = 0, head_dim: int = 0, kv_heads: int = 0,
-                      file_dtype: str = "float32", weight_dtype: str = "", kv_dtype: str = "",
+                      file_dtype: str = "", weight_dtype: str = "", kv_dtype: str = "",
                       rope_theta: float = 10000.0, rms_eps: float = 1e-8, max_context: int = 1024) -> ModelSpec:
-    """Rewrite ``src`` as a file that carries its own ``config`` (and bf16 tensors if asked).
+    """Rewrite ``src`` as a file that carries its own ``config`` (and bf16 or FP8 tensors if asked: with
+    ``weight_dtype="float8_e4m3"`` the matrices are quantised here, once, to the e4m3 codes and per-row scales
+    the device would otherwise compute at every load, and the file is a quarter of the float32 one).
 
     A file that already has ``config`` keeps it (``weight_dtype`` / ``kv_dtype`` can still be
     changed). A file written for the reference has none: ``heads`` and ``head_dim`` must be given
@@ -340,6 +395,8 @@ def convert_model_bin(src: str, dst: str, heads: int = 0, head_dim: int = 0, kv_
         spec.weight_dtype = weight_dtype
     if kv_dtype:
         spec.kv_dtype = kv_dtype
+    if not file_dtype:
+        file_dtype = "float8_e4m3" if spec.weight_dtype == "float8_e4m3" else "float32"
     write_model_bin(dst, spec, weights, file_dtype=file_dtype, with_config=True)
     return spec
 
@@ -354,7 +411,8 @@ def _main(argv) -> int:
     cv.add_argument("--heads", type=int, default=0)
     cv.add_argument("--head-dim", type=int, default=0)
     cv.add_argument("--kv-heads", type=int, default=0)
-    cv.add_argument("--file-dtype", default="float32", choices=["float32", "float64", "bfloat16"])
+    cv.add_argument("--file-dtype", default="", choices=["", "float32", "float64", "bfloat16", "float8_e4m3"],
+                    help="tensor type in the file; default: float8_e4m3 codes with per-row scales when --weight-dtype is float8_e4m3, else float32")
     cv.add_argument("--weight-dtype", default="", choices=["", "float32", "bfloat16", "float8_e4m3"])
     cv.add_argument("--kv-dtype", default="", choices=["", "float32", "bfloat16"])
     cv.add_argument("--rope-theta", type=float, default=10000.0)

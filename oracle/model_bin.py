@@ -26,6 +26,24 @@ BASE_KEYS = (
 OPTIONAL_KEYS = ("queryRMSGamma", "keyRMSGamma", "gatedQueryWeights")
 
 
+def _e4m3_values() -> np.ndarray:
+    """Value of each of the 256 e4m3 codes: 1 sign, 4 exponent (bias 7), 3 mantissa bits; no infinities."""
+    v = np.zeros(256, dtype=np.float32)
+    for c in range(256):
+        e, m = (c >> 3) & 15, c & 7
+        if e == 15 and m == 7:
+            x = np.nan
+        elif e == 0:
+            x = m * 2.0 ** -9
+        else:
+            x = (1.0 + m / 8.0) * 2.0 ** (e - 7)
+        v[c] = -x if c & 0x80 else x
+    return v
+
+
+_E4M3_VALUES = _e4m3_values()
+
+
 def _read_tensor(buf: bytes, off: int, meta: dict):
     shape = [int(s) for s in meta["shape"]]
     n = int(np.prod(shape)) if shape else 1
@@ -40,6 +58,14 @@ def _read_tensor(buf: bytes, off: int, meta: dict):
         bits = np.frombuffer(buf, dtype="<u2", count=n, offset=off).astype(np.uint32) << 16
         a = bits.view(np.float32)
         nb = 2 * n
+    elif dt == "float8_e4m3":
+        # offline-quantised matrix (no counterpart in the reference's loader): e4m3 codes, then one float32
+        # scale per row; value = code * scale[row]
+        rows = shape[0]
+        codes = np.frombuffer(buf, dtype=np.uint8, count=n, offset=off)
+        scale = np.frombuffer(buf, dtype="<f4", count=rows, offset=off + n).astype(np.float32)
+        a = (_E4M3_VALUES[codes].reshape(rows, -1) * scale[:, None]).astype(np.float32).reshape(-1)
+        nb = n + 4 * rows
     else:
         raise ValueError(f"Unsupported dtype: {dt}")      # load_model.cu:55-57
     if off + nb > len(buf):

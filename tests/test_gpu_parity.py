@@ -705,6 +705,29 @@ def test_pool_shards_sequences_over_devices(api, tmp_path, devices):
     assert "device" in str(e.value)
 
 
+def test_fp8_file_gives_the_weights_the_loader_would_quantise(api, tmp_path):
+    """A model stored as e4m3 codes + per-row scales loads to the same device weights as its float32 file
+    quantised at load: identical logits, bit for bit, at batch 1 (FP8 GEMV / single-kernel step) and batch 4."""
+    spec = small(dim=256, heads=4, kv_heads=2, ple_dim=32, layers=4, layer_types=periodic_layer_types(4, 2),
+                 weight_dtype="float8_e4m3", kv_dtype="bfloat16")
+    p32 = write_model(tmp_path, spec, seed=51, name="f32.bin")
+    p8 = write_model(tmp_path, spec, seed=51, name="fp8.bin", file_dtype="float8_e4m3")
+    for batch in (1, 4):
+        prompts = random_prompts(spec.vocab, [6 + 4 * b for b in range(batch)], seed=52)
+        outs = []
+        for path in (p32, p8):
+            model = api.Model(path)
+            sess = api.Session(model, batch)
+            sess.prefill(prompts)
+            toks = sess.decode(6)
+            outs.append((toks, sess.logits().copy(), model.weight_bytes))
+            sess.close()
+            model.close()
+        assert np.array_equal(outs[0][0], outs[1][0])
+        assert np.array_equal(outs[0][1], outs[1][1])
+        assert outs[0][2] == outs[1][2]
+
+
 def test_compat_entry_points(api, tmp_path, capfd):
     """The reference's entry points (loadModel / loadVocab / runInferenceLoop / runInference)
     through their C-linkage twins."""

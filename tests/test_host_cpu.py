@@ -232,3 +232,49 @@ def test_pool_sharding_matches_the_python_sharding_and_refuses_bad_arguments(api
     assert L.mlb_pool_new(b"nowhere.bin", ptr, 1, 0, 0, None, C.byref(h)) == api.MLB_E_INVALID      # empty batch
     assert L.mlb_pool_new(None, ptr, 1, 4, 0, None, C.byref(h)) == api.MLB_E_INVALID
     assert not h
+
+
+def test_fp8_tensors_in_the_model_file(api, tmp_path):
+    """Offline FP8: the converter's e4m3 encoder is the hardware rounding (checked against torch's cast on a
+    sweep including subnormals, ties and saturation), a float8_e4m3 file holds codes and per-row scales for the
+    matrices (bf16 for the per-layer embedding, float32 for the gains), both readers return code * scale, the
+    C parser accepts the file, and the file is about a quarter of the float32 one."""
+    import torch
+    from mini_llm_cuda_b200 import model_file as mf
+    from oracle.model_bin import read_model_bin as oracle_read
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(50000).astype(np.float32) * s for s in (1e-3, 0.02, 1.0, 60.0, 300.0)] +
+                       [np.array([0, -0.0, 448, -448, 500, -1e9, 2 ** -9, 2 ** -10, 1.5 * 2 ** -9, 2.5 * 2 ** -9, 447.9, 464,
+                                  479.9, 15.5 * 2 ** -9, 2 ** -6, 0.99 * 2 ** -6], dtype=np.float32)])
+    ref = torch.from_numpy(np.clip(x, -448, 448)).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(mf._to_e4m3_bits(x), ref)
+    spec = mf.ModelSpec(dim=128, layers=2, heads=2, head_dim=64, ffn_dim=256, vocab=512, max_context=64, ple_dim=32,
+                        layer_types=mf.periodic_layer_types(2, 2), weight_dtype="float8_e4m3", kv_dtype="bfloat16")
+    w = mf.synth_weights(spec, seed=3)
+    p32, p8 = os.path.join(str(tmp_path), "f32.bin"), os.path.join(str(tmp_path), "fp8.bin")
+    mf.write_model_bin(p32, spec, w)
+    mf.write_model_bin(p8, spec, w, file_dtype="float8_e4m3")
+    assert os.path.getsize(p8) < 0.3 * os.path.getsize(p32)
+    header, back = mf.read_model_bin(p8)
+    assert header["transformerBlocks"][0]["queryWeights"]["dtype"] == "float8_e4m3"
+    assert header["transformerBlocks"][0]["rmsGamma"]["dtype"] == "float32"
+    assert {e["name"]: e["dtype"] for e in header["ext"]}["pleTable"] == "bfloat16"
+    q = w["blocks"][0]["queryWeights"]
+    codes, scale = mf.quantize_fp8_rows(q)
+    want = mf._e4m3_values()[codes] * scale[:, None]
+    assert np.array_equal(back["blocks"][0]["queryWeights"], want)
+    assert np.abs(want - q).max() <= np.abs(q).max() / 16            # 3 mantissa bits
+    assert np.array_equal(oracle_read(p8)["blocks"][0]["queryWeights"], want)
+    cfg, n_params = api.inspect_file(p8)
+    cfg32, n32 = api.inspect_file(p32)
+    assert n_params == n32 and cfg.weight_dtype == api.DT_FP8
+    # the converter: float32 file in, FP8 file out by default when the device type is FP8
+    dst = os.path.join(str(tmp_path), "conv.bin")
+    spec2 = mf.convert_model_bin(p32, dst, weight_dtype="float8_e4m3")
+    assert spec2.weight_dtype == "float8_e4m3" and os.path.getsize(dst) == os.path.getsize(p8)
+    # a truncated FP8 tensor is refused like any other
+    raw = open(p8, "rb").read()
+    short = os.path.join(str(tmp_path), "short.bin")
+    open(short, "wb").write(raw[:len(raw) - 64])
+    with pytest.raises(api.MlbError):
+        api.inspect_file(short)
