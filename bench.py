@@ -333,6 +333,23 @@ def run_reference_arm(args, world, rank, local):
     print(json.dumps(out))
 
 
+class timed_range:
+    """NVTX range around a timed region, so that a profiler can be pointed at the steps of one section
+    (ncu --nvtx --nvtx-include "timed_steps_batch256/"); costs nothing without a profiler."""
+
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        import torch
+        torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        import torch
+        torch.cuda.nvtx.range_pop()
+        return False
+
+
 def timed_loop(sess, prompts, W, K, flush, world, local, samp=None):
     """REPEATS times: prompt, W warm-up steps, barrier, K device-timed steps, barrier. Returns the median
     over the repeats of the max over ranks of the K steps' time (ms) and the per-step times of that repeat."""
@@ -341,7 +358,8 @@ def timed_loop(sess, prompts, W, K, flush, world, local, samp=None):
         sess.prefill(prompts)
         sess.decode(W, samp)
         barrier_sync(world, local)
-        step_ms, _ = sess.decode_timed(K, flush, samp)
+        with timed_range(f"timed_steps_batch{sess.batch}"):
+            step_ms, _ = sess.decode_timed(K, flush, samp)
         barrier_sync(world, local)
         mine = float(step_ms.sum()) if flush else sess.last_total_ms
         totals.append(max_over_ranks(mine, world, local))

@@ -1153,33 +1153,59 @@ __device__ __forceinline__ uint32_t float_order_key(float f) {
 }
 
 constexpr int kSampleCap = 1024;       // max candidates kept in shared memory
+constexpr int kSampleKeys = 8192;      // order keys of the first logits kept in shared memory between the passes
 
+__device__ __forceinline__ float float_from_order_key(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+
+// Temperature / top-k / Philox pick of one sequence per CTA (no counterpart in the reference, whose loop
+// is greedy: inference_orchestrator.cu:77-84). The k largest logits are found by a radix select over
+// order-preserving keys, most significant byte first. The keys of the first kSampleKeys logits are computed
+// once (one division each) and kept in shared memory; a warp adds to a histogram bin once per distinct bin
+// (__match_any_sync) - logits share their leading byte, and 8192 atomics on three or four words were most of
+// the kernel's 52 us at 256 sequences.
 static __global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, SampleParams p) {
     const int b = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     if (!seq_active(c, b)) return;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31;
     const float* lg = p.logits + (size_t)b * p.V;
     const float T = p.temperature;
     const int k = min(p.top_k, min(p.V, kSampleCap));
     __shared__ uint32_t hist[256];
     __shared__ uint32_t s_prefix, s_mask, s_need;
+    __shared__ uint32_t skey[kSampleKeys];
     __shared__ float cval[kSampleCap];
     __shared__ int cidx[kSampleCap];
     __shared__ int s_count, s_overflow;
     if (tid == 0) { s_prefix = 0; s_mask = 0; s_need = (uint32_t)k; }
     __syncthreads();
-    // radix select, most significant byte first: after the passes s_prefix is the key of the
-    // k-th largest element.
+    // after the four passes s_prefix is the key of the k-th largest element
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
         hist[tid] = 0;
         __syncthreads();
         const uint32_t prefix = s_prefix, mask = s_mask;
-        for (int i = tid; i < p.V; i += blockDim.x) {
-            uint32_t key = float_order_key(lg[i] / T);
-            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1u);
+        for (int base = 0; base < p.V; base += 256) {
+            const int i = base + tid;
+            uint32_t key = 0;
+            if (i < p.V) {
+                if (pass == 0 || i >= kSampleKeys) {
+                    key = float_order_key(lg[i] / T);
+                    if (i < kSampleKeys) skey[i] = key;
+                } else {
+                    key = skey[i];
+                }
+            }
+            const bool ok = i < p.V && (key & mask) == prefix;
+            const unsigned act = __ballot_sync(0xffffffffu, ok);
+            if (ok) {
+                const uint32_t bin = (key >> shift) & 0xffu;
+                const unsigned peers = __match_any_sync(act, bin);
+                if (lane == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
+            }
         }
         __syncthreads();
         if (tid == 0) {
@@ -1199,10 +1225,10 @@ static __global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, Samp
     if (tid == 0) { s_count = 0; s_overflow = 0; }
     __syncthreads();
     for (int i = tid; i < p.V; i += blockDim.x) {
-        float v = lg[i] / T;
-        if (float_order_key(v) >= kth) {
+        const uint32_t key = i < kSampleKeys ? skey[i] : float_order_key(lg[i] / T);
+        if (key >= kth) {
             int slot = atomicAdd(&s_count, 1);
-            if (slot < kSampleCap) { cval[slot] = v; cidx[slot] = i; } else s_overflow = 1;
+            if (slot < kSampleCap) { cval[slot] = float_from_order_key(key); cidx[slot] = i; } else s_overflow = 1;
         }
     }
     __syncthreads();
@@ -1245,17 +1271,34 @@ static __global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, Samp
             __syncthreads();
         }
     }
+    // the exponentials in parallel, their sums by one thread in descending order (the order is part of the result)
+    const int kk = min(k, n);
+    {
+        const float v0 = cval[0];
+        float e[(kSampleCap + 255) / 256];
+#pragma unroll
+        for (int r = 0; r < (kSampleCap + 255) / 256; ++r) {
+            const int j = tid + 256 * r;
+            e[r] = j < kk ? expf(cval[j] - v0) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < (kSampleCap + 255) / 256; ++r) {
+            const int j = tid + 256 * r;
+            if (j < kk) cval[j] = e[r];
+        }
+        __syncthreads();
+    }
     if (tid == 0) {
-        int kk = min(k, n);
-        float v0 = cval[0], total = 0.f;
-        for (int j = 0; j < kk; ++j) total += expf(cval[j] - v0);
+        float total = 0.f;
+        for (int j = 0; j < kk; ++j) total += cval[j];
         unsigned long long seed = p.seeds[b];
         uint32_t w0 = philox_first_word((uint32_t)(c.pos[b] + 1), (uint32_t)(seed & 0xffffffffull), (uint32_t)(seed >> 32));
         float u = (float)(w0 >> 8) * (1.0f / 16777216.0f);
         float target = u * total, cum = 0.f;
         int pick = kk - 1;
         for (int j = 0; j < kk; ++j) {
-            cum += expf(cval[j] - v0);
+            cum += cval[j];
             if (cum > target) { pick = j; break; }
         }
         advance_seq(c, b, cidx[pick]);
