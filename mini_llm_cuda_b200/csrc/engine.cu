@@ -826,7 +826,7 @@ struct Chain {
         if (rec) {
             uint64_t w, kv, st, rows;
             mlb_session_step_bytes(s, &w, &kv, &st, &rows);
-            if ((rc = rec->begin("grid_decode_step", w + kv + st + rows, 0))) return rc;
+            if ((rc = rec->begin(s->use_lean ? "lean_decode_step" : "grid_decode_step", w + kv + st + rows, 0))) return rc;
         }
         if (s->use_lean) {
             LeanParams lp = s->lean;
