@@ -108,9 +108,6 @@ struct mlb_model {
     std::vector<void*> allocs;
     // FP8 models: the same weights as bf16 (code * row scale, rounded), made on first use for the
     // tensor-core steps that consume a prompt as columns; shares gains, RoPE table and PLE tensors
-    mlb_model* bf16_view = nullptr;
-    bool bf16_view_failed = false;
-    std::mutex view_mu;
 };
 
 namespace mlb {
@@ -220,60 +217,10 @@ static int validate_for_kernels(const mlb_config& c) {
 static void free_model(mlb_model* m) {
     if (!m) return;
     cudaSetDevice(m->device);
-    if (m->bf16_view) free_model(m->bf16_view);
     for (void* p : m->allocs) cudaFree(p);
     delete m;
 }
 
-// The model whose projections the tensor-core steps can read: the model itself (bf16), or its bf16
-// view (FP8, built here on first use: 2 bytes per weight of extra device memory); null for fp32.
-static mlb_model* model_for_tc(mlb_model* m) {
-    if (m->cfg.weight_dtype == MLB_DT_BF16) return m;
-    if (m->cfg.weight_dtype != MLB_DT_FP8_E4M3) return nullptr;
-    std::lock_guard<std::mutex> lock(m->view_mu);
-    if (m->bf16_view || m->bf16_view_failed) return m->bf16_view;
-    cudaSetDevice(m->device);
-    mlb_model* v = new mlb_model();
-    v->cfg = m->cfg;
-    v->cfg.weight_dtype = MLB_DT_BF16;
-    v->device = m->device;
-    v->g_final = m->g_final;
-    v->rope = m->rope;
-    v->layers = m->layers;
-    bool ok = true;
-    uint64_t n_rows = 0;
-    auto widen = [&](const void* src, const float* scale, int rows, int cols) -> void* {
-        if (!ok || !src) return nullptr;
-        n_rows += (uint64_t)rows;
-        void* dst = nullptr;
-        if (cudaMalloc(&dst, (size_t)rows * cols * 2) != cudaSuccess) { cudaGetLastError(); ok = false; return nullptr; }
-        v->allocs.push_back(dst);
-        v->weight_bytes += (uint64_t)rows * cols * 2;
-        dequant_fp8_rows_kernel<<<(rows + 7) / 8, 256>>>(static_cast<const fp8_t*>(src), scale, static_cast<bf16_t*>(dst), rows, cols);
-        return dst;
-    };
-    const mlb_config& c = m->cfg;
-    v->E = widen(m->E, m->Es, c.vocab, c.dim);
-    v->Es = nullptr;
-    for (size_t i = 0; i < v->layers.size(); ++i) {
-        DevLayer& L = v->layers[i];
-        L.Wqkv = widen(L.Wqkv, L.Sqkv, L.n_qkv, c.dim); L.Sqkv = nullptr;
-        L.Wo = widen(L.Wo, L.So, c.dim, L.o_in); L.So = nullptr;
-        L.W1a = widen(L.W1a, L.S1a, c.ffn_dim, c.dim); L.S1a = nullptr;
-        L.W1b = widen(L.W1b, L.S1b, c.ffn_dim, c.dim); L.S1b = nullptr;
-        L.W2 = widen(L.W2, L.S2, c.dim, c.ffn_dim); L.S2 = nullptr;
-    }
-    if (ok && cudaDeviceSynchronize() != cudaSuccess) { cudaGetLastError(); ok = false; }
-    if (!ok) {
-        free_model(v);
-        m->bf16_view_failed = true;       // not enough device memory: the token loop keeps serving prompts
-        return nullptr;
-    }
-    // bytes of a step: the widened tensors, plus what the view shares with the model (gains, PLE tensors)
-    v->weight_bytes += m->weight_bytes - v->weight_bytes / 2 - 4 * n_rows;
-    m->bf16_view = v;
-    return v;
-}
 
 }  // namespace mlb
 
@@ -483,7 +430,8 @@ struct mlb_session {
     // tensor-core projections (bf16 weights, batch >= 16)
     bool use_tc = false;
     int tc_nb = 0, tc_stages = 0, tc_stages_swiglu = 0;
-    int tc_max_split = 2;                     // MLB_TC_SPLIT: largest cluster that may split a GEMM's k-blocks
+    int tc_max_split = 8;                     // largest cluster that may split a GEMM's k-blocks
+    bool tc_split_forced = false;             // MLB_TC_SPLIT given: take it as the limit without the k-blocks-per-CTA rule
     int tc_cluster_cap[4] = {0, 0, 0, 0};     // clusters of 1, 2, 4, 8 GEMM CTAs that can be resident at once
     unsigned long long* tc_trace = nullptr;   // MLB_TC_TRACE=1: [64][8] timer stamps of the step's GEMM launches
     int tc_trace_n = 0;
@@ -643,37 +591,41 @@ static cudaError_t launch_cluster(bool pdl, int cluster_z, void (*kernel)(KArgs.
 // (16..128), so a CTA's k-loop takes 0.4 us per 64-wide k-block (0.8 with two weight tiles) whatever the ring
 // depth, and is the time of the kernel unless the k-blocks are spread over CTAs. Exchanging partial
 // accumulators through distributed shared memory costs 2-3 us per launch with clusters of 4 and 8, more than
-// it saves at these sizes; pairs pay off at small batches (cfg1 step at 32 sequences: 452 -> 424 us) and are
-// neutral at 256, so MLB_TC_SPLIT defaults to 2. One wave of CTAs per launch where possible.
-static TcShape tc_pick_shape(const mlb_session* s, int N, int nkb_all, int na) {
+// it saves at cfg1's sizes (8-23 k-blocks per tile); pairs pay off at small batches (cfg1 step at 32 sequences:
+// 452 -> 424 us) and are neutral at 256. Larger clusters are taken only where a CTA keeps 8 k-blocks or more
+// (cfg4: 32-90 k-blocks per tile and few tiles). MLB_TC_SPLIT sets the limit by hand. One wave of CTAs per
+// launch where possible.
+static TcShape tc_pick_shape(const mlb_session* s, int N, int nkb_all, int na, bool w8, int nacc) {
     const int tiles_m = (N + kTcM - 1) / kTcM;
     const int cap = std::min(256, (s->B + 15) / 16 * 16);
     TcShape best{};
     double best_cost = -1.0;
-    for (int nb = 16; nb <= cap && na * nb <= 512; nb <<= 1) {
+    for (int nb = 16; nb <= cap && nacc * nb <= 512; nb <<= 1) {
         for (int li = 0; li < 4; ++li) {
             const int S = 1 << li;
             if (S > s->tc_max_split || S > nkb_all) break;
+            // clusters of 4 and 8 only where a CTA keeps 8 k-blocks or more: their exchange costs 2-3 us
+            if (S > 2 && !s->tc_split_forced && (nkb_all + S - 1) / S < 8) break;
             if (S > 1 && (nb % S != 0 || s->tc_cluster_cap[li] <= 0)) continue;
-            const size_t stage_bytes = (size_t)na * kTcM * 128 + (size_t)nb * 128;
+            const size_t stage_bytes = (size_t)na * kTcM * 128 + (size_t)nb * 128;      // FP8 codes land inside the operand tile
             const int kpc = (nkb_all + S - 1) / S;
             int st = (int)std::max<size_t>(1, std::min<size_t>(std::min(kpc, 12), kTcRingBytes / stage_bytes));
             const int g = st >= kpc ? 1 : (st >= 8 ? 4 : (st >= 4 ? 2 : 1));
             st -= st % g;
-            const size_t body = std::max((size_t)st * stage_bytes, S > 1 ? (size_t)na * nb * kTcM * 4 : (size_t)0);
+            const size_t body = std::max((size_t)st * stage_bytes, S > 1 ? (size_t)nacc * nb * kTcM * 4 : (size_t)0);
             const size_t smem = 1024 + kTcHeadBytes + kTcStageBytes + body;
             if (smem > 227 * 1024) continue;
             const long ctas = (long)tiles_m * ((s->B + nb - 1) / nb) * S;
             const long resident = S == 1 ? s->sm_count : (long)s->tc_cluster_cap[li] * S;
             const long waves = (ctas + resident - 1) / resident;
             const double t_loop = 0.4 * na * kpc;
-            const double t_red = S > 1 ? 0.5 + (double)na * nb * 512.0 / 65536.0 : 0.0;
+            const double t_red = S > 2 ? 2.5 + (double)nacc * nb * 512.0 / 65536.0 : (S > 1 ? 0.5 + (double)nacc * nb * 512.0 / 65536.0 : 0.0);
             const double t_epi = 0.25 * ((nb / S + 15) / 16);
             const double cost = (double)waves * (t_loop + t_red + t_epi + 0.5);
             if (best_cost < 0 || cost < best_cost) {
                 best_cost = cost;
                 uint32_t cols = 32;
-                while (cols < (uint32_t)(na * nb)) cols <<= 1;
+                while (cols < (uint32_t)(nacc * nb)) cols <<= 1;
                 best = TcShape{nb, S, st, g, smem, cols};
             }
         }
@@ -862,30 +814,33 @@ struct Chain {
     template <int MODE>
     static int gemm_tc(mlb_session* s, const StepCtl& c, const CUtensorMap& A, const CUtensorMap& A2, const CUtensorMap* Bmaps, int N, int K,
                        float* y, bf16_t* h16, bool normed, const float* next_gain, const mlb_session::TcLayerMaps* ext,
-                       const QkvPostParams* q, Recorder* rec, const char* name) {
+                       const QkvPostParams* q, const float* sA, const float* sA2, Recorder* rec, const char* name) {
         GemmTcParams p;
         const int ple = s->m->cfg.ple_dim;
         const int na = MODE == TC_SWIGLU ? 2 : 1;
         p.nkb_x = ext ? (ple + kTcKB - 1) / kTcKB : 0;
-        const TcShape sh = ext ? s->tc_shape_down : tc_pick_shape(s, N, (K + kTcKB - 1) / kTcKB, na);
+        constexpr bool w8 = sizeof(T) == 1;
+        const int nacc = (MODE == TC_SWIGLU || (w8 && MODE == TC_RESID)) ? 2 : 1;
+        const TcShape sh = ext ? s->tc_shape_down : tc_pick_shape(s, N, (K + kTcKB - 1) / kTcKB, na, w8, nacc);
         if (sh.nb == 0) return fail(MLB_E_UNSUPPORTED, "%s: no launch shape fits", name);
         const int nb = sh.nb;
         p.N = N; p.K = K; p.B = s->B; p.Nb = nb;
         p.stages = sh.stages; p.group = sh.group; p.tmem_cols = sh.tmem_cols;
         p.y = y; p.resid = MODE == TC_RESID ? y : nullptr; p.h16 = h16; p.err = s->dev_err;
+        p.sA = sA; p.sA2 = sA2;
         p.trace = s->tc_trace ? s->tc_trace + 8 * (size_t)(s->tc_trace_n++ % 64) : nullptr;
         p.ssq_in = normed ? s->tc_ssq : nullptr; p.ssq_parts = (s->m->cfg.dim + kTcM - 1) / kTcM; p.eps = s->m->cfg.rms_eps;
         p.xg16 = next_gain ? s->xn16 : nullptr; p.gain_next = next_gain; p.ssq_out = next_gain ? s->tc_ssq : nullptr;
         const size_t smem = sh.smem;
         dim3 grid((N + kTcM - 1) / kTcM, (s->B + nb - 1) / nb, sh.split);
         int rc;
-        if (rec && (rc = rec->begin(name, (uint64_t)N * (K + (ext ? ple : 0)) * 2 * na + (uint64_t)s->B * K * 2 + (uint64_t)s->B * N * 4,
+        if (rec && (rc = rec->begin(name, ((uint64_t)N * K * sizeof(T) + (uint64_t)N * (ext ? ple : 0) * 2) * na + (uint64_t)s->B * K * 2 + (uint64_t)s->B * N * 4,
                                     2ull * N * (K + (ext ? ple : 0)) * s->B * na)))
             return rc;
         QkvPostParams q0{};
         const CUtensorMap& Ax = ext ? ext->pleP : A;
         const CUtensorMap& Bx = ext ? ext->pleT : A;
-        cudaError_t e = launch_cluster(s->use_pdl, sh.split, gemm_tc_kernel<MODE, KVT>, grid, dim3(kTcThreads), smem, s->stream, A, A2, Bmaps[nb_index(nb)], Ax, Bx, p,
+        cudaError_t e = launch_cluster(s->use_pdl, sh.split, gemm_tc_kernel<MODE, KVT, T>, grid, dim3(kTcThreads), smem, s->stream, A, A2, Bmaps[nb_index(nb)], Ax, Bx, p,
                                        c, q ? *q : q0);
         if (e != cudaSuccess) return fail(MLB_E_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(e));
         if (rec) return rec->end();
@@ -895,14 +850,14 @@ struct Chain {
     // Large-batch step: projections as tcgen05 GEMMs on bf16 operands with the element-wise work in their
     // epilogues; per layer: projection, attention / delta-net, o-projection, gate-up, down.
     static int run_tc(mlb_session* s, int kind, const StepCtl& c, Recorder* rec, int* n_launches) {
-        if (!std::is_same<T, bf16_t>::value) return fail(MLB_E_UNSUPPORTED, "tensor-core projections need bf16 weights");
+        if (std::is_same<T, float>::value) return fail(MLB_E_UNSUPPORTED, "tensor-core projections need bf16 or FP8 weights");
         const mlb_model* m = s->m;
         const mlb_config& cfg = m->cfg;
         const int d = cfg.dim, F = cfg.ffn_dim, B = s->B, ple = cfg.ple_dim;
         int launches = 0, rc;
         if (rec && (rc = rec->begin("embed_ple_gather_norm", (uint64_t)B * d * 8 + (uint64_t)B * ple * 2 * cfg.layers, 0))) return rc;
-        CU(launch_chain(s->use_pdl, embed_tc_kernel, dim3(B, (d + kTcM - 1) / kTcM), dim3(128), (size_t)ple * 4, s->stream, c,
-                        static_cast<const bf16_t*>(m->E), d, static_cast<const StepLayer*>(s->step_layers), cfg.layers, ple,
+        CU(launch_chain(s->use_pdl, embed_tc_kernel<T>, dim3(B, (d + kTcM - 1) / kTcM), dim3(128), (size_t)ple * 4, s->stream, c,
+                        static_cast<const T*>(m->E), static_cast<const float*>(m->Es), d, static_cast<const StepLayer*>(s->step_layers), cfg.layers, ple,
                         static_cast<const float*>(m->layers[0].g1), s->x, s->xn16, s->tc_ssq, s->tple16));
         if (rec && (rc = rec->end())) return rc;
         ++launches;
@@ -915,7 +870,7 @@ struct Chain {
                 q.kv_heads = cfg.kv_heads; q.qk_norm = cfg.qk_norm; q.eps = cfg.rms_eps; q.gq = L.gq; q.gk = L.gk; q.rope = m->rope;
                 q.kpool = s->kpool[i]; q.vpool = s->vpool[i]; q.page_table = s->page_table; q.pt_stride = s->max_pages;
                 q.qbuf = s->qbuf; q.gbuf = s->gbuf;
-                if ((rc = gemm_tc<TC_QKV>(s, c, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, nullptr, nullptr, true, nullptr, nullptr, &q, rec,
+                if ((rc = gemm_tc<TC_QKV>(s, c, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, nullptr, nullptr, true, nullptr, nullptr, &q, L.Sqkv, nullptr, rec,
                                           "qkv_gemm_tcgen05_norm_rope_kvappend")))
                     return rc;
                 ++launches;
@@ -940,7 +895,7 @@ struct Chain {
                 if (rec && (rc = rec->end())) return rc;
                 ++launches;
             } else {
-                if ((rc = gemm_tc<TC_RAW>(s, c, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, s->raw, nullptr, true, nullptr, nullptr, nullptr, rec,
+                if ((rc = gemm_tc<TC_RAW>(s, c, M.qkv, M.qkv, s->tc_g.xn, L.n_qkv, d, s->raw, nullptr, true, nullptr, nullptr, nullptr, L.Sqkv, nullptr, rec,
                                           "deltanet_proj_gemm_tcgen05")))
                     return rc;
                 ++launches;
@@ -966,18 +921,18 @@ struct Chain {
                 ++launches;
             }
             const CUtensorMap* amap = L.type == MLB_LAYER_ATTENTION ? s->tc_g.a_attn : s->tc_g.a_dn;
-            if ((rc = gemm_tc<TC_RESID>(s, c, M.o, M.o, amap, d, L.o_in, s->x, nullptr, false, L.g2, nullptr, nullptr, rec,
+            if ((rc = gemm_tc<TC_RESID>(s, c, M.o, M.o, amap, d, L.o_in, s->x, nullptr, false, L.g2, nullptr, nullptr, L.So, nullptr, rec,
                                         "oproj_gemm_tcgen05_residual_norm")))
                 return rc;
             ++launches;
-            if ((rc = gemm_tc<TC_SWIGLU>(s, c, M.w1a, M.w1b, s->tc_g.xn, F, d, nullptr, s->h16, true, nullptr, nullptr, nullptr, rec,
+            if ((rc = gemm_tc<TC_SWIGLU>(s, c, M.w1a, M.w1b, s->tc_g.xn, F, d, nullptr, s->h16, true, nullptr, nullptr, nullptr, L.S1a, L.S1b, rec,
                                          "ffn_gateup_gemm_tcgen05_swiglu")))
                 return rc;
             ++launches;
             const bool last = i + 1 == cfg.layers;
             const float* g_next = last ? m->g_final : m->layers[i + 1].g1;
             if ((rc = gemm_tc<TC_RESID>(s, c, M.w2, M.w2, s->tc_g.h, d, F, s->x, nullptr, false, g_next,
-                                        (!last && ple > 0) ? &s->tc_maps[i + 1] : nullptr, nullptr, rec, "ffn_down_gemm_tcgen05_residual_ple_norm")))
+                                        (!last && ple > 0) ? &s->tc_maps[i + 1] : nullptr, nullptr, L.S2, nullptr, rec, "ffn_down_gemm_tcgen05_residual_ple_norm")))
                 return rc;
             ++launches;
         }
@@ -989,7 +944,7 @@ struct Chain {
             if (rec && (rc = rec->end())) return rc;
             ++launches;
         } else {
-            if ((rc = gemm_tc<TC_RAW>(s, c, s->tc_g.E, s->tc_g.E, s->tc_g.xn, cfg.vocab, d, s->logits, nullptr, true, nullptr, nullptr, nullptr, rec,
+            if ((rc = gemm_tc<TC_RAW>(s, c, s->tc_g.E, s->tc_g.E, s->tc_g.xn, cfg.vocab, d, s->logits, nullptr, true, nullptr, nullptr, nullptr, static_cast<const float*>(m->Es), nullptr, rec,
                                       "lmhead_gemm_tcgen05")))
                 return rc;
             ++launches;
@@ -1405,6 +1360,20 @@ static int setup_grid_path(mlb_session* s) {
     return MLB_OK;
 }
 
+template <typename KVT, typename WT>
+static int tc_allow_big_smem_t() {
+    const int big = 227 * 1024;
+    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW, KVT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID, KVT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU, KVT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_QKV, KVT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+    return MLB_OK;
+}
+static int tc_allow_big_smem(int wdt, int kvdt) {
+    if (wdt == MLB_DT_FP8_E4M3) return kvdt == MLB_DT_BF16 ? tc_allow_big_smem_t<bf16_t, fp8_t>() : tc_allow_big_smem_t<float, fp8_t>();
+    return kvdt == MLB_DT_BF16 ? tc_allow_big_smem_t<bf16_t, bf16_t>() : tc_allow_big_smem_t<float, bf16_t>();
+}
+
 // Tensor-core projections for batches of 4 sequences or more with bf16 weights (MLB_GEMM=simt turns it off).
 static int setup_tc_path(mlb_session* s) {
     const mlb_config& c = s->m->cfg;
@@ -1412,10 +1381,11 @@ static int setup_tc_path(mlb_session* s) {
     const char* env = std::getenv("MLB_GEMM");
     const std::string mode = env ? env : "auto";
     if (!s->parent && (mode == "simt" || s->use_grid || s->use_lean)) return MLB_OK;
-    if (c.weight_dtype != MLB_DT_BF16) {
-        if (mode == "tc") return fail(MLB_E_UNSUPPORTED, "MLB_GEMM=tc needs bf16 weights");
+    if (c.weight_dtype != MLB_DT_BF16 && c.weight_dtype != MLB_DT_FP8_E4M3) {
+        if (mode == "tc") return fail(MLB_E_UNSUPPORTED, "MLB_GEMM=tc needs bf16 or FP8 weights");
         return MLB_OK;
     }
+    const bool w8 = c.weight_dtype == MLB_DT_FP8_E4M3;
     // auto: from 4 sequences on. The GEMV kernels re-read nothing, but their time grows with the batch
     // (cfg1: 169 us at 1 sequence, 369 at 4, 537 at 8, 635 at 12), while the tensor-core step costs
     // 360-390 us for any batch up to 16 (its floor is its 60 launches).
@@ -1436,13 +1406,16 @@ static int setup_tc_path(mlb_session* s) {
     if ((rc = build_step_layers(s))) return rc;
     if (const char* v = std::getenv("MLB_TC_TRACE"))
         if (v[0] == '1' && (rc = sess_alloc(s, (void**)&s->tc_trace, 64 * 8 * 8, true))) return rc;
-    s->tc_max_split = 2;
-    if (const char* v = std::getenv("MLB_TC_SPLIT")) s->tc_max_split = std::max(1, std::min(8, std::atoi(v)));
+    s->tc_max_split = 8;
+    if (const char* v = std::getenv("MLB_TC_SPLIT")) {
+        s->tc_max_split = std::max(1, std::min(8, std::atoi(v)));
+        s->tc_split_forced = true;
+    }
     {
         // how many clusters of GEMM CTAs fit on the GPU at once (a 100 KB CTA, typical of a split launch)
         const int big = 227 * 1024;
         void (*kern)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, GemmTcParams, StepCtl, QkvPostParams) =
-            gemm_tc_kernel<TC_RESID, float>;
+            gemm_tc_kernel<TC_RESID, float, bf16_t>;
         CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
         s->tc_cluster_cap[0] = s->sm_count;
         for (int li = 1; li < 4; ++li) {
@@ -1461,7 +1434,7 @@ static int setup_tc_path(mlb_session* s) {
             s->tc_cluster_cap[li] = n;
         }
     }
-    s->tc_shape_down = tc_pick_shape(s, c.dim, (c.ffn_dim + kTcKB - 1) / kTcKB + (c.ple_dim + kTcKB - 1) / kTcKB, 1);
+    s->tc_shape_down = tc_pick_shape(s, c.dim, (c.ffn_dim + kTcKB - 1) / kTcKB + (c.ple_dim + kTcKB - 1) / kTcKB, 1, w8, w8 ? 2 : 1);
     const int parts = (c.dim + kTcM - 1) / kTcM;
     if ((rc = sess_alloc(s, (void**)&s->xn16, (size_t)B * c.dim * 2, true))) return rc;
     if ((rc = sess_alloc(s, (void**)&s->a16, (size_t)B * std::max(nq, a_dn) * 2, true))) return rc;
@@ -1472,18 +1445,19 @@ static int setup_tc_path(mlb_session* s) {
     for (int i = 0; i < c.layers; ++i) {
         const DevLayer& L = s->m->layers[i];
         auto& M = s->tc_maps[i];
-        if ((rc = make_bf16_map(enc, &M.qkv, L.Wqkv, L.n_qkv, c.dim, kTcM))) return rc;
-        if ((rc = make_bf16_map(enc, &M.o, L.Wo, c.dim, L.o_in, kTcM))) return rc;
-        if ((rc = make_bf16_map(enc, &M.w1a, L.W1a, c.ffn_dim, c.dim, kTcM))) return rc;
-        if ((rc = make_bf16_map(enc, &M.w1b, L.W1b, c.ffn_dim, c.dim, kTcM))) return rc;
-        if ((rc = make_bf16_map(enc, &M.w2, L.W2, c.dim, c.ffn_dim, kTcM))) return rc;
+        auto wmap = w8 ? make_u8_map : make_bf16_map;       // FP8: e4m3 codes, widened in the kernel
+        if ((rc = wmap(enc, &M.qkv, L.Wqkv, L.n_qkv, c.dim, kTcM))) return rc;
+        if ((rc = wmap(enc, &M.o, L.Wo, c.dim, L.o_in, kTcM))) return rc;
+        if ((rc = wmap(enc, &M.w1a, L.W1a, c.ffn_dim, c.dim, kTcM))) return rc;
+        if ((rc = wmap(enc, &M.w1b, L.W1b, c.ffn_dim, c.dim, kTcM))) return rc;
+        if ((rc = wmap(enc, &M.w2, L.W2, c.dim, c.ffn_dim, kTcM))) return rc;
         if (c.ple_dim > 0) {
             // operands of the per-layer embedding folded into the previous layer's down projection
             if ((rc = make_bf16_map(enc, &M.pleP, L.pleP, c.dim, c.ple_dim, kTcM))) return rc;
             if ((rc = make_bf16_map(enc, &M.pleT, s->tple16 + (size_t)i * B * c.ple_dim, B, c.ple_dim, s->tc_shape_down.nb))) return rc;
         }
     }
-    if ((rc = make_bf16_map(enc, &s->tc_g.E, s->m->E, c.vocab, c.dim, kTcM))) return rc;
+    if ((rc = (w8 ? make_u8_map : make_bf16_map)(enc, &s->tc_g.E, s->m->E, c.vocab, c.dim, kTcM))) return rc;
     for (int i = 0; i < 5; ++i) {
         const uint32_t nb = 16u << i;
         if ((rc = make_bf16_map(enc, &s->tc_g.xn[i], s->xn16, B, c.dim, nb))) return rc;
@@ -1491,18 +1465,7 @@ static int setup_tc_path(mlb_session* s) {
         if ((rc = make_bf16_map(enc, &s->tc_g.a_dn[i], s->a16, B, a_dn, nb))) return rc;
         if ((rc = make_bf16_map(enc, &s->tc_g.h[i], s->h16, B, c.ffn_dim, nb))) return rc;
     }
-    const int big = 227 * 1024;
-    if (c.kv_dtype == MLB_DT_BF16) {
-        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_QKV, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    } else {
-        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-        CU(cudaFuncSetAttribute(gemm_tc_kernel<TC_QKV, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
-    }
+    if ((rc = tc_allow_big_smem(c.weight_dtype, c.kv_dtype))) return rc;
     s->use_tc = true;
     return MLB_OK;
 }
@@ -1742,16 +1705,7 @@ static int session_create(mlb_model* m, int batch, int max_context, int kv_block
 
 extern "C" int mlb_session_new(mlb_model* m, int batch, int max_context, int kv_block, int kv_pages, mlb_session** out) {
     if (!m || !out) return fail(MLB_E_INVALID, "null argument");
-    // FP8 weights and 4 sequences or more: the steps run as tensor-core GEMMs on the bf16 view of the
-    // weights. The FP8 GEMV re-reads the weights once per 8 sequences (25 ms per step at 64 sequences on
-    // the 1.2 GB configuration); the GEMMs read the 2.4 GB view once. MLB_GEMM=simt keeps the GEMV.
-    mlb_model* use = m;
-    const char* env = std::getenv("MLB_GEMM");
-    if (m->cfg.weight_dtype == MLB_DT_FP8_E4M3 && batch >= 4 && !(env && std::string(env) == "simt")) {
-        CU(cudaSetDevice(m->device));
-        if (mlb_model* v = model_for_tc(m)) use = v;
-    }
-    return session_create(use, batch, max_context, kv_block, kv_pages, nullptr, out);
+    return session_create(m, batch, max_context, kv_block, kv_pages, nullptr, out);
 }
 
 extern "C" int mlb_session_reset(mlb_session* s) {
@@ -1815,9 +1769,7 @@ static int prefill_columns(mlb_session* s, const int32_t* tokens, const int32_t*
     }
     if (!s->cols && !s->cols_tried) {
         s->cols_tried = true;
-        mlb_model* tm = model_for_tc(s->m);            // FP8: the bf16 view of the weights
-        int rc = tm ? session_create(tm, kPromptCols, s->max_ctx, 0, 0, s, &s->cols)
-                    : fail(MLB_E_NOMEM, "no device memory for the bf16 view of the FP8 weights");
+        int rc = session_create(s->m, kPromptCols, s->max_ctx, 0, 0, s, &s->cols);
         if (rc) {
             s->cols = nullptr;
             if (mode == "chunk") return rc;

@@ -62,6 +62,7 @@ struct GemmTcParams {
     // RESID: operand and partial sums for the next norm (null = not wanted)
     bf16_t* xg16; const float* gain_next; float* ssq_out;
     int* err;
+    const float* sA; const float* sA2;   // FP8 weights: per-row scales of the weight tile(s), applied in the epilogue
     unsigned long long* trace;     // diagnostics: five %globaltimer stamps of CTA (0, 0, 0), or null
 };
 
@@ -205,12 +206,42 @@ __device__ __forceinline__ float cluster_ld_f32(uint32_t addr) {
     return v;
 }
 
+// two e4m3 codes -> two bf16 (exact: 3 mantissa bits, exponent range inside bf16's)
+__device__ __forceinline__ uint32_t e4m3x2_to_bf16x2(uint32_t two_codes) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)two_codes, __NV_E4M3);
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+    const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+    return *reinterpret_cast<const uint32_t*>(&b);
+}
+
+// Four e4m3 codes (one 32-bit word) -> four bf16 in two words, with integer instructions: for a normal code the
+// bf16 bit pattern is sign | ((code & 0x7f) << 4) + (120 << 7) (exponent rebias 7 -> 127, mantissa 3 -> 7 bits).
+// Conversion instructions run at a quarter of the integer rate. Not valid for zeros and subnormal codes
+// (exponent field 0, about one weight in 10^4): e4m3_word_has_exp0 tells, and the caller then converts exactly.
+__device__ __forceinline__ void e4m3x4_to_bf16x4_normal(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    const uint32_t x0 = __byte_perm(w, 0u, 0x1404u);      // codes 0, 1 in the high bytes of the two halves
+    const uint32_t x1 = __byte_perm(w, 0u, 0x3424u);      // codes 2, 3
+    lo = (x0 & 0x80008000u) | (((x0 >> 4) & 0x07f007f0u) + 0x3c003c00u);
+    hi = (x1 & 0x80008000u) | (((x1 >> 4) & 0x07f007f0u) + 0x3c003c00u);
+}
+// Nonzero iff one of the four codes has exponent field 0: subtracting 1 from the 4-bit field borrows into the
+// (masked, hence clear) bit above it.
+__device__ __forceinline__ uint32_t e4m3_word_has_exp0(uint32_t w) {
+    const uint32_t e = w & 0x78787878u;
+    return (e - 0x08080808u) & 0x80808080u;
+}
+
+// FP8 weights (WT = fp8_t): the weight tile arrives as e4m3 codes ([128 x 64] bytes by TMA, no swizzle) in a raw
+// area of the stage; warps 4-7 widen it to bf16 into the swizzled operand tile the MMA reads (exact), and the
+// per-row scale multiplies the accumulator row in the epilogue. Half the weight bytes of a bf16 copy, no copy.
+// A bf16 extension operand (the per-layer embedding behind the down projection) then gets an accumulator of
+// its own, since it must not be scaled.
 // grid = (ceil(N / 128), ceil(B / Nb), split) with clusters of (1, 1, split) when split > 1: the `split`
 // CTAs of a cluster take consecutive shares of the k-blocks of one output tile (a tcgen05.mma of these
 // shapes costs about 0.1 us whatever its N, so the k-loop of a lone CTA is the time of the kernel), leave
 // their partial accumulators in shared memory, and each finishes Nb / split columns of the tile from the
 // partials of all of them, read over distributed shared memory in a fixed order.
-template <int MODE, typename KVT>
+template <int MODE, typename KVT, typename WT>
 __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
                                                        const __grid_constant__ CUtensorMap tmA2,
                                                        const __grid_constant__ CUtensorMap tmB,
@@ -222,8 +253,12 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     const bool tracing = p.trace != nullptr && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
     if (tracing) p.trace[0] = globaltimer_ns();          // entry
     constexpr int NA = MODE == TC_SWIGLU ? 2 : 1;
+    constexpr bool W8 = sizeof(WT) == 1;
+    constexpr bool EXT2 = W8 && MODE == TC_RESID;
+    constexpr int NACC = (MODE == TC_SWIGLU || EXT2) ? 2 : 1;      // accumulators of Nb columns each
     const int a_bytes = kTcM * 128;
     const int b_bytes = p.Nb * 128;
+    const int raw_bytes = W8 ? NA * kTcM * kTcKB : 0;     // lands in the upper half of the operand tile it becomes
     const int stage_bytes = NA * a_bytes + b_bytes;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int m0 = blockIdx.x * kTcM;
@@ -234,6 +269,7 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     const int nkb_all = nkb1 + p.nkb_x;
     const int kb_lo = (int)(((long)nkb_all * rank) / split);
     const int nkb = (int)(((long)nkb_all * (rank + 1)) / split) - kb_lo;
+    const int n_main = max(0, min(nkb, nkb1 - kb_lo));             // of them, k-blocks of the main operand pair (first)
 
     // shared memory: [epilogue words][barriers][ring stages | partial accumulators]; the offsets of the first
     // two are the same in every CTA of a cluster
@@ -246,7 +282,8 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = full0 + 8u * p.stages;
     const uint32_t accum = empty0 + 8u * p.stages;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * p.stages + 1);
+    const uint32_t rawfull0 = accum + 8u;                          // FP8: raw weight tile of a stage has landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * p.stages + 1);
     float* stage_s = reinterpret_cast<float*>(smem + kTcHeadBytes);                  // [2 groups][16][128] a chunk of the tile (QKV)
     float* rope_s = stage_s + 2 * 16 * kTcM;                                         // [2 groups][16][128] its RoPE factors (QKV)
     unsigned char* ring = smem + kTcHeadBytes + kTcStageBytes;    // 1024-aligned
@@ -254,8 +291,9 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
 
     if (tid == 0) {
         for (int i = 0; i < p.stages; ++i) {
-            mbar_init(full0 + 8u * i, 1);
+            mbar_init(full0 + 8u * i, W8 ? 5 : 1);        // the loader, plus the four widening warps
             mbar_init(empty0 + 8u * i, 1);
+            mbar_init(rawfull0 + 8u * i, 1);
         }
         mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -276,14 +314,24 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
         // ---- TMA producer ---------------------------------------------------------------------
         // The weight tiles of the first stages depend on nothing: they are on their way before this
         // kernel waits for its predecessor, whose results only the activation tiles need.
-        const uint32_t tx = (uint32_t)stage_bytes;
-        auto load_a = [&](int kb, uint32_t base, uint32_t bar) {
+        auto tx_of = [&](int kb) -> uint32_t {           // bytes that complete the stage's `full` barrier
+            if (!W8) return (uint32_t)stage_bytes;
+            return (uint32_t)(kb < n_main ? b_bytes : a_bytes + b_bytes);
+        };
+        auto load_a = [&](int kb, uint32_t base, uint32_t bar, uint32_t rbar) {
             const int k = kb_lo + kb;
             if (k < nkb1) {
-                tma_load_2d(base, &tmA, k * kTcKB, m0, bar);
-                if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes, &tmA2, k * kTcKB, m0, bar);
+                if (W8) {
+                    mbar_expect_tx(rbar, (uint32_t)raw_bytes);
+                    tma_load_2d(base + a_bytes / 2, &tmA, k * kTcKB, m0, rbar);
+                    if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes + a_bytes / 2, &tmA2, k * kTcKB, m0, rbar);
+                } else {
+                    tma_load_2d(base, &tmA, k * kTcKB, m0, bar);
+                    if (MODE == TC_SWIGLU) tma_load_2d(base + a_bytes, &tmA2, k * kTcKB, m0, bar);
+                }
             } else {
                 tma_load_2d(base, &tmAx, (k - nkb1) * kTcKB, m0, bar);
+                if (W8) mbar_arrive(rbar);           // nothing to widen: the widening warps just pass
             }
         };
         auto load_b = [&](int kb, uint32_t base, uint32_t bar) {
@@ -293,8 +341,8 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
         };
         const int pre = min(p.stages, nkb);
         for (int kb = 0; kb < pre; ++kb) {
-            mbar_expect_tx(full0 + 8u * kb, tx);
-            load_a(kb, smem_u32(ring + (size_t)kb * stage_bytes), full0 + 8u * kb);
+            mbar_expect_tx(full0 + 8u * kb, tx_of(kb));
+            load_a(kb, smem_u32(ring + (size_t)kb * stage_bytes), full0 + 8u * kb, rawfull0 + 8u * kb);
         }
         pdl_wait();                  // the activation operand comes from the predecessor kernel
         if (tracing) p.trace[2] = globaltimer_ns();      // predecessor complete
@@ -304,11 +352,63 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
             const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
             // the stages come back `group` at a time, on the barrier of the group's last stage
             if (kb % p.group == 0 && !tc_wait(empty0 + 8u * (s + p.group - 1), ph ^ 1u, p.err, 11)) break;
-            mbar_expect_tx(full0 + 8u * s, tx);
+            mbar_expect_tx(full0 + 8u * s, tx_of(kb));
             const uint32_t base = smem_u32(ring + (size_t)s * stage_bytes);
-            load_a(kb, base, full0 + 8u * s);
+            load_a(kb, base, full0 + 8u * s, rawfull0 + 8u * s);
             load_b(kb, base, full0 + 8u * s);
         }
+    } else if (W8 && warp >= 4) {
+        // ---- FP8: widen the raw weight tiles into the operand tiles ---------------------------------
+        // Piece q of a tile = 8 codes = row q / 8, 16-byte chunk q % 8 of the bf16 row; consecutive lanes take
+        // consecutive pieces (8-byte reads side by side, the 8 chunks of a row written by 8 lanes). The chunk
+        // lands where the 128-byte swizzle of the MMA's descriptor expects it: chunk ^ (row % 8).
+        const int t = tid - 128;
+        bool dead = false;       // a wait ran out: stop waiting, but keep the four warps in step (they share a barrier)
+        for (int kb = 0; kb < nkb; ++kb) {
+            const int s = kb % p.stages;
+            const uint32_t ph = (uint32_t)(kb / p.stages) & 1u;
+            if (!dead && !tc_wait(rawfull0 + 8u * s, ph, p.err, 14)) dead = true;
+            if (kb < n_main) {
+                unsigned char* st_base = ring + (size_t)s * stage_bytes;
+                const unsigned char* raw = st_base + a_bytes / 2;      // codes of tile a at raw + a * a_bytes
+                uint2 w[NA * 8];
+                uint32_t exp0 = 0;
+#pragma unroll
+                for (int i = 0; i < NA * 8; ++i) {
+                    w[i] = *reinterpret_cast<const uint2*>(raw + (i >> 3) * a_bytes + (t + 128 * (i & 7)) * 8);
+                    exp0 |= e4m3_word_has_exp0(w[i].x) | e4m3_word_has_exp0(w[i].y);
+                }
+                // every code is in registers before any bf16 lands on top of the raw tile
+                asm volatile("bar.sync 3, 128;" ::: "memory");
+                // one branch per k-block and thread (two loops the compiler cannot merge into predicated code)
+                if (exp0 == 0) {
+#pragma unroll
+                    for (int i = 0; i < NA * 8; ++i) {
+                        const int qd = t + 128 * (i & 7), r = qd >> 3, ch = qd & 7;
+                        uint4 o;
+                        e4m3x4_to_bf16x4_normal(w[i].x, o.x, o.y);
+                        e4m3x4_to_bf16x4_normal(w[i].y, o.z, o.w);
+                        *reinterpret_cast<uint4*>(st_base + (i >> 3) * a_bytes + (r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4)) = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < NA * 8; ++i) {
+                        const int qd = t + 128 * (i & 7), r = qd >> 3, ch = qd & 7;
+                        const uint2 wi = w[i];
+                        uint4 o;
+                        o.x = e4m3x2_to_bf16x2(wi.x & 0xffffu);
+                        o.y = e4m3x2_to_bf16x2(wi.x >> 16);
+                        o.z = e4m3x2_to_bf16x2(wi.y & 0xffffu);
+                        o.w = e4m3x2_to_bf16x2(wi.y >> 16);
+                        *reinterpret_cast<uint4*>(st_base + (i >> 3) * a_bytes + (r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4)) = o;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes -> the MMA's reads
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full0 + 8u * s);
+        }
+        pdl_wait();
     } else {
         pdl_wait();
     }
@@ -327,18 +427,23 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
 #pragma unroll
             for (int j = 0; j < kTcKB / 16; ++j) {
                 // 16 bf16 = 32 bytes further along K inside the 128-byte swizzle row
-                const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
-                umma_bf16(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, acc);
-                if (MODE == TC_SWIGLU) umma_bf16(tmem_base + (uint32_t)p.Nb, a2desc + 2u * j, bdesc + 2u * j, idesc, acc);
+                if (EXT2 && kb >= n_main) {
+                    // bf16 extension operand: its own accumulator (the main one is scaled per row afterwards)
+                    umma_bf16(tmem_base + (uint32_t)p.Nb, adesc + 2u * j, bdesc + 2u * j, idesc, (kb > n_main || j > 0) ? 1u : 0u);
+                } else {
+                    const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
+                    umma_bf16(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, acc);
+                    if (MODE == TC_SWIGLU) umma_bf16(tmem_base + (uint32_t)p.Nb, a2desc + 2u * j, bdesc + 2u * j, idesc, acc);
+                }
             }
             // hand stages back only where the loader will refill them, a group at a time
             if (kb % p.group == p.group - 1 && kb - (p.group - 1) + p.stages < nkb) umma_commit(empty0 + 8u * s);
         }
         umma_commit(accum);                        // the accumulators are complete (at once, if there was no k-block)
     }
-    if (warp >= 2) {
+    if (warp >= 2 && !(W8 && warp >= 4)) {
         // scale of column b from the partial sums of squares its producer left (inference.cu:24-50)
-        for (int j = tid - 64; j < p.Nb; j += kTcThreads - 64) {
+        for (int j = tid - 64; j < p.Nb; j += (W8 ? 64 : kTcThreads - 64)) {
             float r = 1.0f;
             const int b = b0 + j;
             if (p.ssq_in != nullptr && b < p.B) {
@@ -404,6 +509,11 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     float* st = stage_s + grp * 16 * kTcM;
     float* rp = rope_s + grp * 16 * kTcM;
     float gn_other = 1.0f;
+    float sa = 1.0f, sa2 = 1.0f;
+    if (W8 && row_ok) {
+        if (p.sA != nullptr) sa = p.sA[row];
+        if (MODE == TC_SWIGLU && p.sA2 != nullptr) sa2 = p.sA2[row];
+    }
     if (MODE == TC_QKV && q.qk_norm && seg < 2 && (row ^ 1) < p.N) gn_other = seg == 0 ? q.gq[row ^ 1] : q.gk[(row ^ 1) - seg_q];
     auto stage_rope = [&](int c0) {
         float t[16];
@@ -422,12 +532,14 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
     if (split > 1) {
         // partial accumulators of all Nb columns into shared memory (the ring is idle: every MMA that read it
         // has completed), column-major so that a warp writes and later reads 128 consecutive bytes
-        for (int c0 = 16 * grp; c0 < NA * p.Nb; c0 += 32) {
+        for (int c0 = 16 * grp; c0 < NACC * p.Nb; c0 += 32) {
             uint32_t t[16];
             tmem_ld16_issue(tmem_base + lane_base + (uint32_t)c0, t);
             tmem_ld_wait();
+            // an accumulator no MMA of this CTA wrote holds nothing
+            const bool written = EXT2 ? (c0 < p.Nb ? n_main > 0 : nkb > n_main) : nkb > 0;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) part[(size_t)(c0 + j) * kTcM + (tid & 127)] = nkb > 0 ? __uint_as_float(t[j]) : 0.f;
+            for (int j = 0; j < 16; ++j) part[(size_t)(c0 + j) * kTcM + (tid & 127)] = written ? __uint_as_float(t[j]) : 0.f;
         }
         cluster_sync_all();
     }
@@ -456,7 +568,7 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
                 for (int j = 0; j < 16; ++j) {
                     if (c0 + j < ce) {
                         v[j] += cluster_ld_f32(base + (uint32_t)(c0 + j) * (kTcM * 4u));
-                        if (MODE == TC_SWIGLU) u[j] += cluster_ld_f32(base + (uint32_t)(p.Nb + c0 + j) * (kTcM * 4u));
+                        if (NACC == 2) u[j] += cluster_ld_f32(base + (uint32_t)(p.Nb + c0 + j) * (kTcM * 4u));
                     }
                 }
             }
@@ -464,12 +576,21 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
             uint32_t t[16], t2[16];
             const uint32_t cc = (uint32_t)(c0 < ce ? c0 : cb);       // a masked round reads a valid chunk and drops it
             tmem_ld16_issue(tmem_base + lane_base + cc, t);
-            if (MODE == TC_SWIGLU) tmem_ld16_issue(tmem_base + lane_base + (uint32_t)p.Nb + cc, t2);
+            if (NACC == 2) tmem_ld16_issue(tmem_base + lane_base + (uint32_t)p.Nb + cc, t2);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 v[j] = __uint_as_float(t[j]);
-                if (MODE == TC_SWIGLU) u[j] = __uint_as_float(t2[j]);
+                if (NACC == 2) u[j] = (EXT2 && nkb <= n_main) ? 0.f : __uint_as_float(t2[j]);
+            }
+        }
+        if (W8) {
+            // per-row scales of the FP8 weights; the extension operand's accumulator is not scaled
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                v[j] *= sa;
+                if (MODE == TC_SWIGLU) u[j] *= sa2;
+                if (EXT2) v[j] += u[j];
             }
         }
         if (MODE == TC_QKV) {
@@ -574,7 +695,8 @@ __global__ void __launch_bounds__(kTcThreads) gemm_tc_kernel(const __grid_consta
 // stream (inference.cu:137-170), its bf16(x * gain) operand and partial sums of squares for the first
 // projection, and the per-layer embedding rows T_l[tok] of the later layers gathered as bf16 operands of
 // the down projections. grid = (B, ceil(d / 128)), block = 128: one feature per thread.
-static __global__ void __launch_bounds__(128) embed_tc_kernel(StepCtl c, const bf16_t* __restrict__ E, int d,
+template <typename WT>
+__global__ void __launch_bounds__(128) embed_tc_kernel(StepCtl c, const WT* __restrict__ E, const float* __restrict__ escale, int d,
                                                               const StepLayer* __restrict__ layers, int n_layers, int ple,
                                                               const float* __restrict__ gain, float* __restrict__ x,
                                                               bf16_t* __restrict__ xg16, float* __restrict__ ssq,
@@ -603,7 +725,7 @@ static __global__ void __launch_bounds__(128) embed_tc_kernel(StepCtl c, const b
     const int i = blockIdx.y * 128 + tid;
     float v = 0.f;
     if (i < d) {
-        v = __bfloat162float(E[(size_t)t * d + i]);
+        v = Elem<WT>::get(E, (size_t)t * d + i) * (escale ? escale[t] : 1.0f);
         if (ple > 0) {
             float a = 0.f;
             const bf16_t* prow = static_cast<const bf16_t*>(layers[0].pleP) + (size_t)i * ple;

@@ -1335,17 +1335,6 @@ static __global__ void cvt_f32_to_bf16_kernel(const float* __restrict__ src, bf1
     for (; i < n; i += stride) dst[i] = __float2bfloat16_rn(src[i]);
 }
 
-// Inverse of the row quantisation below into bf16: dst = bf16(e4m3 code * row scale). One warp per row.
-static __global__ void dequant_fp8_rows_kernel(const fp8_t* __restrict__ src, const float* __restrict__ scale,
-                                               bf16_t* __restrict__ dst, int rows, int cols) {
-    int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    int lane = threadIdx.x & 31;
-    if (row >= rows) return;
-    const float sc = scale ? scale[row] : 1.0f;
-    for (int i = lane; i < cols; i += 32)
-        dst[(size_t)row * cols + i] = __float2bfloat16_rn(Elem<fp8_t>::get(src, (size_t)row * cols + i) * sc);
-}
-
 // One warp per row: scale = max|row| / 448 (1 when the row is all zero), code = e4m3(w / scale).
 static __global__ void quant_fp8_rows_kernel(const float* __restrict__ src, fp8_t* __restrict__ dst,
                                       float* __restrict__ scale, int rows, int cols) {

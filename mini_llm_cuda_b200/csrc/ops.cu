@@ -150,6 +150,7 @@ extern "C" int mlb_op_gemm_bf16(const void* W, const void* W_up_or_null, const v
     if (p.stages > 6) p.stages = 6;
     p.group = 1;
     p.trace = nullptr;
+    p.sA = nullptr; p.sA2 = nullptr;
     uint32_t cols = 32;
     while (cols < (uint32_t)na * (uint32_t)Nb) cols <<= 1;
     p.tmem_cols = cols;
@@ -163,14 +164,14 @@ extern "C" int mlb_op_gemm_bf16(const void* W, const void* W_up_or_null, const v
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
     if (W_up_or_null) {
-        e = cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e == cudaSuccess) gemm_tc_kernel<TC_SWIGLU, float><<<grid, kTcThreads, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
+        e = cudaFuncSetAttribute(gemm_tc_kernel<TC_SWIGLU, float, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e == cudaSuccess) gemm_tc_kernel<TC_SWIGLU, float, bf16_t><<<grid, kTcThreads, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
     } else if (resid_or_null) {
-        e = cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e == cudaSuccess) gemm_tc_kernel<TC_RESID, float><<<grid, kTcThreads, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
+        e = cudaFuncSetAttribute(gemm_tc_kernel<TC_RESID, float, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e == cudaSuccess) gemm_tc_kernel<TC_RESID, float, bf16_t><<<grid, kTcThreads, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
     } else {
-        e = cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-        if (e == cudaSuccess) gemm_tc_kernel<TC_RAW, float><<<grid, kTcThreads, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
+        e = cudaFuncSetAttribute(gemm_tc_kernel<TC_RAW, float, bf16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e == cudaSuccess) gemm_tc_kernel<TC_RAW, float, bf16_t><<<grid, kTcThreads, smem, st>>>(tA, tA2, tB, tA, tB, p, c0, q0);
     }
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
