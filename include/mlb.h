@@ -141,10 +141,11 @@ int mlb_pool_decode_n(mlb_pool* p, const mlb_sampling* sampling, int n, int32_t*
  * (inference.cu:376-752), whose [V x L] scores the reference's trainer consumes
  * (training_orchestrator.cu:308). logits_out [len][V] fp32 host, row t = prediction after
  * tokens[0..t] (the reference's column t of vocabScores_DEVICE, before the softmax). The tokens
- * run as columns of tensor-core steps like a long prompt, with the LM head on every column:
- * needs bf16 or FP8 weights (MLB_E_UNSUPPORTED otherwise); activations are bf16, i.e. the logits agree
- * with the fp32 forward within the low-precision tolerance. Uses sequence 0 of the session; the
- * session is reset before and after. */
+ * run as columns of tensor-core steps like a long prompt, with the LM head on every column (bf16 or FP8
+ * weights; activations are bf16, i.e. the logits agree with the fp32 forward within the low-precision
+ * tolerance). With fp32 weights, or with MLB_SCORE=step in the environment, the tokens run through the
+ * token loop instead (fp32 activations, the fp32 bound of the decode path; about 0.2 ms per token).
+ * Uses sequence 0 of the session; the session is reset before and after. */
 int mlb_score_tokens(mlb_session* s, const int32_t* tokens, int len, float* logits_out);
 
 /* Replaces one iteration of the while loop of runInferenceLoop

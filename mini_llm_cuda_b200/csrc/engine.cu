@@ -1892,8 +1892,26 @@ extern "C" int mlb_score_tokens(mlb_session* s, const int32_t* tokens, int len, 
     const int V = s->m->cfg.vocab;
     for (int i = 0; i < len; ++i)
         if (tokens[i] < 0 || tokens[i] >= V) return fail(MLB_E_INVALID, "token %d at position %d is outside the vocabulary (%d)", tokens[i], i, V);
-    if (s->m->cfg.weight_dtype != MLB_DT_BF16 && s->m->cfg.weight_dtype != MLB_DT_FP8_E4M3)
-        return fail(MLB_E_UNSUPPORTED, "the scoring forward needs bf16 or FP8 weights (tensor-core columns)");
+    const char* mode = std::getenv("MLB_SCORE");
+    const bool by_steps = (mode && std::string(mode) == "step") ||
+                          (s->m->cfg.weight_dtype != MLB_DT_BF16 && s->m->cfg.weight_dtype != MLB_DT_FP8_E4M3);
+    if (by_steps) {
+        // fp32 weights (or MLB_SCORE=step): the token loop with the given ids forced in, fp32 activations, the
+        // logits of every step copied out - what the reference's trainer reads after runInference(L)
+        // (training_orchestrator.cu:308), within the fp32 bound of the decode path
+        std::vector<int32_t> first(s->B, 0), lens(s->B, 1), in(s->B, 0), out(s->B, 0);
+        first[0] = tokens[0];
+        int rc = mlb_prefill(s, first.data(), lens.data(), 1);
+        if (rc) return rc;
+        std::vector<float> row((size_t)s->B * V);
+        for (int t = 0; t < len; ++t) {
+            in[0] = tokens[t];
+            if ((rc = mlb_decode_step(s, nullptr, in.data(), out.data()))) return rc;
+            if ((rc = mlb_get_logits(s, row.data()))) return rc;
+            std::memcpy(logits_out + (size_t)t * V, row.data(), (size_t)V * 4);
+        }
+        return mlb_session_reset(s);
+    }
     int rc = mlb_session_reset(s);
     if (rc) return rc;
     bool has_attn = false;

@@ -357,6 +357,31 @@ def test_scoring_forward_matches_oracle(api, tmp_path, name, length):
     model.close()
 
 
+@pytest.mark.parametrize("name,step_mode", [("attn_fp32", False), ("mixed_ple", False), ("bf16", True)])
+def test_scoring_forward_in_fp32_activations(api, tmp_path, monkeypatch, name, step_mode):
+    """mlb_score_tokens on fp32 weights (and, with MLB_SCORE=step, on bf16 weights): the token loop with the
+    given ids forced in. Every position within the fp32 bound of the decode path (1e-3), identical argmax -
+    the precision the reference's trainer gets from runInference(L)."""
+    if step_mode:
+        monkeypatch.setenv("MLB_SCORE", "step")
+    spec = dataclasses.replace(SPECS[name], max_context=128)
+    path = write_model(tmp_path, spec, seed=33)
+    oracle = load_oracle(path)
+    tokens = random_prompts(spec.vocab, [90], seed=39)[0]
+    st = oracle.new_state()
+    want = np.stack([np.asarray(oracle.step(st, int(t))) for t in tokens])
+    model = api.Model(path)
+    sess = api.Session(model, 1)
+    got = sess.score(tokens)
+    assert got.shape == want.shape
+    assert max(logits_error(got[i], want[i]) for i in range(len(tokens))) < TOL_FP32
+    assert np.array_equal(got.argmax(axis=1), want.argmax(axis=1))
+    sess.prefill([tokens[:20]])                    # the session is reset afterwards
+    assert sess.positions().tolist() == [19]
+    sess.close()
+    model.close()
+
+
 def test_prompt_by_columns_needs_bf16_weights(api, tmp_path, monkeypatch):
     monkeypatch.setenv("MLB_PREFILL", "chunk")
     spec = SPECS["attn_fp32"]
