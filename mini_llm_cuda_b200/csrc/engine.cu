@@ -396,6 +396,7 @@ struct mlb_session {
     bool table_dirty = true;
     bool have_logits = false;
     mlb_kv_alloc alloc;
+    int attn_min_pps = 16;                    // KV pages a flash-decode split must hold before a sequence uses it
     int splits = 1, lm_rows = 32, lm_parts = 1, raw_stride = 0, max_q = 0;
     // graphs
     cudaGraphExec_t graphs[3] = {nullptr, nullptr, nullptr};
@@ -879,7 +880,7 @@ struct Chain {
                 a.page_table = s->page_table; a.pt_stride = s->max_pages;
                 a.qbuf = s->qbuf; a.gbuf = L.ng ? s->gbuf : nullptr; a.abuf = s->abuf; a.abuf16 = s->a16;
                 a.part = s->part; a.ticket = s->attn_ticket;
-                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads; a.num_pages = 0; a.err = nullptr;
+                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads; a.num_pages = 0; a.err = nullptr; a.min_pages_per_split = s->attn_min_pps;
                 if (rec) {
                     uint64_t kvb = 0, fl = 0;
                     for (int b = 0; b < B; ++b) {
@@ -1003,7 +1004,7 @@ struct Chain {
                 a.page_table = s->page_table; a.pt_stride = s->max_pages;
                 a.qbuf = s->qbuf; a.gbuf = L.ng ? s->gbuf : nullptr; a.abuf = s->abuf; a.abuf16 = nullptr;
                 a.part = s->part; a.ticket = s->attn_ticket;
-                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads; a.num_pages = 0; a.err = nullptr;
+                a.heads = cfg.heads; a.kv_heads = cfg.kv_heads; a.num_pages = 0; a.err = nullptr; a.min_pages_per_split = s->attn_min_pps;
                 if (rec) {
                     uint64_t kvb = 0, fl = 0;
                     for (int b = 0; b < B; ++b) {
@@ -1632,6 +1633,10 @@ static int session_create(mlb_model* m, int batch, int max_context, int kv_block
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, m->device);
     int want = (4 * sm_count + c.kv_heads * batch - 1) / (c.kv_heads * batch);
     s->splits = std::max(1, std::min(std::min(want, 32), std::max(1, s->max_pages / 4)));
+    if (const char* v = std::getenv("MLB_ATTN_SPLITS")) s->splits = std::max(1, std::min(32, std::atoi(v)));
+    // positions a split must hold before a sequence uses it: 256, or 1024 once one split per (kv head, sequence) fills the GPU twice
+    s->attn_min_pps = c.kv_heads * batch >= 2 * sm_count ? 64 : 16;
+    if (const char* v = std::getenv("MLB_ATTN_MIN_PAGES")) s->attn_min_pps = std::max(1, std::atoi(v));
     SA(sess_alloc(s, (void**)&s->part, B * c.heads * s->splits * (c.head_dim + 2) * 4, true));
     SA(sess_alloc(s, (void**)&s->attn_ticket, B * c.heads * 4, true));
     s->lm_rows = 16;

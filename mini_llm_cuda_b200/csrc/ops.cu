@@ -86,7 +86,7 @@ int run_attn(void* scratch, const void* kpool, const void* vpool, int kv_dtype, 
     p.kpool = kpool; p.vpool = vpool; p.page_table = page_table; p.pt_stride = pt_stride;
     p.qbuf = q; p.gbuf = gate; p.abuf = out; p.abuf16 = nullptr; p.part = sc.part; p.ticket = sc.ticket;
     p.heads = heads; p.kv_heads = kv_heads; p.hg = 1;
-    p.num_pages = num_pages; p.err = sc.err;
+    p.num_pages = num_pages; p.err = sc.err; p.min_pages_per_split = 1;
     const int G = heads / kv_heads;
     cudaError_t e;
     if (kv_dtype == MLB_DT_F32)
