@@ -1192,17 +1192,7 @@ static __global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, Samp
         hist[tid] = 0;
         __syncthreads();
         const uint32_t prefix = s_prefix, mask = s_mask;
-        for (int base = 0; base < p.V; base += 256) {
-            const int i = base + tid;
-            uint32_t key = 0;
-            if (i < p.V) {
-                if (pass == 0 || i >= kSampleKeys) {
-                    key = float_order_key(lg[i] / T);
-                    if (i < kSampleKeys) skey[i] = key;
-                } else {
-                    key = skey[i];
-                }
-            }
+        auto count = [&](int i, uint32_t key) {
             const bool ok = i < p.V && (key & mask) == prefix;
             const unsigned act = __ballot_sync(0xffffffffu, ok);
             if (ok) {
@@ -1210,18 +1200,61 @@ static __global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, Samp
                 const unsigned peers = __match_any_sync(act, bin);
                 if (lane == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
             }
+        };
+        // logits from global memory eight at a time per thread: one L2 latency per eight values instead of
+        // one per value (the ballot below consumes a value as soon as it is there); keys of later passes come
+        // from shared memory
+        for (int base = 0; base < p.V; base += 8 * 256) {
+            const bool from_global = pass == 0 || base + 8 * 256 > kSampleKeys;
+            float v[8];
+            if (from_global) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const int i = base + u * 256 + tid;
+                    v[u] = i < p.V ? lg[i] : 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * 256 + tid;
+                uint32_t key = 0;
+                if (from_global) {
+                    key = float_order_key(v[u] / T);
+                    if (pass == 0 && i < p.V && i < kSampleKeys) skey[i] = key;
+                } else if (i < p.V) {
+                    key = skey[i];
+                }
+                count(i, key);
+            }
         }
         __syncthreads();
-        if (tid == 0) {
-            uint32_t need = s_need, bin = 255;
-            for (;; --bin) {
-                uint32_t h = hist[bin];
-                if (h >= need || bin == 0) break;
-                need -= h;
+        if (tid < 32) {
+            // the bin that holds the `need`-th largest key of this digit: lane l sums bins 255 - 8l .. 248 - 8l,
+            // an exclusive scan over the lanes finds the lane, which then walks its eight bins
+            const uint32_t need = s_need;
+            uint32_t mine = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) mine += hist[255 - 8 * lane - j];
+            uint32_t incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
             }
-            s_need = need;
-            s_prefix = prefix | (bin << shift);
-            s_mask = mask | (0xffu << shift);
+            const uint32_t before = incl - mine;
+            // the last lane also takes the case of fewer than `need` candidates in all bins (k > count)
+            const bool here = (before < need && need <= incl) || (lane == 31 && incl < need);
+            if (here) {
+                uint32_t left = need - before, bin = 255 - 8 * lane;
+                for (int j = 0; j < 8; ++j, --bin) {
+                    const uint32_t h = hist[bin];
+                    if (h >= left || bin == 0) break;
+                    left -= h;
+                }
+                s_need = left;
+                s_prefix = prefix | (bin << shift);
+                s_mask = mask | (0xffu << shift);
+            }
         }
         __syncthreads();
     }
