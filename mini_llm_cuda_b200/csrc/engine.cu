@@ -1980,8 +1980,24 @@ static int decode_impl(mlb_session* s, const mlb_sampling* sp, int n, const int3
     if (n == 1 && !step_ms && !s->use_grid && !s->use_lean) {
         // the one-token call: one graph launch, one synchronisation
         if ((rc = ensure_token_graph(s, kind, in_tokens != nullptr))) return rc;
+        // The kernel that advances a sequence writes its id to pinned host memory (the error word first, by
+        // sequence 0): the host polls those words instead of synchronising the stream, which wakes it later.
+        const bool poll = seq_live(s, 0);
+        volatile int* words = s->pinned_out;
+        if (poll)
+            for (int b = 0; b < B; ++b) words[b] = seq_live(s, b) ? -2 : -1;
         CU(cudaGraphLaunch(s->tgraphs[kind * 2 + (in_tokens ? 1 : 0)], s->stream));
-        CU(cudaStreamSynchronize(s->stream));
+        bool arrived = false;
+        if (poll) {
+            const auto t0 = std::chrono::steady_clock::now();
+            for (unsigned spins = 0; !arrived; ++spins) {
+                arrived = true;
+                for (int b = 0; b < B; ++b)
+                    if (words[b] == -2) { arrived = false; break; }
+                if (!arrived && (spins & 0xfffu) == 0xfffu && std::chrono::steady_clock::now() - t0 > std::chrono::seconds(5)) break;
+            }
+        }
+        if (!arrived) CU(cudaStreamSynchronize(s->stream));
         for (int b = 0; b < B; ++b) {
             out_tokens[b] = s->pinned_out[b];
             note_outputs(s, b, &out_tokens[b], 1);
