@@ -178,14 +178,19 @@ def test_ragged_batch_matches_oracle(api, tmp_path, monkeypatch, name, batch, pa
     model.close()
 
 
-@pytest.mark.parametrize("name,batch,gemm", [("bf16", 16, "tc"), ("bf16", 40, "tc"), ("bf16_w_f32_kv", 24, "tc"), ("bf16", 5, "auto"),
-                                             ("bf16_w_f32_kv", 9, "auto"), ("fp8", 12, "auto"), ("bf16_wide_ple", 6, "auto")])
-def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name, batch, gemm):
-    """Batch >= 4 with bf16 weights (or FP8 weights, through their bf16 view) runs the projections as
-    tcgen05 GEMMs on bf16 activations.
+@pytest.mark.parametrize("name,batch,gemm,split", [("bf16", 16, "tc", 0), ("bf16", 40, "tc", 0), ("bf16_w_f32_kv", 24, "tc", 0),
+                                                   ("bf16", 5, "auto", 0), ("bf16_w_f32_kv", 9, "auto", 0), ("fp8", 12, "auto", 0),
+                                                   ("bf16_wide_ple", 6, "auto", 0), ("bf16", 40, "tc", 8), ("fp8", 12, "auto", 4),
+                                                   ("bf16_wide_ple", 6, "auto", 8), ("bf16", 16, "tc", 1)])
+def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name, batch, gemm, split):
+    """Batch >= 4 with bf16 weights, or FP8 weights widened to bf16 tile by tile inside the kernel, runs the
+    projections as tcgen05 GEMMs on bf16 activations. `split` pins the largest thread-block cluster that may
+    share the k-blocks of an output tile (0: the library's choice).
     Teacher-forced on the oracle's tokens: logits within 2e-2 at every step; the device pick equals
     the oracle's wherever the oracle's top-2 margin exceeds that bound."""
     monkeypatch.setenv("MLB_GEMM", gemm)
+    if split:
+        monkeypatch.setenv("MLB_TC_SPLIT", str(split))
     spec = SPECS[name]
     path = write_model(tmp_path, spec, seed=6)
     oracle = load_oracle(path)
@@ -222,7 +227,7 @@ BASELINE_BATCHED = {
     # the gated-delta-net stress widths (d=1024, 8 heads, key/value dim 128, ffn 2816) at batch 64, 3 of its 12 layers
     "cfg3": (dict(dim=1024, layers=3, heads=8, head_dim=128, ffn_dim=2816, vocab=2048, max_context=128, rms_eps=1e-5,
                   layer_types=periodic_layer_types(3, 1), weight_dtype="bfloat16", kv_dtype="bfloat16"), 64, False),
-    # the quantised larger model's widths (d=2048, 16 query / 4 kv heads of 128, ffn 5632, PLE 128, FP8) at batch 64, 2 layers
+    # the quantised larger model's widths (d=2048, 16 query / 4 kv heads of 128, ffn 5632, PLE 128, FP8 tiles widened in the GEMM) at batch 64, 2 layers
     "cfg4": (dict(dim=2048, layers=2, heads=16, kv_heads=4, head_dim=128, ffn_dim=5632, vocab=4096, max_context=128, rms_eps=1e-5,
                   ple_dim=128, layer_types=periodic_layer_types(2, 2), weight_dtype="float8_e4m3", kv_dtype="bfloat16"), 64, False),
 }
