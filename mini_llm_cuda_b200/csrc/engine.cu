@@ -396,7 +396,7 @@ struct mlb_session {
     bool table_dirty = true;
     bool have_logits = false;
     mlb_kv_alloc alloc;
-    int attn_min_pps = 16;                    // KV pages a flash-decode split must hold before a sequence uses it
+    int attn_min_pps = 11;                    // KV pages a flash-decode split must hold before a sequence uses it
     int splits = 1, lm_rows = 32, lm_parts = 1, raw_stride = 0, max_q = 0;
     // graphs
     cudaGraphExec_t graphs[3] = {nullptr, nullptr, nullptr};
@@ -1634,8 +1634,11 @@ static int session_create(mlb_model* m, int batch, int max_context, int kv_block
     int want = (4 * sm_count + c.kv_heads * batch - 1) / (c.kv_heads * batch);
     s->splits = std::max(1, std::min(std::min(want, 32), std::max(1, s->max_pages / 4)));
     if (const char* v = std::getenv("MLB_ATTN_SPLITS")) s->splits = std::max(1, std::min(32, std::atoi(v)));
-    // positions a split must hold before a sequence uses it: 256, or 1024 once one split per (kv head, sequence) fills the GPU twice
-    s->attn_min_pps = c.kv_heads * batch >= 2 * sm_count ? 64 : 16;
+    // pages a split must hold before a sequence uses it (the grid above already caps the splits at about four
+    // CTAs per SM). Measured: cfg1 at 32 / 64 sequences and a context of 260, one split beats two (12.6 vs 15.5,
+    // 16.3 vs 22.8 us per launch); the GQA model at 64 sequences and a context of 576, three splits of 11 pages
+    // beat two of 18 and four of 9 (63 vs 78 and 74 us).
+    s->attn_min_pps = 11;
     if (const char* v = std::getenv("MLB_ATTN_MIN_PAGES")) s->attn_min_pps = std::max(1, std::atoi(v));
     SA(sess_alloc(s, (void**)&s->part, B * c.heads * s->splits * (c.head_dim + 2) * 4, true));
     SA(sess_alloc(s, (void**)&s->attn_ticket, B * c.heads * 4, true));

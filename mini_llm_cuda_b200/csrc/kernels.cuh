@@ -659,8 +659,7 @@ struct AttnParams {
     int num_pages;
     int* err;
     // A split is worth its partials and the combine only with enough positions in it: a sequence uses
-    // min(grid splits, pages / min_pages_per_split) of them (measured at a context of 260: one split beats two by
-    // 16.3 vs 22.8 us per launch at 64 sequences, 12.6 vs 15.5 at 32). 1 = every page may be a split.
+    // min(grid splits, pages / min_pages_per_split) of them. 1 = every page may be a split.
     int min_pages_per_split;
 };
 
