@@ -53,6 +53,12 @@ SPECS = {
                            layer_types=periodic_layer_types(2, 2), weight_dtype="bfloat16", kv_dtype="bfloat16"),
     "fp8": small(dim=256, heads=4, kv_heads=2, ple_dim=32, layers=4, layer_types=periodic_layer_types(4, 4),
                  weight_dtype="float8_e4m3", kv_dtype="bfloat16"),
+    # widths that end inside a tile: k-blocks of 64 (d = 192 = 3 blocks, ffn 328 = 5.1 blocks, PLE 24), row tiles of
+    # 128 (ffn 328, vocabulary 1000, delta-net projection 3 * (2 * 64 + 64) + 6 = 582 rows), QK-norm and gating on
+    "odd_bf16": small(dim=192, heads=3, head_dim=64, ffn_dim=328, vocab=1000, ple_dim=24, layers=4, qk_norm=True,
+                      query_gating=True, layer_types=periodic_layer_types(4, 2), weight_dtype="bfloat16", kv_dtype="bfloat16"),
+    "odd_fp8": small(dim=192, heads=3, head_dim=64, ffn_dim=336, vocab=1000, ple_dim=24, layers=4, qk_norm=True,
+                     layer_types=periodic_layer_types(4, 2), weight_dtype="float8_e4m3", kv_dtype="bfloat16"),
 }
 
 
@@ -181,7 +187,8 @@ def test_ragged_batch_matches_oracle(api, tmp_path, monkeypatch, name, batch, pa
 @pytest.mark.parametrize("name,batch,gemm,split", [("bf16", 16, "tc", 0), ("bf16", 40, "tc", 0), ("bf16_w_f32_kv", 24, "tc", 0),
                                                    ("bf16", 5, "auto", 0), ("bf16_w_f32_kv", 9, "auto", 0), ("fp8", 12, "auto", 0),
                                                    ("bf16_wide_ple", 6, "auto", 0), ("bf16", 40, "tc", 8), ("fp8", 12, "auto", 4),
-                                                   ("bf16_wide_ple", 6, "auto", 8), ("bf16", 16, "tc", 1)])
+                                                   ("bf16_wide_ple", 6, "auto", 8), ("bf16", 16, "tc", 1), ("odd_bf16", 21, "auto", 0),
+                                                   ("odd_bf16", 21, "auto", 4), ("odd_fp8", 37, "auto", 0), ("odd_fp8", 37, "auto", 2)])
 def test_tensor_core_batch_path_matches_oracle(api, tmp_path, monkeypatch, name, batch, gemm, split):
     """Batch >= 4 with bf16 weights, or FP8 weights widened to bf16 tile by tile inside the kernel, runs the
     projections as tcgen05 GEMMs on bf16 activations. `split` pins the largest thread-block cluster that may
@@ -286,11 +293,12 @@ def test_baseline_batched_shapes_match_oracle(api, tmp_path, name):
 
 @pytest.mark.parametrize("name,lens,decode_path", [("bf16", [131], "chain"), ("bf16", [1, 2, 130, 60, 201, 17], "auto"),
                                                    ("bf16_w_f32_kv", [300, 5, 129], "chain"), ("bf16", [257], "grid"),
-                                                   ("fp8", [280, 3, 70], "auto")])
+                                                   ("fp8", [280, 3, 70], "auto"), ("odd_fp8", [90, 2, 77, 31], "auto"),
+                                                   ("odd_bf16", [101, 64], "auto")])
 def test_prompt_by_columns_matches_oracle(api, tmp_path, monkeypatch, name, lens, decode_path):
     """The prompt consumed as columns of tensor-core steps (256 per chunk; prompts that end inside a
     chunk, span several, or have a single token), attention and delta-net layers mixed, PLE; FP8
-    weights run the columns on their bf16 view: the
+    weights are widened tile by tile inside the GEMMs: the
     decode steps that follow, teacher-forced on the oracle's tokens, give its logits within 2e-2,
     and the positions are those the token loop leaves."""
     monkeypatch.setenv("MLB_PREFILL", "chunk")
