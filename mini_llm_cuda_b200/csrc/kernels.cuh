@@ -1191,13 +1191,20 @@ static __global__ void __launch_bounds__(256) sample_topk_kernel(StepCtl c, Samp
         hist[tid] = 0;
         __syncthreads();
         const uint32_t prefix = s_prefix, mask = s_mask;
+        // The first digit (sign and exponent bits) is shared by most logits: lanes with the same bin add once
+        // (__match_any_sync). From the second digit on only the few keys under the chosen prefix count and their
+        // bins differ: plain atomics, no warp-wide exchange.
         auto count = [&](int i, uint32_t key) {
             const bool ok = i < p.V && (key & mask) == prefix;
-            const unsigned act = __ballot_sync(0xffffffffu, ok);
-            if (ok) {
-                const uint32_t bin = (key >> shift) & 0xffu;
-                const unsigned peers = __match_any_sync(act, bin);
-                if (lane == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
+            const uint32_t bin = (key >> shift) & 0xffu;
+            if (pass == 0) {
+                const unsigned act = __ballot_sync(0xffffffffu, ok);
+                if (ok) {
+                    const unsigned peers = __match_any_sync(act, bin);
+                    if (lane == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
+                }
+            } else if (ok) {
+                atomicAdd(&hist[bin], 1u);
             }
         };
         // logits from global memory eight at a time per thread: one L2 latency per eight values instead of
