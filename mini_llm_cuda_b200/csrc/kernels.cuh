@@ -941,8 +941,15 @@ __global__ void __launch_bounds__(256) delta_net_kernel(StepCtl c, const float* 
     for (int i = 0; i < ROWS_PER_WARP; ++i) {
         int row = row0 + i;
         if (row < dv) {
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) s[i][e] = __ldcg(&Sh[(size_t)row * DK + lane * EPL + e]);
+            // one vector load per lane and row: a warp reads the row's DK floats as one contiguous piece (element by
+            // element, each instruction touched every sector of the row again: four L2 requests per sector at DK = 128)
+            if (EPL == 4) {
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(&Sh[(size_t)row * DK + lane * 4]));
+                s[i][0] = t.x; s[i][1] = t.y; s[i][2 % EPL] = t.z; s[i][3 % EPL] = t.w;
+            } else {
+                const float2 t = __ldcg(reinterpret_cast<const float2*>(&Sh[(size_t)row * DK + lane * 2]));
+                s[i][0] = t.x; s[i][1] = t.y;
+            }
         } else {
 #pragma unroll
             for (int e = 0; e < EPL; ++e) s[i][e] = 0.f;
@@ -989,8 +996,8 @@ __global__ void __launch_bounds__(256) delta_net_kernel(StepCtl c, const float* 
         for (int e = 0; e < EPL; ++e) { s[i][e] = fmaf(cf, kn[e], s[i][e]); d2 = fmaf(s[i][e], qn[e], d2); }
         d2 = warp_sum(d2);
         if (row < dv) {
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) Sh[(size_t)row * DK + lane * EPL + e] = s[i][e];
+            if (EPL == 4) *reinterpret_cast<float4*>(&Sh[(size_t)row * DK + lane * 4]) = make_float4(s[i][0], s[i][1], s[i][2 % EPL], s[i][3 % EPL]);
+            else *reinterpret_cast<float2*>(&Sh[(size_t)row * DK + lane * 2]) = make_float2(s[i][0], s[i][1]);
             if (lane == 0) {
                 abuf[((size_t)b * H + h) * dv + row] = d2;
                 if (abuf16) abuf16[((size_t)b * H + h) * dv + row] = __float2bfloat16_rn(d2);
@@ -1055,9 +1062,19 @@ __global__ void __launch_bounds__(256) delta_net_cols_kernel(StepCtl c, const in
     float* Sh = state + ((size_t)cur * H + h) * (size_t)dv * DK;
     float s[ROWS_PER_WARP][EPL];
 #pragma unroll
-    for (int i = 0; i < ROWS_PER_WARP; ++i)
+    for (int i = 0; i < ROWS_PER_WARP; ++i) {
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) s[i][e] = row0 + i < dv ? __ldcg(&Sh[(size_t)(row0 + i) * DK + lane * EPL + e]) : 0.f;
+        for (int e = 0; e < EPL; ++e) s[i][e] = 0.f;
+        if (row0 + i < dv) {                     // one vector load per lane and row, as in delta_net_kernel
+            if (EPL == 4) {
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(&Sh[(size_t)(row0 + i) * DK + lane * 4]));
+                s[i][0] = t.x; s[i][1] = t.y; s[i][2 % EPL] = t.z; s[i][3 % EPL] = t.w;
+            } else {
+                const float2 t = __ldcg(reinterpret_cast<const float2*>(&Sh[(size_t)(row0 + i) * DK + lane * 2]));
+                s[i][0] = t.x; s[i][1] = t.y;
+            }
+        }
+    }
     // one column's inputs: normalised q and k of the head (EPL values per lane), the warp's 4 values
     // of v, the two gates
     float qn[EPL], kn[EPL], vr[ROWS_PER_WARP], beta, alpha;
@@ -1119,9 +1136,10 @@ __global__ void __launch_bounds__(256) delta_net_cols_kernel(StepCtl c, const in
     }
 #pragma unroll
     for (int i = 0; i < ROWS_PER_WARP; ++i)
-        if (row0 + i < dv)
-#pragma unroll
-            for (int e = 0; e < EPL; ++e) Sh[(size_t)(row0 + i) * DK + lane * EPL + e] = s[i][e];
+        if (row0 + i < dv) {
+            if (EPL == 4) *reinterpret_cast<float4*>(&Sh[(size_t)(row0 + i) * DK + lane * 4]) = make_float4(s[i][0], s[i][1], s[i][2 % EPL], s[i][3 % EPL]);
+            else *reinterpret_cast<float2*>(&Sh[(size_t)(row0 + i) * DK + lane * 2]) = make_float2(s[i][0], s[i][1]);
+        }
 }
 
 // ------------------------------------------------------------------------------------
